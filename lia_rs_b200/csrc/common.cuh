@@ -1,0 +1,64 @@
+// Shared helpers of the sm_100a kernel library.
+//
+// Conventions of every launcher in this library:
+//  * exported with C linkage, called from Python through ctypes;
+//  * returns 0 on success or a negative code (see LIA_ERR_*), never throws, never allocates;
+//  * validates sizes on the host before the launch and refuses what the kernel cannot
+//    compute rather than computing it wrongly;
+//  * runs on the stream it is given.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LIA_OK 0
+#define LIA_ERR_SIZE (-1)        // a size the kernel refuses
+#define LIA_ERR_ALIGN (-2)       // a pointer or stride that is not aligned as required
+#define LIA_ERR_LAUNCH (-3)      // cudaGetLastError() after the launch was not cudaSuccess
+#define LIA_ERR_DRIVER (-4)      // a driver entry point (tensor map encode) is missing or failed
+#define LIA_ERR_DTYPE (-5)       // a combination of element types that has no instantiation
+
+#define LIA_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Element type codes shared with the Python side.
+#define LIA_F32 0
+#define LIA_BF16 1
+
+static inline int lia_check_launch() {
+    return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
+}
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads.  `scratch` holds 32 floats of shared memory.
+// The order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int warps = (blockDim.x + 31) >> 5;
+    float total = (lane < warps) ? scratch[lane] : 0.f;
+    total = warp_sum(total);
+    return total;
+}

@@ -1,0 +1,177 @@
+// Embedding gather, RMSNorm, and the rotary encoding fused with the key/value append.
+// Every kernel takes all sizes as arguments; the residual stream is always 32-bit.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// Embedding: h[t, :] = table[token_t, :] * scale, written in 32-bit.
+// A token id outside [0, vocab) writes zeros and raises the error flag (no read out of range).
+template <typename TW>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                 float* __restrict__ out, int n_tokens, int hidden, int vocab,
+                                 float scale, int* __restrict__ error_flag) {
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    const int token = tokens[t];
+    const bool ok = token >= 0 && token < vocab;
+    if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+    const TW* row = table + (size_t)(ok ? token : 0) * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        dst[i] = ok ? to_float(row[i]) * scale : 0.f;
+}
+
+LIA_EXPORT int lia_embedding(const int* tokens, const void* table, int table_dtype, float* out,
+                             int n_tokens, int hidden, int vocab, float scale, int* error_flag,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return LIA_OK;
+    if (hidden <= 0 || vocab <= 0) return LIA_ERR_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == LIA_BF16)
+        embedding_kernel<<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out,
+                                                           n_tokens, hidden, vocab, scale, error_flag);
+    else if (table_dtype == LIA_F32)
+        embedding_kernel<<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, n_tokens,
+                                                           hidden, vocab, scale, error_flag);
+    else
+        return LIA_ERR_DTYPE;
+    return lia_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm of 32-bit rows: y = x * rsqrt(mean(x^2) + eps) * w * out_scale.
+// Sum of squares, mean, eps and the reciprocal root are 32-bit; the order of the additions
+// depends on `hidden` alone, not on the number of rows.  `rows_index` (optional) gathers:
+// output row r is computed from input row rows_index[r] (negative index -> zeros).
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
+                               const TW* __restrict__ weight, TO* __restrict__ out, int rows,
+                               int hidden, float eps, float out_scale) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int src = rows_index ? rows_index[r] : r;
+    TO* dst = out + (size_t)r * hidden;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<TO>(0.f);
+        return;
+    }
+    const float* row = x + (size_t)src * hidden;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = row[i];
+        sum = fmaf(v, v, sum);
+    }
+    sum = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(sum / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        dst[i] = from_float<TO>(row[i] * inv * to_float(weight[i]) * out_scale);
+}
+
+LIA_EXPORT int lia_rmsnorm(const float* x, const int* rows_index, const void* weight, int weight_dtype,
+                           void* out, int out_dtype, int rows, int hidden, float eps, float out_scale,
+                           cudaStream_t stream) {
+    if (rows <= 0) return LIA_OK;
+    if (hidden <= 0) return LIA_ERR_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+#define LIA_NORM(TW, TO)                                                                          \
+    rmsnorm_kernel<TW, TO><<<rows, threads, 0, stream>>>(x, rows_index, (const TW*)weight, (TO*)out, \
+                                                         rows, hidden, eps, out_scale)
+    if (weight_dtype == LIA_BF16 && out_dtype == LIA_BF16) LIA_NORM(__nv_bfloat16, __nv_bfloat16);
+    else if (weight_dtype == LIA_BF16 && out_dtype == LIA_F32) LIA_NORM(__nv_bfloat16, float);
+    else if (weight_dtype == LIA_F32 && out_dtype == LIA_BF16) LIA_NORM(float, __nv_bfloat16);
+    else if (weight_dtype == LIA_F32 && out_dtype == LIA_F32) LIA_NORM(float, float);
+    else return LIA_ERR_DTYPE;
+#undef LIA_NORM
+    return lia_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotary encoding (rotate-half over the first `rotary_dim` elements of each head; 0 = none)
+// of q and k, fused with the append of k and v to the paged cache.
+//   qkv      [n_tokens, (nq + 2 nkv) d] 32-bit: q heads, then k heads, then v heads
+//   q_out    [n_tokens, nq d]
+//   k_pages, v_pages [num_pages, page_size, nkv, d]
+//   block_table [slots, table_stride]: page of (slot, position / page_size)
+//   inv_freq [rotary_dim / 2] 32-bit: theta^(-2i/rotary_dim), rounded once from 64-bit on the host
+// The angle pos * inv_freq[i] and its sine and cosine are 32-bit (the reference likewise casts
+// the position to f32 and multiplies: src/gpu/kernels/llama_position.rs:35-46).
+// A token whose slot is negative is padding and is skipped.  `write_kv` = 0 leaves the cache
+// alone (a layer that reads another layer's cache).
+template <typename TQ, typename TC>
+__global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                               const int* __restrict__ slots, const int* __restrict__ block_table,
+                               int table_stride, TQ* __restrict__ q_out, TC* __restrict__ k_pages,
+                               TC* __restrict__ v_pages, int n_tokens, int nq, int nkv, int d,
+                               int rotary_dim, const float* __restrict__ inv_freq, int page_size,
+                               int num_pages, int write_kv, int* __restrict__ error_flag) {
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const int width = (nq + 2 * nkv) * d;
+    const float* row = qkv + (size_t)t * width;
+    const int half = rotary_dim / 2;
+    size_t cache_row = 0;
+    bool cache_ok = false;
+    if (write_kv) {
+        const int page = block_table[(size_t)slot * table_stride + pos / page_size];
+        cache_ok = page >= 0 && page < num_pages;
+        if (!cache_ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+        cache_row = ((size_t)(cache_ok ? page : 0) * page_size + pos % page_size) * nkv * d;
+    }
+    const int rot_heads = nq + nkv;
+    // rotated part: one work item per (head, i < half)
+    for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
+        const int head = w / half, i = w % half;
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float a = row[head * d + i], b = row[head * d + i + half];
+        const float ra = a * c - b * s, rb = b * c + a * s;
+        if (head < nq) {
+            TQ* dst = q_out + (size_t)t * nq * d + head * d;
+            dst[i] = from_float<TQ>(ra);
+            dst[i + half] = from_float<TQ>(rb);
+        } else if (cache_ok) {
+            TC* dst = k_pages + cache_row + (head - nq) * d;
+            dst[i] = from_float<TC>(ra);
+            dst[i + half] = from_float<TC>(rb);
+        }
+    }
+    // pass-through part of q and k (elements beyond rotary_dim)
+    const int rest = d - rotary_dim;
+    if (rest > 0) {
+        for (int w = threadIdx.x; w < rot_heads * rest; w += blockDim.x) {
+            const int head = w / rest, i = rotary_dim + w % rest;
+            const float a = row[head * d + i];
+            if (head < nq) q_out[(size_t)t * nq * d + head * d + i] = from_float<TQ>(a);
+            else if (cache_ok) k_pages[cache_row + (head - nq) * d + i] = from_float<TC>(a);
+        }
+    }
+    if (cache_ok) {
+        const float* v = row + (nq + nkv) * d;
+        for (int w = threadIdx.x; w < nkv * d; w += blockDim.x)
+            v_pages[cache_row + w] = from_float<TC>(v[w]);
+    }
+}
+
+LIA_EXPORT int lia_rope_kv_write(const float* qkv, const int* positions, const int* slots,
+                                 const int* block_table, int table_stride, void* q_out, void* k_pages,
+                                 void* v_pages, int dtype, int n_tokens, int nq, int nkv, int d,
+                                 int rotary_dim, const float* inv_freq, int page_size, int num_pages,
+                                 int write_kv, int* error_flag, cudaStream_t stream) {
+    if (n_tokens <= 0) return LIA_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > d ||
+        (rotary_dim & 1) || (rotary_dim > 0 && !inv_freq))
+        return LIA_ERR_SIZE;
+    const int threads = 256;
+#define LIA_ROPE(T)                                                                                 \
+    rope_kv_kernel<T, T><<<n_tokens, threads, 0, stream>>>(                                         \
+        qkv, positions, slots, block_table, table_stride, (T*)q_out, (T*)k_pages, (T*)v_pages,      \
+        n_tokens, nq, nkv, d, rotary_dim, inv_freq, page_size, num_pages, write_kv, error_flag)
+    if (dtype == LIA_BF16) LIA_ROPE(__nv_bfloat16);
+    else if (dtype == LIA_F32) LIA_ROPE(float);
+    else return LIA_ERR_DTYPE;
+#undef LIA_ROPE
+    return lia_check_launch();
+}

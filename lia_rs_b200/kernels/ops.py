@@ -1,0 +1,142 @@
+"""Python faces of the CUDA entry points.  Every function takes CUDA tensors, checks what the
+kernel assumes, launches on the current stream and raises on a refusal; there is no CPU or
+library fallback here."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+GEMM_STORE, GEMM_ACCUM, GEMM_SWIGLU = 0, 1, 2
+
+_ERRORS = {-1: "a size the kernel refuses", -2: "a pointer or stride that is not aligned as required",
+           -3: "the launch failed (cudaGetLastError)", -4: "a driver entry point is missing or failed",
+           -5: "no instantiation for this combination of element types"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = build.load()
+        for name in dir(_Signatures):
+            if name.startswith("lia_"):
+                fn = getattr(_lib, name)
+                fn.argtypes = getattr(_Signatures, name)
+                fn.restype = c_int
+    return _lib
+
+
+class _Signatures:
+    lia_embedding = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+    lia_rmsnorm = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p]
+    lia_rope_kv_write = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                         c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+    lia_gemm_simt = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                     c_int, c_int, c_float, c_void_p]
+    lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {dtype} has no kernel")
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernels need contiguous CUDA tensors (there is no CPU path)")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, code)}")
+
+
+def embedding(tokens, table, out, scale: float, error_flag=None):
+    _cuda(tokens, table, out, error_flag)
+    n, hidden = out.shape
+    _check(lib().lia_embedding(_p(tokens), _p(table), dtype_code(table.dtype), _p(out), n, hidden,
+                               table.shape[0], scale, _p(error_flag), _stream()), "embedding")
+
+
+def rmsnorm(x, weight, out, eps: float, out_scale: float = 1.0, rows_index=None):
+    _cuda(x, weight, out, rows_index)
+    rows, hidden = out.shape
+    if x.dtype != torch.float32 or x.shape[1] != hidden:
+        raise KernelError("rmsnorm takes 32-bit rows of the same width as its output")
+    _check(lib().lia_rmsnorm(_p(x), _p(rows_index), _p(weight), dtype_code(weight.dtype), _p(out),
+                             dtype_code(out.dtype), rows, hidden, eps, out_scale, _stream()), "rmsnorm")
+
+
+def rope_kv_write(qkv, positions, slots, block_table, q_out, k_pages, v_pages, nq, nkv, d, rotary_dim,
+                  inv_freq, write_kv=True, error_flag=None):
+    _cuda(qkv, positions, slots, block_table, q_out, k_pages, v_pages, inv_freq, error_flag)
+    n = qkv.shape[0]
+    if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
+        raise KernelError("rope_kv_write takes 32-bit q|k|v rows")
+    if q_out.dtype != k_pages.dtype or k_pages.dtype != v_pages.dtype:
+        raise KernelError("rope_kv_write: q and the cache must have one element type")
+    num_pages, page_size = k_pages.shape[0], k_pages.shape[1]
+    _check(lib().lia_rope_kv_write(_p(qkv), _p(positions), _p(slots), _p(block_table), block_table.shape[1],
+                                   _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), n, nq, nkv, d,
+                                   rotary_dim, _p(inv_freq), page_size, num_pages, 1 if write_kv else 0,
+                                   _p(error_flag), _stream()), "rope_kv_write")
+
+
+def gemm_simt(mode, a, w, out, alpha: float = 1.0):
+    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the 32-bit pipes; see csrc/gemm_simt.cu."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = out.shape[1]
+    rows_w = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or rows_w != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(lib().lia_gemm_simt(mode, _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
+                               w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0), M, N, K, alpha,
+                               _stream()), "gemm_simt")
+
+
+def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale):
+    _cuda(q, k_pages, v_pages, positions, slots, block_table, out)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
+        raise KernelError("attention: q, cache and out must have one element type")
+    n = q.shape[0]
+    _check(lib().lia_attention_generic(_p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(positions),
+                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), n, nq, nkv,
+                                       d, k_pages.shape[1], int(window or 0), scale, _stream()),
+           "attention_generic")
+
+
+def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
+    _cuda(logits, out, temperature, seeds, positions)
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or out.dtype != torch.int32:
+        raise KernelError("select_tokens takes 32-bit logits and writes int32 tokens")
+    if temperature is not None and (seeds is None or positions is None):
+        raise KernelError("select_tokens: temperature needs seeds and positions")
+    _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
+                                   _p(positions), _p(out), rows, _stream()), "select_tokens")

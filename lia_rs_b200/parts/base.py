@@ -1,0 +1,163 @@
+"""Interfaces of the parts a decoder layer is put together from, and one registry per kind.
+
+A layer is an *arrangement* (how norms, mixer, feed-forward and the residual stream are wired)
+of four kinds of parts:
+
+  mixer              moves information between positions (attention here); may own a cache
+                     (keys and values in pages) and/or per-request state of fixed size
+  feed-forward       acts on each position alone (dense SwiGLU here; experts elsewhere)
+  norm               normalises rows of the residual stream
+  position encoding  how positions enter the mixer (rotary here)
+
+Every part is built from a `PartSpec` (its kind and its parameters: all sizes and constants)
+and from the tensors it declared.  No part knows which model it is in: the model builder
+(`models/`) chooses the parts layer by layer from the configuration.
+
+The residual stream is always a 32-bit tensor [tokens, hidden].  Mixers and feed-forwards obey
+one contract: `forward(ctx, x, residual, scale, ...)` ADDS `scale * f(x)` into `residual`
+in place, where x is the normalised input in the compute element type.  This lets a part fuse
+the residual sum into its last kernel, and lets a toy part do `residual.add_(y, alpha=scale)`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str
+    params: dict = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
+class KVCacheRequest:
+    """What a mixer needs from the paged cache: `kv_heads` x `head_dim` keys and values per
+    token, all of them (`window` None) or the last `window` of them."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Per-request state of fixed size: one tensor of `shape` and `dtype` per live request,
+    zeroed when the request is admitted."""
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+class Runtime:
+    """Device and compute element type of one engine; parts launch kernels through `ops`."""
+
+    def __init__(self, device, compute_dtype: torch.dtype):
+        from ..kernels import ops
+        if compute_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("compute element type must be float32 or bfloat16")
+        self.device = torch.device(device)
+        self.compute_dtype = compute_dtype
+        self.ops = ops
+
+
+class Part:
+    """Base of all parts.  `tensor_specs` declares the checkpoint tensors (names relative to
+    `prefix`); `__init__` receives them already on the device, in their storage element type."""
+
+    @staticmethod
+    def tensor_specs(params: dict, prefix: str) -> list:
+        return []
+
+    def __init__(self, params: dict, tensors: dict, prefix: str, runtime: Runtime):
+        self.params = params
+        self.runtime = runtime
+
+
+class Norm(Part):
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows_index=None, out_scale: float = 1.0):
+        """out[r] = norm(x[rows_index[r]] or x[r]) * out_scale; x 32-bit, out compute type."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Owned by a mixer.  Encodes q and k in place of the mixer and appends k, v to the cache."""
+
+    def encode_and_store(self, ctx, qkv: torch.Tensor, q_out: torch.Tensor, kv, nq: int, nkv: int, d: int):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    @staticmethod
+    def cache_request(params: dict) -> Optional[KVCacheRequest]:
+        return None
+
+    @staticmethod
+    def state_request(params: dict) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, scale: float, kv=None, state=None):
+        """residual += scale * mixer(x).  `kv` is the layer's `cache.KVView` (or None), `state`
+        the tensor [slots, *shape] of its per-request state (or None)."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, scale: float):
+        """residual += scale * feed_forward(x)."""
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How one layer wires its parts around the residual stream."""
+
+    @staticmethod
+    def tensor_specs(layer_spec, prefix: str) -> list:
+        raise NotImplementedError
+
+    def __init__(self, layer_spec, tensors: dict, prefix: str, runtime: Runtime):
+        raise NotImplementedError
+
+    def forward(self, ctx, residual: torch.Tensor, kv=None, state=None):
+        raise NotImplementedError
+
+
+MIXERS: dict = {}
+FEED_FORWARDS: dict = {}
+NORMS: dict = {}
+POSITION_ENCODINGS: dict = {}
+ARRANGEMENTS: dict = {}
+
+
+def _register(table: dict, kind: str):
+    def decorate(cls):
+        table[kind] = cls
+        cls.kind = kind
+        return cls
+    return decorate
+
+
+def register_mixer(kind: str):
+    return _register(MIXERS, kind)
+
+
+def register_feed_forward(kind: str):
+    return _register(FEED_FORWARDS, kind)
+
+
+def register_norm(kind: str):
+    return _register(NORMS, kind)
+
+
+def register_position_encoding(kind: str):
+    return _register(POSITION_ENCODINGS, kind)
+
+
+def register_arrangement(kind: str):
+    return _register(ARRANGEMENTS, kind)
+
+
+def lookup(table: dict, kind: str, what: str):
+    if kind not in table:
+        raise KeyError(f"unknown {what} {kind!r}; registered: {sorted(table)}")
+    return table[kind]

@@ -1,0 +1,24 @@
+"""Matrix products of the parts: out (op)= alpha * a @ w^T with an epilogue.
+
+`prepare_weight` brings a checkpoint matrix to the compute element type once, at load.
+`linear` chooses the kernel: the tcgen05 kernel for bfloat16 when the shape allows it, else the
+product on the 32-bit pipes (always, for the 32-bit path)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+STORE, ACCUM, SWIGLU = ops.GEMM_STORE, ops.GEMM_ACCUM, ops.GEMM_SWIGLU
+
+
+def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
+    return weight.to(runtime.compute_dtype).contiguous()
+
+
+def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
+    fast = getattr(ops, "gemm_tc", None)
+    if fast is not None and a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
+        fast(mode, a, w, out, alpha)
+    else:
+        ops.gemm_simt(mode, a, w, out, alpha)

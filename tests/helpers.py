@@ -1,0 +1,127 @@
+"""Shared by the tests: the tiny configurations, model folders with random weights, traces and
+the comparison with the plain implementation."""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+import torch
+
+import plain_impl
+
+# Three tiny configurations of the architecture that differ in every size and option: head counts and
+# groups (2:1, multi-query 3:1, 2:1 with a head size that is no power of two), widths, layers,
+# vocabulary, theta, eps, tied or untied head, MiniCPM's scalars present or absent, page size, and
+# (tiny-C) a sliding window on one of two layers, which gives the cache two groups of pages.
+TINY = {
+    "tiny-A": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=64,
+                    intermediate_size=192, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=16, vocab_size=256, max_position_embeddings=256, rms_norm_eps=1e-5,
+                    rope_theta=10000.0, tie_word_embeddings=True, scale_emb=12, scale_depth=1.4,
+                    dim_model_base=32, initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=0, page_size=8),
+    "tiny-B": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=96,
+                    intermediate_size=256, num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1,
+                    head_dim=32, vocab_size=384, max_position_embeddings=512, rms_norm_eps=1e-6,
+                    rope_theta=1e6, tie_word_embeddings=False, scale_emb=1, scale_depth=1.0,
+                    dim_model_base=96, initializer_range=0.05, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=2, page_size=16),
+    "tiny-C": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=144,
+                    intermediate_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3,
+                    head_dim=48, vocab_size=301, max_position_embeddings=384, rms_norm_eps=3e-6,
+                    rope_theta=50000.0, tie_word_embeddings=False, sliding_window=21,
+                    layer_types=["sliding_attention", "full_attention"], initializer_range=0.03,
+                    hidden_act="silu", torch_dtype="bfloat16"),
+        seed=7, page_size=4),
+}
+
+# q and k projections are scaled up so that attention is peaked: with the usual small random
+# weights every key gets nearly the same probability and a wrong or missing key would hide.
+SHARPEN = 6.0
+
+
+def make_model(folder: str, name: str) -> dict:
+    """Write the folder through the package's random-weights mode, then sharpen q/k and rewrite.
+    Returns {dir, config (dict), weights (dict by checkpoint name, as stored), page_size}."""
+    from safetensors.torch import load_file, save_file
+
+    from lia_rs_b200 import LlamaConfig, write_random_model
+    entry = TINY[name]
+    write_random_model(LlamaConfig.from_dict(entry["config"]), folder, seed=entry["seed"])
+    path = os.path.join(folder, "model.safetensors")
+    weights = load_file(path)            # the safetensors library, independent of the package's reader
+    for key in list(weights):
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            weights[key] = (weights[key].float() * SHARPEN).to(torch.bfloat16)
+    save_file(weights, path)
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    return dict(dir=folder, config=config, weights=weights, page_size=entry["page_size"], name=name)
+
+
+def random_tokens(vocab: int, count: int, seed: int) -> list:
+    rng = np.random.default_rng(seed)
+    return [int(t) for t in rng.integers(0, vocab, size=count)]
+
+
+_PLAIN_CACHE = {}
+
+
+def plain_logits(model: dict, tokens) -> torch.Tensor:
+    """64-bit logits [T, V] of the plain implementation (cached per model and sequence)."""
+    key = (model["name"], tuple(tokens))
+    if key not in _PLAIN_CACHE:
+        _PLAIN_CACHE[key] = plain_impl.forward(model["config"], model["weights"], tokens, torch.float64)
+    return _PLAIN_CACHE[key]
+
+
+# Tolerances, fixed once from the size of rounding in each path and never widened to pass:
+#  * float32: products and sums of ~100-300 terms in 32-bit; logits are O(1)..O(10).
+#  * bfloat16: activations between kernels, the cache and the probabilities are rounded to 8 bits of
+#    mantissa (relative 2^-9 each); errors add up over layers.  Measured against the logits' scale.
+def tolerance(dtype: str, reference: torch.Tensor) -> float:
+    scale = max(1.0, float(reference.abs().max()))
+    return (2e-4 if dtype == "float32" else 4e-2) * scale
+
+
+def assert_close(actual, reference, dtype: str, what: str):
+    actual = torch.as_tensor(np.asarray(actual), dtype=torch.float64)
+    reference = reference.to(torch.float64)
+    assert actual.shape == reference.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(reference.shape)}"
+    assert torch.isfinite(actual).all(), f"{what}: non-finite logits"
+    error = (actual - reference).abs()
+    worst = float(error.max())
+    limit = tolerance(dtype, reference)
+    if worst > limit:
+        row = int(error.max(dim=-1).values.argmax()) if error.dim() > 1 else 0
+        raise AssertionError(f"{what}: max abs error {worst:.3e} > {limit:.3e} (first at wanted row {row})")
+
+
+class Replayer:
+    """Drives an Engine the way bin/trace_run does, in process: requests by name, their positions,
+    reservation of pages, release at `end`."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.live = {}
+
+    def step(self, entries, end=()):
+        from lia_rs_b200.engine import StepEntry
+        batch = []
+        for name, tokens, want in entries:
+            if name not in self.live:
+                self.live[name] = [self.engine.admit(), 0]
+            slot, fed = self.live[name]
+            assert self.engine.reserve(slot, fed, fed + len(tokens)), "pool exhausted"
+            batch.append(StepEntry(slot, list(tokens), fed, list(want)))
+            self.live[name][1] = fed + len(tokens)
+        logits = self.engine.step(batch).float().cpu().numpy().copy() if batch else None
+        self.engine.synchronize()
+        for name in end:
+            self.engine.release(self.live.pop(name)[0])
+        self.engine.cache.check()
+        return logits

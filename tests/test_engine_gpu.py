@@ -1,0 +1,188 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way of
+cutting the work: whole, most + last 32 one by one, portions of changing size, and mixed batches
+with so few pages that they are used again."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+MODELS = list(helpers.TINY)
+LENGTHS = [1, 2, 9, 17, 41, 70, 100]
+
+
+def make_engine(model, dtype, max_tokens, max_seqs=4):
+    from lia_rs_b200.engine import Engine
+    return Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=max_tokens,
+                  max_seqs=max_seqs, max_batch_tokens=max(256, max_tokens))
+
+
+def sequences(model, lengths=LENGTHS, seed=11):
+    vocab = model["config"]["vocab_size"]
+    return {f"r{i}": helpers.random_tokens(vocab, n, seed + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_whole(tiny_models, name, dtype):
+    model = tiny_models[name]
+    engine = make_engine(model, dtype, 128)
+    replay = helpers.Replayer(engine)
+    for rid, tokens in sequences(model).items():
+        logits = replay.step([(rid, tokens, range(len(tokens)))], end=[rid])
+        helpers.assert_close(logits, helpers.plain_logits(model, tokens), dtype, f"{name} {rid} whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_prompt_then_last_32_one_by_one(tiny_models, name, dtype):
+    model = tiny_models[name]
+    engine = make_engine(model, dtype, 128)
+    replay = helpers.Replayer(engine)
+    for rid, tokens in sequences(model).items():
+        if len(tokens) <= 33:
+            continue
+        reference = helpers.plain_logits(model, tokens)
+        head = len(tokens) - 32
+        rows = [replay.step([(rid, tokens[:head], [head - 1])])]
+        for i in range(head, len(tokens)):
+            rows.append(replay.step([(rid, [tokens[i]], [0])], end=[rid] if i == len(tokens) - 1 else []))
+        helpers.assert_close(np.concatenate(rows), reference[head - 1:], dtype, f"{name} {rid} last 32")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_portions_of_changing_size(tiny_models, name, dtype):
+    model = tiny_models[name]
+    engine = make_engine(model, dtype, 128)
+    replay = helpers.Replayer(engine)
+    sizes = [5, 2, 7, 3, 2, 11, 4, 2, 9, 6]
+    for rid, tokens in sequences(model).items():
+        rows, at, k = [], 0, 0
+        while at < len(tokens):
+            n = min(sizes[k % len(sizes)], len(tokens) - at)
+            k += 1
+            last = at + n == len(tokens)
+            rows.append(replay.step([(rid, tokens[at:at + n], range(n))], end=[rid] if last else []))
+            at += n
+        helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens), dtype,
+                             f"{name} {rid} portions")
+
+
+def mixed_trace(requests, rng, decode_tail=6):
+    """Steps of up to four live requests: portions of some beside single tokens of others; a
+    request is sometimes left out of a step.  Returns [(entries, end)] with entries
+    (id, tokens, want=all)."""
+    waiting = list(requests.items())
+    live, steps = {}, []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            rid, tokens = waiting.pop(0)
+            live[rid] = [tokens, 0]
+        entries, end = [], []
+        for rid, (tokens, at) in list(live.items()):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                    # left out of this step
+            left = len(tokens) - at
+            n = 1 if left <= decode_tail else int(min(left - decode_tail, rng.choice([2, 3, 5, 8, 13])))
+            entries.append((rid, tokens[at:at + n], range(n)))
+            live[rid][1] = at + n
+            if at + n == len(tokens):
+                end.append(rid)
+                del live[rid]
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_mixed_batches_with_page_reuse(tiny_models, name, dtype):
+    model = tiny_models[name]
+    lengths = [33, 7, 64, 19, 1, 50, 16, 41, 2, 27]
+    requests = sequences(model, lengths, seed=23)
+    ps = model["page_size"]
+    # the pool holds the four longest requests at once, far fewer pages than all requests together
+    pool_tokens = sum(sorted((n + ps - 1) // ps * ps for n in lengths)[-4:])
+    assert sum((n + ps - 1) // ps for n in lengths) > pool_tokens // ps, "pages would not be used again"
+    engine = make_engine(model, dtype, pool_tokens)
+    replay = helpers.Replayer(engine)
+    got = {rid: [] for rid in requests}
+    for entries, end in mixed_trace(requests, np.random.default_rng(5)):
+        logits = replay.step(entries, end)
+        at = 0
+        for rid, tokens, want in entries:
+            got[rid].append(logits[at:at + len(want)])
+            at += len(want)
+    for group in engine.cache.groups:
+        assert group.pool.in_use() == 0
+    for rid, tokens in requests.items():
+        helpers.assert_close(np.concatenate(got[rid]), helpers.plain_logits(model, tokens), dtype,
+                             f"{name} {rid} mixed")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_long_decoding(tiny_models, name, dtype):
+    model = tiny_models[name]
+    total = 200
+    tokens = helpers.random_tokens(model["config"]["vocab_size"], total, 77)
+    engine = make_engine(model, dtype, 256)
+    replay = helpers.Replayer(engine)
+    rows = [replay.step([("x", tokens[:3], range(3))])]
+    for i in range(3, total):
+        rows.append(replay.step([("x", [tokens[i]], [0])]))
+    helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens), dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
+    model = tiny_models[name]
+    tokens = helpers.random_tokens(model["config"]["vocab_size"], 4, 3)
+    reference = helpers.plain_logits(model, tokens)
+    engine = make_engine(model, dtype, 64)
+    replay = helpers.Replayer(engine)
+    one_by_one = np.concatenate([replay.step([("a", [t], [0])]) for t in tokens])
+    helpers.assert_close(one_by_one, reference, dtype, f"{name} first tokens one by one")
+    whole = replay.step([("b", tokens, range(4))], end=["a", "b"])
+    helpers.assert_close(whole, reference, dtype, f"{name} first tokens whole")
+    # a step that wants nothing still writes the cache
+    assert replay.step([("c", tokens[:2], [])]) is None or True
+    tail = replay.step([("c", tokens[2:], [0, 1])], end=["c"])
+    helpers.assert_close(tail, reference[2:], dtype, f"{name} after a step that wanted nothing")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(tiny_models, tmp_path, dtype):
+    """bin/trace_run as a user runs it: steps on standard input, <step>.f32 files, `done` lines."""
+    model = tiny_models["tiny-B"]
+    vocab = model["config"]["vocab_size"]
+    a, b = helpers.random_tokens(vocab, 21, 1), helpers.random_tokens(vocab, 9, 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:10], "want": [0, 9]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[10:12], "want": []},
+                                {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[8:], "want": [0]},
+                                {"id": "a", "tokens": a[12:], "want": [8]}], "end": ["a", "b"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model["dir"],
+                           "--dtype", dtype, "--out", str(tmp_path), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert done.stdout.split() == ["done", "0", "done", "1", "done", "2"]
+    ref_a, ref_b = helpers.plain_logits(model, a), helpers.plain_logits(model, b)
+    read = lambda s: np.fromfile(tmp_path / f"{s}.f32", dtype="<f4").reshape(-1, vocab)
+    helpers.assert_close(read(0), ref_a[[0, 9]], dtype, "trace step 0")
+    helpers.assert_close(read(1), ref_b[[7]], dtype, "trace step 1")
+    helpers.assert_close(read(2), torch.cat([ref_b[[8]], ref_a[[20]]]), dtype, "trace step 2")

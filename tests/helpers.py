@@ -21,14 +21,14 @@ TINY = {
                     head_dim=16, vocab_size=256, max_position_embeddings=256, rms_norm_eps=1e-5,
                     rope_theta=10000.0, tie_word_embeddings=True, scale_emb=12, scale_depth=1.4,
                     dim_model_base=32, initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"),
-        seed=0, page_size=8),
+        seed=0, page_size=8, sharpen=8.0),
     "tiny-B": dict(
         config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=96,
                     intermediate_size=256, num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1,
                     head_dim=32, vocab_size=384, max_position_embeddings=512, rms_norm_eps=1e-6,
                     rope_theta=1e6, tie_word_embeddings=False, scale_emb=1, scale_depth=1.0,
                     dim_model_base=96, initializer_range=0.05, hidden_act="silu", torch_dtype="bfloat16"),
-        seed=2, page_size=16),
+        seed=2, page_size=16, sharpen=3.0),
     "tiny-C": dict(
         config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=144,
                     intermediate_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3,
@@ -36,12 +36,11 @@ TINY = {
                     rope_theta=50000.0, tie_word_embeddings=False, sliding_window=21,
                     layer_types=["sliding_attention", "full_attention"], initializer_range=0.03,
                     hidden_act="silu", torch_dtype="bfloat16"),
-        seed=7, page_size=4),
+        seed=7, page_size=4, sharpen=5.0),
 }
 
-# q and k projections are scaled up so that attention is peaked: with the usual small random
-# weights every key gets nearly the same probability and a wrong or missing key would hide.
-SHARPEN = 6.0
+# `sharpen`: q and k projections are scaled up so that attention is peaked: with the usual small
+# random weights every key gets nearly the same probability and a wrong or missing key would hide.
 
 
 def make_model(folder: str, name: str) -> dict:
@@ -56,7 +55,7 @@ def make_model(folder: str, name: str) -> dict:
     weights = load_file(path)            # the safetensors library, independent of the package's reader
     for key in list(weights):
         if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
-            weights[key] = (weights[key].float() * SHARPEN).to(torch.bfloat16)
+            weights[key] = (weights[key].float() * entry["sharpen"]).to(torch.bfloat16)
     save_file(weights, path)
     with open(os.path.join(folder, "config.json")) as f:
         config = json.load(f)
@@ -71,21 +70,35 @@ def random_tokens(vocab: int, count: int, seed: int) -> list:
 _PLAIN_CACHE = {}
 
 
-def plain_logits(model: dict, tokens) -> torch.Tensor:
-    """64-bit logits [T, V] of the plain implementation (cached per model and sequence)."""
-    key = (model["name"], tuple(tokens))
+def rounds_probabilities(head_dim: int) -> bool:
+    """The bfloat16 path's tensor-core attention kernels (head sizes 64 and 128) feed 16-bit
+    probabilities to the tensor cores; the kernel for every other head size keeps them in 32-bit."""
+    return False
+
+
+def plain_logits(model: dict, tokens, dtype: str = "float32") -> torch.Tensor:
+    """64-bit logits [T, V] of the plain implementation (cached per model and sequence): the exact
+    model for the 32-bit path; for the bfloat16 path the model with the values that path keeps in
+    16 bits rounded at the same places."""
+    key = (model["name"], tuple(tokens), dtype)
     if key not in _PLAIN_CACHE:
-        _PLAIN_CACHE[key] = plain_impl.forward(model["config"], model["weights"], tokens, torch.float64)
+        store = plain_impl._identity if dtype == "float32" else plain_impl.round_to_bfloat16
+        store_p = None
+        if dtype != "float32" and rounds_probabilities(plain_impl.head_dim_of(model["config"])):
+            store_p = plain_impl.round_to_bfloat16
+        _PLAIN_CACHE[key] = plain_impl.forward(model["config"], model["weights"], tokens, torch.float64,
+                                               store=store, store_p=store_p)
     return _PLAIN_CACHE[key]
 
 
 # Tolerances, fixed once from the size of rounding in each path and never widened to pass:
 #  * float32: products and sums of ~100-300 terms in 32-bit; logits are O(1)..O(10).
-#  * bfloat16: activations between kernels, the cache and the probabilities are rounded to 8 bits of
-#    mantissa (relative 2^-9 each); errors add up over layers.  Measured against the logits' scale.
+#  * bfloat16: compared with the plain implementation that rounds to bfloat16 where the serving path
+#    stores 16-bit values.  What remains is the order of sums and a value here and there that rounds
+#    the other way (one unit of 2^-8 relative in one stored element).
 def tolerance(dtype: str, reference: torch.Tensor) -> float:
     scale = max(1.0, float(reference.abs().max()))
-    return (2e-4 if dtype == "float32" else 4e-2) * scale
+    return (2e-4 if dtype == "float32" else 1e-2) * scale
 
 
 def assert_close(actual, reference, dtype: str, what: str):

@@ -71,7 +71,7 @@ def rotary(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tens
     return torch.cat([left * cos - right * sin, right * cos + left * sin], dim=-1)
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window) -> torch.Tensor:
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window, store=None) -> torch.Tensor:
     """Causal grouped-query attention of one whole sequence.  q-head h reads kv-head
     h div g; s_j = (q.k_j)/sqrt(d) for keys j <= pos (src/gpu/kernels/llama.rs:62-159,
     GQA map src/gpu/kernels/llama_flash_math.rs:152); with a window w only keys
@@ -88,11 +88,26 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window) -> torc
         kh = h // g
         scores = (q[:, h, :] @ k[:, kh, :].T) * (1.0 / math.sqrt(d))
         scores = scores.masked_fill(~visible, float("-inf"))
-        out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, kh, :]
+        if store is None:
+            out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, kh, :]
+        else:
+            # the serving path feeds 16-bit probabilities to the tensor cores and divides by the
+            # 32-bit sum afterwards
+            p = torch.exp(scores - scores.max(dim=-1, keepdim=True).values)
+            out[:, h, :] = (store(p) @ v[:, kh, :]) / p.sum(dim=-1, keepdim=True)
     return out
 
 
-def attention_mixer(x, w, prefix, cfg, positions, window, dtype):
+def _identity(x):
+    return x
+
+
+def round_to_bfloat16(x: torch.Tensor) -> torch.Tensor:
+    """The values that survive a store in bfloat16 (round to nearest even), kept in x's type."""
+    return x.to(torch.float32).to(torch.bfloat16).to(x.dtype)
+
+
+def attention_mixer(x, w, prefix, cfg, positions, window, dtype, store=_identity, store_p=None):
     """q,k,v projections without bias (src/inference/llama.rs:92-112), RoPE on q and k,
     attention, output projection (src/inference/llama.rs:290-298)."""
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], head_dim_of(cfg)
@@ -101,41 +116,42 @@ def attention_mixer(x, w, prefix, cfg, positions, window, dtype):
     k = (x @ w[prefix + "self_attn.k_proj.weight"].to(dtype).T).view(T, nkv, d)
     v = (x @ w[prefix + "self_attn.v_proj.weight"].to(dtype).T).view(T, nkv, d)
     theta = float(_f(cfg, "rope_theta", 10000.0))
-    q = rotary(q, positions, theta)
-    k = rotary(k, positions, theta)
-    o = attention(q, k, v, window).reshape(T, nq * d)
+    q = store(rotary(q, positions, theta))
+    k = store(rotary(k, positions, theta))
+    o = store(attention(q, k, store(v), window, store_p).reshape(T, nq * d))
     return o @ w[prefix + "self_attn.o_proj.weight"].to(dtype).T
 
 
-def swiglu_feed_forward(x, w, prefix, dtype):
+def swiglu_feed_forward(x, w, prefix, dtype, store=_identity):
     """act = up * gate/(1+exp(-gate)); f = act W_down^T (src/inference/moe.rs:31-61,
     src/gpu/kernels/basic.rs:150-157)."""
     gate = x @ w[prefix + "mlp.gate_proj.weight"].to(dtype).T
     up = x @ w[prefix + "mlp.up_proj.weight"].to(dtype).T
-    act = up * (gate / (1.0 + torch.exp(-gate)))
+    act = store(up * (gate / (1.0 + torch.exp(-gate))))
     return act @ w[prefix + "mlp.down_proj.weight"].to(dtype).T
 
 
-def decoder_block(h, w, layer, cfg, positions, window, dtype):
+def decoder_block(h, w, layer, cfg, positions, window, dtype, store=_identity, store_p=None):
     """Pre-norm block: r = h + s*attn(norm(h)); h' = r + s*ffn(norm(r))
     (src/inference/llama_fusion.rs:41-117), s = scale_depth/sqrt(num_layers) (MiniCPM) or 1."""
     prefix = f"model.layers.{layer}."
     eps = float(cfg["rms_norm_eps"])
     scale_depth = cfg.get("scale_depth")
     s = 1.0 if scale_depth is None else float(scale_depth) / math.sqrt(cfg["num_hidden_layers"])
-    a = attention_mixer(rms_norm(h, w[prefix + "input_layernorm.weight"], eps), w, prefix, cfg,
-                        positions, window, dtype)
+    a = attention_mixer(store(rms_norm(h, w[prefix + "input_layernorm.weight"], eps)), w, prefix, cfg,
+                        positions, window, dtype, store, store_p)
     r = h + a * s
-    f = swiglu_feed_forward(rms_norm(r, w[prefix + "post_attention_layernorm.weight"], eps), w,
-                            prefix, dtype)
+    f = swiglu_feed_forward(store(rms_norm(r, w[prefix + "post_attention_layernorm.weight"], eps)), w,
+                            prefix, dtype, store)
     return r + f * s
 
 
-def lm_head(h, w, cfg, dtype):
+def lm_head(h, w, cfg, dtype, store=_identity):
     """Final RMSNorm (src/inference/paging.rs:310-315), division by hidden_size/dim_model_base
     (MiniCPM), product with the output matrix, which is the embedding table when tied
     (src/inference/paging.rs:316)."""
     y = rms_norm(h, w["model.norm.weight"], float(cfg["rms_norm_eps"]))
+    y = store(y)
     base = cfg.get("dim_model_base")
     if base is not None:
         y = y / (cfg["hidden_size"] / float(base))
@@ -146,16 +162,22 @@ def lm_head(h, w, cfg, dtype):
     return y @ out.to(dtype).T
 
 
-def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, order=None) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, order=None, store=_identity,
+            store_p=None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence.  `order` is the list of layer
-    indices to run (default 0..L-1)."""
+    indices to run (default 0..L-1).  `store` is applied wherever the serving path keeps a value
+    in 16 bits between kernels (normalised activations, rotated q and k, v, attention output,
+    the SwiGLU product, the final normalised row): the identity gives the exact model,
+    `round_to_bfloat16` the model that the bfloat16 path computes, up to the order of sums.
+    `store_p` (None or a rounding) is applied to the unnormalised softmax probabilities, which the
+    tensor-core attention kernels feed to the tensor cores in 16 bits."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.numel())
     h = embedding(tokens, weights["model.embed_tokens.weight"], float(_f(cfg, "scale_emb", 1.0)), dtype)
     windows = layer_windows(cfg)
     for layer in (order if order is not None else range(cfg["num_hidden_layers"])):
-        h = decoder_block(h, weights, layer, cfg, positions, windows[layer], dtype)
-    return lm_head(h, weights, cfg, dtype)
+        h = decoder_block(h, weights, layer, cfg, positions, windows[layer], dtype, store, store_p)
+    return lm_head(h, weights, cfg, dtype, store)
 
 
 def greedy(cfg, weights, prompt, steps: int, dtype=torch.float64) -> list:

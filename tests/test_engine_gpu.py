@@ -38,7 +38,7 @@ def test_whole(tiny_models, name, dtype):
     replay = helpers.Replayer(engine)
     for rid, tokens in sequences(model).items():
         logits = replay.step([(rid, tokens, range(len(tokens)))], end=[rid])
-        helpers.assert_close(logits, helpers.plain_logits(model, tokens), dtype, f"{name} {rid} whole")
+        helpers.assert_close(logits, helpers.plain_logits(model, tokens, dtype), dtype, f"{name} {rid} whole")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -50,7 +50,7 @@ def test_prompt_then_last_32_one_by_one(tiny_models, name, dtype):
     for rid, tokens in sequences(model).items():
         if len(tokens) <= 33:
             continue
-        reference = helpers.plain_logits(model, tokens)
+        reference = helpers.plain_logits(model, tokens, dtype)
         head = len(tokens) - 32
         rows = [replay.step([(rid, tokens[:head], [head - 1])])]
         for i in range(head, len(tokens)):
@@ -73,7 +73,7 @@ def test_portions_of_changing_size(tiny_models, name, dtype):
             last = at + n == len(tokens)
             rows.append(replay.step([(rid, tokens[at:at + n], range(n))], end=[rid] if last else []))
             at += n
-        helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens), dtype,
+        helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens, dtype), dtype,
                              f"{name} {rid} portions")
 
 
@@ -125,7 +125,7 @@ def test_mixed_batches_with_page_reuse(tiny_models, name, dtype):
     for group in engine.cache.groups:
         assert group.pool.in_use() == 0
     for rid, tokens in requests.items():
-        helpers.assert_close(np.concatenate(got[rid]), helpers.plain_logits(model, tokens), dtype,
+        helpers.assert_close(np.concatenate(got[rid]), helpers.plain_logits(model, tokens, dtype), dtype,
                              f"{name} {rid} mixed")
 
 
@@ -140,7 +140,7 @@ def test_long_decoding(tiny_models, name, dtype):
     rows = [replay.step([("x", tokens[:3], range(3))])]
     for i in range(3, total):
         rows.append(replay.step([("x", [tokens[i]], [0])]))
-    helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens), dtype, f"{name} long decode")
+    helpers.assert_close(np.concatenate(rows), helpers.plain_logits(model, tokens, dtype), dtype, f"{name} long decode")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -148,7 +148,7 @@ def test_long_decoding(tiny_models, name, dtype):
 def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
     model = tiny_models[name]
     tokens = helpers.random_tokens(model["config"]["vocab_size"], 4, 3)
-    reference = helpers.plain_logits(model, tokens)
+    reference = helpers.plain_logits(model, tokens, dtype)
     engine = make_engine(model, dtype, 64)
     replay = helpers.Replayer(engine)
     one_by_one = np.concatenate([replay.step([("a", [t], [0])]) for t in tokens])
@@ -181,7 +181,7 @@ def test_trace_run_program(tiny_models, tmp_path, dtype):
                           text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     assert done.stdout.split() == ["done", "0", "done", "1", "done", "2"]
-    ref_a, ref_b = helpers.plain_logits(model, a), helpers.plain_logits(model, b)
+    ref_a, ref_b = helpers.plain_logits(model, a, dtype), helpers.plain_logits(model, b, dtype)
     read = lambda s: np.fromfile(tmp_path / f"{s}.f32", dtype="<f4").reshape(-1, vocab)
     helpers.assert_close(read(0), ref_a[[0, 9]], dtype, "trace step 0")
     helpers.assert_close(read(1), ref_b[[7]], dtype, "trace step 1")

@@ -1,4 +1,4 @@
 from .engine import Engine
-from .step import StepContext, StepEntry, StepError
+from .step import StepContext, StepEntry, StepError, StepRuntime
 
-__all__ = ["Engine", "StepContext", "StepEntry", "StepError"]
+__all__ = ["Engine", "StepContext", "StepEntry", "StepError", "StepRuntime"]

@@ -19,7 +19,7 @@ from ..kernels import ops
 from ..models import DecoderModel
 from ..parts import Runtime
 from ..weights import load_weights
-from .step import StepContext, StepEntry, StepError
+from .step import StepEntry, StepError, StepRuntime
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -27,21 +27,28 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
-                 max_context: int = None):
+                 max_context: int = None, _random=None):
+        """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
+        `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
+        `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
+        request (default: the model's max_position_embeddings)."""
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be one of {sorted(_DTYPES)}")
         if not torch.cuda.is_available():
             raise RuntimeError("lia_rs_b200 needs a CUDA device: there is no CPU execution path")
         ops.lib()                                            # build/load the kernels now, loudly
-        raw = read_config_json(model_dir)
+        raw = _random[0].to_dict() if _random else read_config_json(model_dir)
         self.architecture = resolve_architecture(raw)
-        self.config = self.architecture.config_class.from_dict(raw)
+        self.config = _random[0] if _random else self.architecture.config_class.from_dict(raw)
         self.spec = self.architecture.build(self.config)
         self.dtype_name = "bfloat16" if _DTYPES[dtype] == torch.bfloat16 else "float32"
         self.runtime = Runtime(device, _DTYPES[dtype])
         self.device = self.runtime.device
         torch.cuda.set_device(self.device)
-        tensors = load_weights(model_dir, self.spec.tensor_specs())
+        if _random:
+            tensors = self._random_tensors(_random[1])
+        else:
+            tensors = load_weights(model_dir, self.spec.tensor_specs())
         self.model = DecoderModel(self.spec, tensors, self.runtime)
         del tensors
         self.page_size = int(page_size)
@@ -54,15 +61,28 @@ class Engine:
         self.cache = CacheManager(self.spec.cache_requests(), self.spec.state_requests(), num_pages,
                                   self.page_size, self.max_seqs, self.max_context, self.runtime.compute_dtype,
                                   self.device)
-        cap = self.max_batch_tokens
-        self._meta_host = torch.zeros(4 * cap, dtype=torch.int32, pin_memory=True)
-        self._meta_device = torch.zeros(4 * cap, dtype=torch.int32, device=self.device)
-        self._error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-        self._copy_event = torch.cuda.Event()
-        self._buffers = {}
-        self._logits_buffer = None
+        self.runtime_step = StepRuntime(self.cache, self.spec.vocab_size, self.max_batch_tokens, self.device)
         self.stats = {"steps": 0, "tokens": 0}
+
+    @classmethod
+    def random(cls, config, seed: int = 0, **options) -> "Engine":
+        """An engine whose weights are drawn on the device from `seed` (N(0, initializer_range),
+        norm weights 1), without writing a folder: for benchmarks of sizes that would take long to
+        write.  `weights.write_random_model` is the mode that writes a folder."""
+        return cls(None, _random=(config, seed), **options)
+
+    def _random_tensors(self, seed: int) -> dict:
+        generator = torch.Generator(device=self.device)
+        generator.manual_seed(int(seed))
+        std = float(getattr(self.config, "initializer_range", 0.02))
+        out = {}
+        for spec in self.spec.tensor_specs():
+            if spec.kind == "norm":
+                out[spec.name] = torch.ones(spec.shape, dtype=torch.bfloat16, device=self.device)
+            else:
+                out[spec.name] = (torch.randn(spec.shape, generator=generator, device=self.device,
+                                              dtype=torch.float32) * std).to(torch.bfloat16)
+        return out
 
     # ---- requests and pages (thin faces of the cache manager) ----
     def admit(self) -> int:
@@ -74,77 +94,43 @@ class Engine:
     def release(self, slot: int) -> None:
         self.cache.release(slot)
 
-    # ---- memory ----
-    def _workspace(self, name, shape, dtype):
-        rows, width = shape
-        key = (name, width, dtype)
-        buf = self._buffers.get(key)
-        if buf is None or buf.shape[0] < rows:
-            buf = torch.empty((max(rows, self.max_batch_tokens), width), dtype=dtype, device=self.device)
-            self._buffers[key] = buf
-        return buf[:rows]
-
-    def _logits(self, rows, vocab):
-        buf = self._logits_buffer
-        if buf is None or buf.shape[0] < rows:
-            buf = torch.empty((max(rows, self.max_seqs), vocab), dtype=torch.float32, device=self.device)
-            self._logits_buffer = buf
-        return buf[:rows]
-
     # ---- the step ----
     def step(self, entries) -> torch.Tensor:
         """Run one batch.  Returns 32-bit logits [wanted, vocab] on the device, in the order of the
         entries and of each entry's `want`.  The pages for every position must have been reserved."""
-        tokens, positions, slots, out_rows, segments = [], [], [], [], []
-        seen = set()
-        vocab = self.spec.vocab_size
-        for entry in entries:
-            count = len(entry.tokens)
-            if count == 0:
-                raise StepError("a step entry brings no tokens")
-            if entry.slot in seen:
-                raise StepError(f"request slot {entry.slot} appears twice in one step")
-            seen.add(entry.slot)
-            if entry.slot not in self.cache._live:
-                raise StepError(f"request slot {entry.slot} is not live")
-            if entry.start < 0 or entry.start + count > self.cache.length[entry.slot]:
-                raise StepError(f"slot {entry.slot}: positions [{entry.start}, {entry.start + count}) have no "
-                                f"reserved pages (reserved up to {self.cache.length[entry.slot]})")
-            low, high = min(entry.tokens), max(entry.tokens)
-            if low < 0 or high >= vocab:
-                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of {vocab}")
-            offset = len(tokens)
-            for w in entry.want:
-                if not 0 <= w < count:
-                    raise StepError(f"wanted index {w} is outside the entry's {count} tokens")
-                out_rows.append(offset + w)
-            segments.append((entry.slot, entry.start, count, offset))
-            tokens.extend(entry.tokens)
-            positions.extend(range(entry.start, entry.start + count))
-            slots.extend([entry.slot] * count)
-        n, n_out, cap = len(tokens), len(out_rows), self.max_batch_tokens
-        if n == 0:
-            return self._logits(0, vocab)
-        if n > cap:
-            raise StepError(f"{n} tokens in one step exceed max_batch_tokens={cap}")
-        self._copy_event.synchronize()               # the staging buffer of the last step is free again
-        self._raise_device_errors()
-        host = self._meta_host
-        host[0:n] = torch.tensor(tokens, dtype=torch.int32)
-        host[cap:cap + n] = torch.tensor(positions, dtype=torch.int32)
-        host[2 * cap:2 * cap + n] = torch.tensor(slots, dtype=torch.int32)
-        if n_out:
-            host[3 * cap:3 * cap + n_out] = torch.tensor(out_rows, dtype=torch.int32)
+        entries = list(entries)
+        if not entries:
+            return self.runtime_step.logits(0, self.spec.vocab_size)
         with torch.cuda.device(self.device):
-            self._meta_device.copy_(host, non_blocking=True)
-            self.cache.flush()
-            self._copy_event.record()
-            ctx = StepContext(self, n, n_out, segments)
+            ctx = self.runtime_step.begin(entries)
             logits = self.model.forward(ctx)
-            self._error_host.copy_(self._error_flag, non_blocking=True)
+            self.runtime_step.finish()
         self.stats["steps"] += 1
-        self.stats["tokens"] += n
+        self.stats["tokens"] += ctx.n_tokens
         return logits
+
+    # ---- token selection ----
+    def select_tokens(self, logits: torch.Tensor, samplings, positions) -> list:
+        """One token per row of `logits` on the device (greedy, or Gumbel-max keyed by seed and
+        position); returns host integers.  This is the step's device-to-host read."""
+        rows = logits.shape[0]
+        out = self._workspace("select.out", (1, max(rows, self.max_seqs)), torch.int32)[0, :rows]
+        if all(s.greedy for s in samplings):
+            ops.select_tokens(logits, out)
+        else:
+            temperature = torch.tensor([s.temperature for s in samplings], dtype=torch.float32)
+            seeds = torch.tensor([s.seed & 0x7FFFFFFFFFFFFFFF for s in samplings], dtype=torch.int64)
+            where = torch.tensor(list(positions), dtype=torch.int64)
+            ops.select_tokens(logits, out, temperature.to(self.device), seeds.to(self.device),
+                              where.to(self.device))
+        tokens = out.tolist()
+        self._raise_device_errors()
+        return tokens
+
+    def logits_to_host(self, logits: torch.Tensor):
+        rows = logits.float().cpu().numpy()
+        self._raise_device_errors()
+        return rows
 
     def synchronize(self) -> None:
         """Wait for the device and raise if a kernel flagged an error."""
@@ -152,13 +138,7 @@ class Engine:
         self._raise_device_errors()
 
     def _raise_device_errors(self):
-        code = int(self._error_host[0])
-        if code:
-            self._error_host[0] = 0
-            self._error_flag.zero_()
-            raise StepError({1: "a token id outside the vocabulary reached the embedding kernel",
-                             2: "a token's block table entry has no page"}.get(code, f"device error {code}"))
+        self.runtime_step.raise_device_errors()
 
-    def _attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):
-        ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
-                              nq, nkv, d, window, scale)
+    def _workspace(self, name, shape, dtype):
+        return self.runtime_step.workspace(name, shape, dtype)

@@ -7,6 +7,11 @@ The reference's counterpart is `Engine::forward_paged(rows, tables, outputs)`
 sequence, and the indices of the rows whose logits are returned.  Its host checks are kept
 (src/inference/paging.rs:120-172): positions of a request are consecutive, no request appears
 twice in a step, every token id is in the vocabulary, pages exist for every row.
+
+`StepRuntime` owns what a step needs besides the model: the cache manager, the staging of the
+step's metadata (host pinned -> device, one copy), the workspace that parts take their buffers
+from, the device error flag, and the choice of attention kernel.  `StepContext` is the view of
+one step that the parts see.
 """
 from __future__ import annotations
 
@@ -14,6 +19,8 @@ from dataclasses import dataclass, field
 from typing import Sequence
 
 import torch
+
+from ..kernels import ops
 
 
 class StepError(RuntimeError):
@@ -33,31 +40,126 @@ class StepEntry:
 class StepContext:
     """Everything the parts may ask for during one step."""
 
-    def __init__(self, engine, n_tokens, n_out, segments):
-        self.engine = engine
+    def __init__(self, runtime, n_tokens, n_out, segments, meta):
+        self.runtime = runtime
         self.n_tokens, self.n_out = n_tokens, n_out
-        self.segments = segments                      # [(slot, start, count, offset in batch)]
-        meta, cap = engine._meta_device, engine.max_batch_tokens
-        self.tokens = meta[0:n_tokens]
-        self.positions = meta[cap:cap + n_tokens]
-        self.slots = meta[2 * cap:2 * cap + n_tokens]
-        self.out_rows = meta[3 * cap:3 * cap + n_out]
-        self.error_flag = engine._error_flag
+        self.segments = segments                      # [(slot, start, count, offset in the batch)]
+        self.tokens, self.positions, self.slots, self.out_rows = meta
+        self.error_flag = runtime.error_flag
         self.decode_only = all(count == 1 for _, _, count, _ in segments)
         self.max_context = max((start + count for _, start, count, _ in segments), default=0)
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
-        return self.engine._workspace(name, shape, dtype)
+        """A buffer [rows, width] of the workspace; the same name, width and type give the same
+        memory in every step (a part must not expect it to survive a step)."""
+        return self.runtime.workspace(name, shape, dtype)
 
     def logits_buffer(self, rows: int, vocab: int) -> torch.Tensor:
-        return self.engine._logits(rows, vocab)
+        return self.runtime.logits(rows, vocab)
 
     def kv_view(self, cache_id, writes):
-        return self.engine.cache.kv_view(cache_id, writes)
+        return self.runtime.cache.kv_view(cache_id, writes)
 
     def state(self, state_id):
-        return self.engine.cache.state(state_id)
+        return self.runtime.cache.state(state_id)
 
     def attention(self, q, kv, out, nq, nkv, d, window, scale):
         """out = causal attention of q over the cache `kv`, for the tokens of this step."""
-        self.engine._attention(self, q, kv, out, nq, nkv, d, window, scale)
+        self.runtime.attention(self, q, kv, out, nq, nkv, d, window, scale)
+
+
+class StepRuntime:
+    def __init__(self, cache, vocab_size: int, max_batch_tokens: int, device):
+        self.cache = cache
+        self.vocab_size = int(vocab_size)
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.device = torch.device(device)
+        cap = self.max_batch_tokens
+        self._meta_host = torch.zeros(4 * cap, dtype=torch.int32, pin_memory=True)
+        self._meta_device = torch.zeros(4 * cap, dtype=torch.int32, device=self.device)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._copy_event = torch.cuda.Event()
+        self._buffers = {}
+        self._logits_buffer = None
+
+    # ---- memory ----
+    def workspace(self, name, shape, dtype):
+        rows, width = shape
+        key = (name, width, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
+            buf = torch.empty((max(rows, self.max_batch_tokens), width), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:rows]
+
+    def logits(self, rows, vocab):
+        buf = self._logits_buffer
+        if buf is None or buf.shape[0] < rows or buf.shape[1] != vocab:
+            buf = torch.empty((max(rows, self.cache.max_slots), vocab), dtype=torch.float32, device=self.device)
+            self._logits_buffer = buf
+        return buf[:rows]
+
+    # ---- a step's metadata ----
+    def begin(self, entries) -> StepContext:
+        """Check the batch, stage its metadata and the changed block-table rows on the device,
+        and return the context for the model."""
+        tokens, positions, slots, out_rows, segments = [], [], [], [], []
+        seen = set()
+        for entry in entries:
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepError("a step entry brings no tokens")
+            if entry.slot in seen:
+                raise StepError(f"request slot {entry.slot} appears twice in one step")
+            seen.add(entry.slot)
+            if entry.slot not in self.cache._live:
+                raise StepError(f"request slot {entry.slot} is not live")
+            if entry.start < 0 or entry.start + count > self.cache.length[entry.slot]:
+                raise StepError(f"slot {entry.slot}: positions [{entry.start}, {entry.start + count}) have no "
+                                f"reserved pages (reserved up to {self.cache.length[entry.slot]})")
+            low, high = min(entry.tokens), max(entry.tokens)
+            if low < 0 or high >= self.vocab_size:
+                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
+                                f"{self.vocab_size}")
+            offset = len(tokens)
+            for w in entry.want:
+                if not 0 <= w < count:
+                    raise StepError(f"wanted index {w} is outside the entry's {count} tokens")
+                out_rows.append(offset + w)
+            segments.append((entry.slot, entry.start, count, offset))
+            tokens.extend(entry.tokens)
+            positions.extend(range(entry.start, entry.start + count))
+            slots.extend([entry.slot] * count)
+        n, n_out = len(tokens), len(out_rows)
+        if n > self.max_batch_tokens:
+            raise StepError(f"{n} tokens in one step exceed max_batch_tokens={self.max_batch_tokens}")
+        self._copy_event.synchronize()               # the staging buffer of the last step is free again
+        self.raise_device_errors()
+        host = self._meta_host
+        packed = torch.tensor(tokens + positions + slots + out_rows, dtype=torch.int32)
+        total = 3 * n + n_out
+        host[:total] = packed
+        self._meta_device[:total].copy_(host[:total], non_blocking=True)
+        self.cache.flush()
+        self._copy_event.record()
+        dev = self._meta_device
+        meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:3 * n + n_out])
+        self.h2d_bytes = total * 4
+        return StepContext(self, n, n_out, segments, meta)
+
+    def finish(self):
+        self._error_host.copy_(self.error_flag, non_blocking=True)
+
+    def raise_device_errors(self):
+        code = int(self._error_host[0])
+        if code:
+            self._error_host[0] = 0
+            self.error_flag.zero_()
+            raise StepError({1: "a token id outside the vocabulary reached the embedding kernel",
+                             2: "a token's block table entry has no page"}.get(code, f"device error {code}"))
+
+    # ---- attention ----
+    def attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):
+        ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
+                              nq, nkv, d, window, scale)

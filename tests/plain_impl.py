@@ -107,9 +107,12 @@ def round_to_bfloat16(x: torch.Tensor) -> torch.Tensor:
     return x.to(torch.float32).to(torch.bfloat16).to(x.dtype)
 
 
-def attention_mixer(x, w, prefix, cfg, positions, window, dtype, store=_identity, store_p=None):
+def attention_mixer(x, w, prefix, cfg, positions, window, dtype, store=_identity, store_p=None, kv=None,
+                    keep=None):
     """q,k,v projections without bias (src/inference/llama.rs:92-112), RoPE on q and k,
-    attention, output projection (src/inference/llama.rs:290-298)."""
+    attention, output projection (src/inference/llama.rs:290-298).  `kv` = (k, v) of another layer
+    replaces this layer's own keys and values (a layer that reads another layer's cache); `keep`
+    (a list) receives this layer's (k, v)."""
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], head_dim_of(cfg)
     T = x.shape[0]
     q = (x @ w[prefix + "self_attn.q_proj.weight"].to(dtype).T).view(T, nq, d)
@@ -118,7 +121,12 @@ def attention_mixer(x, w, prefix, cfg, positions, window, dtype, store=_identity
     theta = float(_f(cfg, "rope_theta", 10000.0))
     q = store(rotary(q, positions, theta))
     k = store(rotary(k, positions, theta))
-    o = store(attention(q, k, store(v), window, store_p).reshape(T, nq * d))
+    v = store(v)
+    if kv is not None:
+        k, v = kv
+    if keep is not None:
+        keep.append((k, v))
+    o = store(attention(q, k, v, window, store_p).reshape(T, nq * d))
     return o @ w[prefix + "self_attn.o_proj.weight"].to(dtype).T
 
 
@@ -131,7 +139,8 @@ def swiglu_feed_forward(x, w, prefix, dtype, store=_identity):
     return act @ w[prefix + "mlp.down_proj.weight"].to(dtype).T
 
 
-def decoder_block(h, w, layer, cfg, positions, window, dtype, store=_identity, store_p=None):
+def decoder_block(h, w, layer, cfg, positions, window, dtype, store=_identity, store_p=None, kv=None,
+                  keep=None):
     """Pre-norm block: r = h + s*attn(norm(h)); h' = r + s*ffn(norm(r))
     (src/inference/llama_fusion.rs:41-117), s = scale_depth/sqrt(num_layers) (MiniCPM) or 1."""
     prefix = f"model.layers.{layer}."
@@ -139,7 +148,7 @@ def decoder_block(h, w, layer, cfg, positions, window, dtype, store=_identity, s
     scale_depth = cfg.get("scale_depth")
     s = 1.0 if scale_depth is None else float(scale_depth) / math.sqrt(cfg["num_hidden_layers"])
     a = attention_mixer(store(rms_norm(h, w[prefix + "input_layernorm.weight"], eps)), w, prefix, cfg,
-                        positions, window, dtype, store, store_p)
+                        positions, window, dtype, store, store_p, kv, keep)
     r = h + a * s
     f = swiglu_feed_forward(store(rms_norm(r, w[prefix + "post_attention_layernorm.weight"], eps)), w,
                             prefix, dtype, store)
@@ -163,20 +172,24 @@ def lm_head(h, w, cfg, dtype, store=_identity):
 
 
 def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, order=None, store=_identity,
-            store_p=None) -> torch.Tensor:
+            store_p=None, reads=None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence.  `order` is the list of layer
     indices to run (default 0..L-1).  `store` is applied wherever the serving path keeps a value
     in 16 bits between kernels (normalised activations, rotated q and k, v, attention output,
     the SwiGLU product, the final normalised row): the identity gives the exact model,
     `round_to_bfloat16` the model that the bfloat16 path computes, up to the order of sums.
     `store_p` (None or a rounding) is applied to the unnormalised softmax probabilities, which the
-    tensor-core attention kernels feed to the tensor cores in 16 bits."""
+    tensor-core attention kernels feed to the tensor cores in 16 bits.  `reads` maps a place in
+    `order` to an earlier place whose keys and values that entry uses instead of its own."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.numel())
     h = embedding(tokens, weights["model.embed_tokens.weight"], float(_f(cfg, "scale_emb", 1.0)), dtype)
     windows = layer_windows(cfg)
-    for layer in (order if order is not None else range(cfg["num_hidden_layers"])):
-        h = decoder_block(h, weights, layer, cfg, positions, windows[layer], dtype, store, store_p)
+    kept = []
+    for place, layer in enumerate(order if order is not None else range(cfg["num_hidden_layers"])):
+        source = (reads or {}).get(place)
+        h = decoder_block(h, weights, layer, cfg, positions, windows[layer], dtype, store, store_p,
+                          kv=None if source is None else kept[source], keep=kept)
     return lm_head(h, weights, cfg, dtype, store)
 
 

@@ -1,0 +1,219 @@
+"""Each kernel alone against a plain torch reference in 64-bit, at sizes other than the engine's.
+Inputs are built so that faults would show: a far key that dominates, a window's edge, scrambled
+pages, widths and vocabularies that are no power of two."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from lia_rs_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.6e-2       # bfloat16: 2 units of 2^-8 relative on O(1) values
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_scales_rows_and_flags_bad_ids(dtype):
+    table = torch.randn(301, 72, device=DEV).to(dtype)
+    tokens = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embedding(tokens, table, out, 12.0, flag)
+    assert torch.equal(out, table[tokens.long()].float() * 12.0) and flag.item() == 0
+    ops().embedding(torch.tensor([3, 301], dtype=torch.int32, device=DEV), table, out[:2], 1.0, flag)
+    assert flag.item() == 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("w_dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [48, 1000, 2048, 4100])
+def test_rmsnorm(hidden, w_dtype, out_dtype):
+    x = torch.randn(7, hidden, device=DEV) * 3
+    w = (torch.rand(hidden, device=DEV) + 0.5).to(w_dtype)
+    out = torch.empty(7, hidden, device=DEV, dtype=out_dtype)
+    ops().rmsnorm(x, w, out, 1e-5, 0.5)
+    xd = x.double()
+    want = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * w.double() * 0.5
+    assert float((out.double() - want).abs().max()) <= tol(out_dtype) * float(want.abs().max())
+    rows = torch.tensor([6, -1, 0], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, hidden, device=DEV, dtype=out_dtype)
+    ops().rmsnorm(x, w, picked, 1e-5, 0.5, rows)
+    assert torch.equal(picked[0], out[6]) and torch.equal(picked[2], out[0]) and float(picked[1].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 40, 24), (5, 130, 100), (67, 64, 257), (130, 301, 72)])
+def test_gemm_simt_all_epilogues(M, N, K, dtype):
+    o = ops()
+    a = torch.randn(M, K, device=DEV).to(dtype)
+    w = torch.randn(2 * N, K, device=DEV).to(dtype) / math.sqrt(K)
+    exact = a.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    o.gemm_simt(o.GEMM_STORE, a, w[:N], out, 0.25)
+    assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * max(1.0, float(exact.abs().max()))
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    o.gemm_simt(o.GEMM_ACCUM, a, w[:N], acc, 1.5)
+    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5
+    act = torch.empty(M, N, device=DEV, dtype=dtype)
+    o.gemm_simt(o.GEMM_SWIGLU, a, w, act)
+    gate, up = exact[:, :N], exact[:, N:]
+    want = up * gate / (1 + torch.exp(-gate))
+    assert float((act.double() - want).abs().max()) <= tol(dtype) * max(1.0, float(want.abs().max()))
+    # a row's result does not depend on the other rows of the batch
+    alone = torch.empty(1, N, device=DEV)
+    o.gemm_simt(o.GEMM_STORE, a[M - 1:M].contiguous(), w[:N], alone, 0.25)
+    assert torch.equal(alone[0], out[M - 1])
+
+
+def paged(values, page_size, num_pages, order):
+    """Scatter [T, heads, d] into pages in the given physical order; returns pages and the table."""
+    T = values.shape[0]
+    pages = torch.zeros(num_pages, page_size, *values.shape[1:], dtype=values.dtype, device=DEV)
+    blocks = (T + page_size - 1) // page_size
+    table = torch.full((blocks,), -1, dtype=torch.int32)
+    for b in range(blocks):
+        table[b] = order[b]
+        chunk = values[b * page_size:(b + 1) * page_size]
+        pages[order[b], :chunk.shape[0]] = chunk
+    return pages, table
+
+
+def reference_attention(q, k, v, positions, window, scale):
+    out = torch.zeros_like(q, dtype=torch.float64)
+    g = q.shape[1] // k.shape[1]
+    for t, pos in enumerate(positions):
+        first = 0 if not window else max(0, pos - window + 1)
+        for h in range(q.shape[1]):
+            s = (k[first:pos + 1, h // g].double() @ q[t, h].double()) * scale
+            p = torch.softmax(s, dim=0)
+            out[t, h] = p @ v[first:pos + 1, h // g].double()
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,nq,nkv,page_size,window", [(16, 4, 2, 8, None), (48, 6, 3, 4, 21), (128, 8, 1, 16, None),
+                                                       (80, 5, 5, 32, 100), (256, 2, 1, 16, None)])
+def test_attention_generic_far_key_window_edge_and_scrambled_pages(d, nq, nkv, page_size, window, dtype):
+    torch.manual_seed(d)
+    T = 333
+    k = torch.randn(T, nkv, d, device=DEV) * 0.3
+    v = torch.randn(T, nkv, d, device=DEV)
+    positions = [0, 1, page_size - 1, page_size, 2 * page_size + 1, 200, 331, 332]
+    q = torch.randn(len(positions), nq, d, device=DEV) * 0.3
+    # one far key stands out for the last query: key 5 (or the window's first key) carries the score
+    far = 5 if not window else 332 - window + 1
+    k[far, :, :] = 0
+    k[far, :, 0] = 6.0
+    q[-1, :, 0] = 5.0 * math.sqrt(d)
+    # and the key just outside the window would dominate if it were seen
+    if window:
+        k[far - 1, :, 1] = 50.0
+        q[-1, :, 1] = 5.0 * math.sqrt(d)
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    num_pages = 2 * ((T + page_size - 1) // page_size) + 3
+    order = np.random.default_rng(0).permutation(num_pages)[:(T + page_size - 1) // page_size]
+    kp, table = paged(k, page_size, num_pages, order)
+    vp, _ = paged(v, page_size, num_pages, order)
+    bt = torch.full((3, table.numel() + 2), -1, dtype=torch.int32)
+    bt[1, :table.numel()] = table                                        # the request sits in slot 1
+    out = torch.empty_like(q)
+    pos = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slots = torch.ones(len(positions), dtype=torch.int32, device=DEV)
+    slots[3] = -1                                                        # padding row: left alone
+    out[3] = 7.0
+    scale = 1 / math.sqrt(d)
+    ops().attention_generic(q.view(-1, nq * d), kp, vp, pos, slots, bt.to(DEV), out.view(-1, nq * d), nq, nkv, d,
+                            window, scale)
+    want = reference_attention(q, k, v, positions, window, scale)
+    keep = [i for i in range(len(positions)) if i != 3]
+    error = float((out.double()[keep] - want[keep]).abs().max())
+    assert error <= tol(dtype) * max(1.0, float(want.abs().max())), error
+    assert float((out[3].float() - 7.0).abs().max()) == 0
+    # the last query's output is the far key's value, almost alone
+    assert float((out[-1, 0].double() - v[far, 0].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,rotary_dim", [(16, 16), (48, 48), (64, 32), (128, 128), (32, 0)])
+def test_rope_kv_write(d, rotary_dim, dtype):
+    nq, nkv, page_size, theta = 3, 2, 4, 50000.0
+    positions = [0, 1, 3, 4, 7, 8, 1000, 30000]
+    n = len(positions)
+    qkv = torch.randn(n, (nq + 2 * nkv) * d, device=DEV)
+    blocks = max(positions) // page_size + 1
+    table = torch.full((2, blocks), -1, dtype=torch.int32)
+    for i, pos in enumerate(positions):
+        if table[1, pos // page_size] < 0:
+            table[1, pos // page_size] = 10 - i                          # pages out of order
+    kp = torch.zeros(12, page_size, nkv, d, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    q_out = torch.zeros(n, nq * d, device=DEV, dtype=dtype)
+    inv = None
+    if rotary_dim:
+        inv = (1.0 / theta ** (2.0 * torch.arange(rotary_dim // 2, dtype=torch.float64) / rotary_dim)).float().to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().rope_kv_write(qkv, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                        torch.ones(n, dtype=torch.int32, device=DEV), table.to(DEV), q_out, kp, vp, nq, nkv, d,
+                        rotary_dim, inv, True, flag)
+    assert flag.item() == 0
+    x = qkv.double().view(n, nq + 2 * nkv, d)
+    rotated = x.clone()
+    if rotary_dim:
+        half = rotary_dim // 2
+        angle = torch.tensor(positions, dtype=torch.float64, device=DEV)[:, None] * inv.double()[None, :]
+        c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        a, b = x[..., :half], x[..., half:rotary_dim]
+        rotated[..., :half] = a * c - b * s
+        rotated[..., half:rotary_dim] = b * c + a * s
+    limit = 1e-5 * 4 if dtype == torch.float32 else 2.0 ** -8 * 4
+    # 32-bit angles: at position 30000 the product pos * inv_freq is rounded to 2^-24 relative
+    limit += 30000 * 2.0 ** -23 * 4
+    assert float((q_out.double().view(n, nq, d) - rotated[:, :nq]).abs().max()) < limit
+    for i, pos in enumerate(positions):
+        page = int(table[1, pos // page_size])
+        assert float((kp[page, pos % page_size].double() - rotated[i, nq:nq + nkv]).abs().max()) < limit
+        assert float((vp[page, pos % page_size].double() - x[i, nq + nkv:]).abs().max()) < limit
+    # a position whose block has no page raises the flag and writes nothing
+    ops().rope_kv_write(qkv[:1], torch.tensor([8 * page_size], dtype=torch.int32, device=DEV),
+                        torch.zeros(1, dtype=torch.int32, device=DEV), table.to(DEV), q_out[:1], kp, vp, nq, nkv, d,
+                        rotary_dim, inv, True, flag)
+    assert flag.item() == 2
+
+
+def test_select_tokens_greedy_ties_and_gumbel_matches_the_host_rule():
+    from lia_rs_b200.sampling import RequestSampler, Sampling
+    vocab = 73448 // 8 + 3
+    logits = torch.randn(6, vocab, device=DEV)
+    logits[0, [5, 900, 4000]] = 9.0                   # equal maxima: the largest id wins
+    logits[1, vocab - 1] = 11.0
+    logits[2, 0] = 11.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops().select_tokens(logits, out)
+    assert out.tolist()[:3] == [4000, vocab - 1, 0]
+    assert out.tolist() == [RequestSampler(Sampling()).sample(row, 0) for row in logits.cpu().numpy()]
+    temperature = torch.tensor([0.7, 1.0, 0.0, 1.5, 0.3, 1.0], device=DEV)
+    seeds = torch.tensor([1, 2, 3, 2 ** 40 + 5, 5, 6], dtype=torch.int64, device=DEV)
+    positions = torch.tensor([0, 17, 5, 123456, 9, 2 ** 33], dtype=torch.int64, device=DEV)
+    ops().select_tokens(logits, out, temperature, seeds, positions)
+    host = []
+    for i, row in enumerate(logits.cpu().numpy()):
+        s = Sampling(temperature=float(temperature[i]), seed=int(seeds[i]), sampler="murmur3_gumbel")
+        host.append(RequestSampler(s).sample(row, int(positions[i])))
+    assert out.tolist() == host
+    # frequencies follow softmax(logits / T)
+    small = torch.tensor([[0.0, math.log(2.0), math.log(5.0)]], device=DEV).repeat(4000, 1).contiguous()
+    picks = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops().select_tokens(small, picks, torch.ones(4000, device=DEV), torch.full((4000,), 9, dtype=torch.int64, device=DEV),
+                        torch.arange(4000, dtype=torch.int64, device=DEV))
+    freq = torch.bincount(picks.long(), minlength=3).double() / 4000
+    assert torch.allclose(freq.cpu(), torch.tensor([1 / 8, 2 / 8, 5 / 8], dtype=torch.float64), atol=0.03)

@@ -1,0 +1,90 @@
+"""Host sampling against the reference's own test vectors and closed forms, and against the
+plain implementation's sampler."""
+import math
+
+import numpy as np
+import pytest
+
+import plain_impl
+from lia_rs_b200.sampling import MT19937, RequestSampler, Sampling, distribution, gumbel_noise, murmur_hash
+
+
+def test_mt19937_published_vector_and_reference_doubles():
+    # src/sampling/random.rs:55-70
+    r = MT19937(5489)
+    assert [r.next() for _ in range(10)] == [3499211612, 581869302, 3890346734, 3586334585, 545404204,
+                                             4161255391, 3922919429, 949333985, 2715962298, 1323567403]
+    r = MT19937(5489)
+    for _ in range(9999):
+        r.next()
+    assert r.next() == 4123659995
+    r = MT19937(42)
+    assert abs(r.uniform() - 0.796542984287846) < 1e-15 and abs(r.uniform() - 0.18343478789336848) < 1e-15
+    p = plain_impl.MT19937(42)
+    q = MT19937(42)
+    assert [p.uniform() for _ in range(700)] == [q.uniform() for _ in range(700)]
+
+
+def test_distribution_closed_forms():
+    logits = np.array([0.0, math.log(2.0), math.log(4.0), -np.inf], dtype=np.float32)
+    entries = distribution(logits, 1.0, 0, 1.0)
+    assert [t for t, _ in entries] == [2, 1, 0]
+    assert np.allclose([p for _, p in entries], [4 / 7, 2 / 7, 1 / 7], atol=1e-7)
+    assert [t for t, _ in distribution(logits, 1.0, 2, 1.0)] == [2, 1]
+    assert [t for t, _ in distribution(logits, 1.0, 0, 0.5)] == [2]
+    assert [t for t, _ in distribution(logits, 1.0, 0, 0.6)] == [2, 1]
+    half = distribution(logits, 2.0, 0, 1.0)                      # temperature 2: weights 2, sqrt 2, 1
+    assert np.allclose([p for _, p in half], np.array([2, math.sqrt(2), 1]) / (3 + math.sqrt(2)), atol=1e-7)
+    ties = distribution(np.array([1.0, 1.0, 1.0], dtype=np.float32), 1.0, 2, 1.0)
+    assert [t for t, _ in ties] == [2, 1]                         # ties: the larger id first
+    with pytest.raises(ValueError):
+        distribution(np.array([np.nan, 1.0], dtype=np.float32), 1.0, 0, 1.0)
+
+
+def test_matches_the_plain_sampler_draw_by_draw():
+    rng = np.random.default_rng(0)
+    for temperature, top_k, top_p in [(0.8, 0, 1.0), (1.3, 20, 0.95), (0.5, 3, 0.7)]:
+        ours = RequestSampler(Sampling(temperature=temperature, top_k=top_k, top_p=top_p, seed=99))
+        theirs = plain_impl.MT19937(99)
+        for _ in range(40):
+            logits = rng.normal(size=300).astype(np.float32) * 3
+            want = plain_impl.draw(plain_impl.distribution(logits, temperature, top_k, top_p), theirs)
+            assert ours.sample(logits, 0) == want
+
+
+def test_greedy_keeps_the_last_maximum_and_presence_penalty():
+    s = RequestSampler(Sampling())
+    assert s.sample(np.array([1, 5, 5, 2], dtype=np.float32), 0) == 2
+    p = RequestSampler(Sampling(presence_penalty=2.0))
+    row = np.array([0, 3, 2.5, 0], dtype=np.float32)
+    assert [p.sample(row, i) for i in range(3)] == [1, 2, 1]     # 1 is penalised to 1.0, then 2 to 0.5
+
+
+def test_gumbel_draw_depends_on_seed_position_token_only():
+    assert murmur_hash(42, 0, 0) == murmur_hash(42, 0, 0) and murmur_hash(42, 0, 0) != murmur_hash(42, 1, 0)
+    assert all(math.isfinite(gumbel_noise(w)) for w in (0, 1, 65535, 1 << 16, (1 << 32) - 1, 123456789))
+    rng = np.random.default_rng(1)
+    logits = rng.normal(size=500).astype(np.float32)
+    a = RequestSampler(Sampling(temperature=1.0, seed=5, sampler="murmur3_gumbel"))
+    b = RequestSampler(Sampling(temperature=1.0, seed=5, sampler="murmur3_gumbel"))
+    b.sample(rng.normal(size=500).astype(np.float32), 3)         # an earlier draw does not matter
+    assert a.sample(logits, 17) == b.sample(logits, 17)
+    counts = np.zeros(3)
+    for position in range(3000):                                  # frequencies follow the softmax
+        s = RequestSampler(Sampling(temperature=1.0, seed=11, sampler="murmur3_gumbel"))
+        counts[s.sample(np.array([0.0, math.log(2.0), math.log(3.0)], dtype=np.float32), position)] += 1
+    assert np.allclose(counts / 3000, [1 / 6, 2 / 6, 3 / 6], atol=0.03)
+
+
+def test_request_fields_defaults_and_refusals():
+    s = Sampling.from_request({}, environ={})
+    assert (s.temperature, s.top_k, s.top_p, s.seed, s.presence_penalty) == (1.0, 20, 0.95, 42, 0.0)
+    assert Sampling.from_request({"temperature": 0}, environ={}).greedy
+    assert Sampling.from_request({}, environ={"LIA_SAMPLER": "murmur3_gumbel"}).sampler == "murmur3_gumbel"
+    for bad in ({"frequency_penalty": 0.5}, {"repetition_penalty": 1.1}, {"min_p": 0.1}, {"top_k": 21},
+                {"top_p": 0.0}, {"presence_penalty": 3}, {"temperature": -1}):
+        with pytest.raises(ValueError):
+            Sampling.from_request(bad, environ={})
+    with pytest.raises(ValueError, match="LIA_SAMPLER"):
+        Sampling.from_request({}, environ={"LIA_SAMPLER": "xorshift"})
+    assert Sampling(temperature=0.9, sampler="murmur3_gumbel").on_device and not Sampling(temperature=0.9).on_device

@@ -1,0 +1,164 @@
+"""The scheduler's decisions on the CPU, with a stand-in for the engine that keeps a real cache
+manager and returns logits that make the next token predictable."""
+import numpy as np
+import pytest
+import torch
+
+from lia_rs_b200.cache import CacheManager
+from lia_rs_b200.engine.scheduler import Scheduler, SchedulerError
+from lia_rs_b200.parts import KVCacheRequest
+from lia_rs_b200.sampling import Sampling
+
+VOCAB = 50
+
+
+class StandInEngine:
+    """next token = (sum of the request's tokens so far) mod VOCAB; records every batch and checks
+    that each batch continues each request exactly where its cache ends."""
+
+    def __init__(self, num_pages, page_size=4, max_slots=4, context=256):
+        self.cache = CacheManager({0: KVCacheRequest(1, 16)}, {}, num_pages, page_size, max_slots, context,
+                                  torch.float32, "cpu")
+        self.seen = {}            # slot -> tokens in the cache
+        self.batches = []
+
+    def step(self, entries):
+        rows = []
+        self.batches.append([(e.slot, e.start, len(e.tokens), list(e.want)) for e in entries])
+        for e in entries:
+            have = self.seen.setdefault(e.slot, [])
+            if e.start == 0:
+                have.clear()
+            assert e.start == len(have), "a portion does not continue where the cache ends"
+            assert e.start + len(e.tokens) <= self.cache.length[e.slot], "tokens without pages"
+            have.extend(e.tokens)
+            for w in e.want:
+                row = np.full(VOCAB, -1.0, dtype=np.float32)
+                row[sum(have[:e.start + w + 1]) % VOCAB] = 1.0
+                rows.append(row)
+        self.cache.check()
+        return torch.tensor(np.array(rows)) if rows else torch.zeros(0, VOCAB)
+
+    def select_tokens(self, logits, samplings, positions):
+        return [int(t) for t in logits.argmax(dim=-1)]
+
+    def logits_to_host(self, logits):
+        return logits.numpy()
+
+
+def expected(prompt, n):
+    tokens, out = list(prompt), []
+    for _ in range(n):
+        out.append(sum(tokens) % VOCAB)
+        tokens.append(out[-1])
+    return out
+
+
+def test_prompts_are_cut_under_the_token_budget_and_decodes_come_first():
+    engine = StandInEngine(num_pages=64)
+    s = Scheduler(engine, max_batch_tokens=8)
+    b = s.add("b", [7, 8, 9], max_tokens=4)
+    a = s.add("a", list(range(1, 20)), max_tokens=3)
+    s.run()
+    assert a.generated == expected(a.prompt, 3) and b.generated == expected(b.prompt, 4)
+    assert all(sum(n for _, _, n, _ in batch) <= 8 for batch in engine.batches)
+    # b's whole prompt and the first 5 tokens of a fill the budget of 8
+    assert engine.batches[0] == [(0, 0, 3, [2]), (1, 0, 5, [])]
+    # then b decodes: its single token comes first and a's portion gets the other 7 rows
+    assert engine.batches[1] == [(0, 3, 1, [0]), (1, 5, 7, [])]
+    assert engine.batches[2] == [(0, 4, 1, [0]), (1, 12, 7, [6])]
+    assert s.stats["prefill_tokens"] == 19 + 3 and engine.cache.available_pages() == 64
+
+
+def test_even_split_gives_every_request_its_share():
+    engine = StandInEngine(num_pages=64)
+    s = Scheduler(engine, max_batch_tokens=8, even_split=True)
+    a = s.add("a", list(range(1, 20)), max_tokens=2)
+    b = s.add("b", list(range(3, 15)), max_tokens=2)
+    s.step()
+    assert engine.batches[0] == [(0, 0, 4, []), (1, 0, 4, [])]
+    s.run()
+    assert a.generated == expected(a.prompt, 2) and b.generated == expected(b.prompt, 2)
+
+
+def test_admission_is_first_come_first_served_and_waits_for_a_slot():
+    engine = StandInEngine(num_pages=64, max_slots=2)
+    s = Scheduler(engine, max_batch_tokens=64)
+    requests = [s.add(i, [i + 1, i + 2], max_tokens=2 + i) for i in range(4)]
+    s.step()
+    assert [r.slot for r in requests] == [0, 1, None, None] and len(s.queue) == 2
+    s.run()
+    assert [r.generated for r in requests] == [expected(r.prompt, 2 + i) for i, r in enumerate(requests)]
+    order = [r.rid for r in s.finished]
+    assert order.index(0) < order.index(2) and s.stats["admitted"] == 4
+
+
+def test_end_of_sequence_and_limits():
+    engine = StandInEngine(num_pages=64)
+    stop = expected([5, 6], 3)[2]
+    s = Scheduler(engine, eos_token_ids=[stop], context=16)
+    r = s.add("r", [5, 6], max_tokens=10)
+    clamped = s.add("c", list(range(1, 13)), max_tokens=100)
+    too_long = s.add("t", list(range(1, 17)))
+    s.run()
+    assert r.generated == expected([5, 6], 3) and r.stopped
+    assert len(clamped.generated) == 4 and not clamped.stopped        # 16 - 12 tokens of context left
+    assert too_long.error == "prompt exceeds request context" and not too_long.generated
+
+
+def test_pages_run_out_preempt_recompute_and_finish():
+    # 6 pages of 4 tokens: two requests of 10 + 12 tokens cannot both reach their full length
+    engine = StandInEngine(num_pages=6)
+    s = Scheduler(engine, max_batch_tokens=64)
+    a = s.add("a", list(range(1, 9)), max_tokens=6)
+    b = s.add("b", list(range(2, 10)), max_tokens=6)
+    s.run()
+    assert a.generated == expected(a.prompt, 6) and b.generated == expected(b.prompt, 6)
+    assert s.stats["preemptions"] >= 1 and a.preemptions + b.preemptions == s.stats["preemptions"]
+    restarts = [batch for batch in engine.batches[1:] for (_, start, n, _) in batch if start == 0 and n > 1]
+    assert restarts, "a preempted request is recomputed from position 0"
+    assert engine.cache.available_pages() == 6 and engine.cache.free_slots() == 4
+
+
+def test_victim_is_the_request_that_already_produced_a_token_then_holds_most_pages():
+    engine = StandInEngine(num_pages=5)
+    s = Scheduler(engine, max_batch_tokens=8)
+    old = s.add("old", list(range(1, 8)), max_tokens=8)           # 7 tokens: 2 pages, then it decodes
+    s.step()
+    new = s.add("new", list(range(1, 13)), max_tokens=8)          # 12 tokens, 7 of them fit the next step
+    s.step()
+    assert len(old.generated) == 2 and new.computed == 7 and engine.cache.available_pages() == 1
+    s.step()              # old takes the last page for position 8; new's portion stops at its page's end
+    assert engine.batches[-1] == [(0, 8, 1, [0]), (1, 7, 1, [])] and engine.cache.available_pages() == 0
+    s.step()              # new needs a page and none is free: the request that already decodes is paused
+    assert s.stats["preemptions"] == 1 and old.slot is None and new.slot is not None and new.computed > 8
+    s.run()
+    assert old.generated == expected(old.prompt, 8) and new.generated == expected(new.prompt, 8)
+
+
+def test_one_request_larger_than_the_pool_is_an_error():
+    engine = StandInEngine(num_pages=2)
+    s = Scheduler(engine, max_batch_tokens=64)
+    s.add("big", list(range(1, 8)), max_tokens=5)
+    with pytest.raises(SchedulerError, match="one request exceeded its physical KV capacity"):
+        s.run()
+
+
+def test_a_portion_is_shortened_at_the_page_that_cannot_be_had():
+    engine = StandInEngine(num_pages=3)
+    s = Scheduler(engine, max_batch_tokens=64)
+    a = s.add("a", list(range(1, 7)), max_tokens=1)               # 6 tokens: 2 pages
+    b = s.add("b", list(range(1, 11)), max_tokens=1)              # 10 tokens: would need 3 pages
+    s.step()
+    assert engine.batches[0] == [(0, 0, 6, [5]), (1, 0, 4, [])]   # b gets the one page that is left
+    s.run()
+    assert a.generated == expected(a.prompt, 1) and b.generated == expected(b.prompt, 1)
+
+
+def test_host_sampling_is_used_when_the_rule_needs_it():
+    engine = StandInEngine(num_pages=16)
+    s = Scheduler(engine)
+    r = s.add("r", [1, 2, 3], Sampling(temperature=0.7, top_k=5, top_p=0.9, seed=3), max_tokens=5)
+    g = s.add("g", [1, 2, 3], Sampling(temperature=0.7, seed=3, presence_penalty=1.5), max_tokens=5)
+    s.run()
+    assert len(r.generated) == 5 and len(g.generated) == 5

@@ -1,0 +1,295 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the 2B-class MiniCPM5 Llama configuration on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of `--batch` requests, each with a 2,048-token uniform-random prompt in
+the cache (the pool is sized for the 32,768-token context of the configuration).  One JSON line is
+printed:
+
+  value      decoded tokens a second, K steps timed on the device with CUDA events (the tokens fed
+             are fixed beforehand, so the device never waits for the host)
+  e2e        the same through the scheduler that `generate()` runs: every step copies that step's
+             token ids, positions and slots from pinned host memory to the device and reads the
+             sampled token ids back to the host, which feed the next step
+  prefill    one step of a single 2,048-token prompt: tokens/s, ms, and flops / time / peak
+  roofline   the decode step's bytes (every weight once + the live requests' cache) / time / peak
+  points     decode tokens/s at batch 1 and 64
+
+Weights (4.1 GB) and cache are far larger than the 126 MB L2, so no L2 flush is needed between
+timed steps.  Peaks come from MEASURED_PEAKS.json beside this file when it exists.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the 2B-class configuration
+CONFIG_2B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048, intermediate_size=6144,
+                 num_hidden_layers=40, num_attention_heads=16, num_key_value_heads=2, head_dim=128,
+                 vocab_size=73448, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+                 scale_emb=12, scale_depth=1.4, dim_model_base=256, max_position_embeddings=32768,
+                 initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16")
+PROMPT = 2048
+PAGE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=p["hbm_gbs"], tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm=6650.0, tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", "0", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                         text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, top, reasons = [], None, set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                top = float(f[2])
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": top, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_bytes(cfg, layers):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nq + 2 * nkv) * d * h + nq * d * h + 3 * i * h + 2 * h
+    head = v * h                                     # tied: the table is read once, as the output matrix
+    return 2 * (layers * per_layer + head + h), 2 * layers * 2 * nkv * d      # weight bytes, cache bytes per token
+
+
+def prefill_flops(cfg, layers, tokens):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = 2 * tokens * layers * ((nq + 2 * nkv) * d * h + nq * d * h + 3 * i * h) + 2 * v * h
+    attention = layers * 4 * nq * d * tokens * (tokens + 1) / 2
+    return linear + attention
+
+
+def fill(engine, batch, prompt_tokens, rng_seed):
+    """Admit `batch` requests and put their prompts' keys and values in the cache by real prefill."""
+    import numpy as np
+    from lia_rs_b200.engine import StepEntry
+    rng = np.random.default_rng(rng_seed)
+    slots = []
+    vocab = engine.spec.vocab_size
+    for _ in range(batch):
+        slot = engine.admit()
+        tokens = [int(t) for t in rng.integers(0, vocab, size=prompt_tokens)]
+        assert engine.reserve(slot, 0, prompt_tokens)
+        engine.step([StepEntry(slot, tokens, 0, [])])
+        slots.append(slot)
+    engine.synchronize()
+    return slots
+
+
+def time_decode(engine, slots, start, steps, warmup):
+    """Device time of `steps` decode steps after `warmup` untimed ones; tokens are fixed beforehand."""
+    import numpy as np
+    import torch
+    from lia_rs_b200.engine import StepEntry
+    from lia_rs_b200.kernels import ops
+    rng = np.random.default_rng(1)
+    vocab = engine.spec.vocab_size
+    total = steps + warmup
+    feed = rng.integers(0, vocab, size=(total, len(slots)))
+    for slot in slots:
+        assert engine.reserve(slot, start, start + total)
+    picked = torch.empty(len(slots), dtype=torch.int32, device=engine.device)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    for k in range(total):
+        if k == warmup:
+            torch.cuda.synchronize()
+            launches = ops.LAUNCHES
+            begin.record()
+        entries = [StepEntry(slot, [int(feed[k, j])], start + k, [0]) for j, slot in enumerate(slots)]
+        logits = engine.step(entries)
+        ops.select_tokens(logits, picked)
+    end.record()
+    torch.cuda.synchronize()
+    engine.synchronize()
+    return begin.elapsed_time(end) / steps, (ops.LAUNCHES - launches) // steps
+
+
+def time_e2e(engine, batch, steps, warmup):
+    """Wall time per decode step through the scheduler: host token ids in, host token ids out."""
+    import numpy as np
+    import torch
+    from lia_rs_b200.engine.scheduler import Scheduler
+    rng = np.random.default_rng(2)
+    vocab = engine.spec.vocab_size
+    scheduler = Scheduler(engine, max_batch_tokens=engine.max_batch_tokens)
+    for i in range(batch):
+        scheduler.add(i, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], max_tokens=steps + warmup + 4)
+    while any(not r.generated for r in scheduler.live()) or scheduler.queue:
+        scheduler.step()
+    for _ in range(warmup):
+        scheduler.step()
+    torch.cuda.synchronize()
+    h2d = d2h = 0
+    started = time.perf_counter()
+    for _ in range(steps):
+        scheduler.step()
+        h2d += engine.runtime_step.h2d_bytes
+        d2h += 4 * batch
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    for request in scheduler.live():
+        engine.release(request.slot)
+    return seconds / steps, h2d // steps, d2h // steps
+
+
+def time_prefill(engine, warmup=2, repeats=3):
+    import numpy as np
+    import torch
+    from lia_rs_b200.engine import StepEntry
+    rng = np.random.default_rng(3)
+    tokens = [int(t) for t in rng.integers(0, engine.spec.vocab_size, size=PROMPT)]
+    best = None
+    for k in range(warmup + repeats):
+        slot = engine.admit()
+        assert engine.reserve(slot, 0, PROMPT)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        engine.step([StepEntry(slot, tokens, 0, [PROMPT - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.synchronize()
+        engine.release(slot)
+        if k >= warmup:
+            ms = begin.elapsed_time(end)
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=CONFIG_2B["num_hidden_layers"],
+                        help="run fewer layers than the configuration's 40 (both numbers are reported)")
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "Heltion/lia.rs is a Rust crate (nightly toolchain + NVIDIA cuda-rust git dependency, no "
+                          "Python package); pip cannot install it offline and no cargo/rustc exists in this image"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from lia_rs_b200 import LlamaConfig
+    from lia_rs_b200.engine import Engine
+
+    cfg = dict(CONFIG_2B, num_hidden_layers=args.layers)
+    config = LlamaConfig.from_dict(cfg)
+    peak = peaks()
+    largest = args.batch if args.no_points else max(args.batch, 64)
+    total_steps = args.steps + args.warmup
+    pool = largest * ((PROMPT + total_steps + 8 + 63) // 64 * 64) + PROMPT
+    engine = Engine.random(config, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=largest,
+                           max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
+    weight_bytes, cache_bytes_per_token = model_bytes(cfg, args.layers)
+
+    def decode_point(batch, steps, warmup):
+        slots = fill(engine, batch, PROMPT, 10 + batch)
+        ms, launches = time_decode(engine, slots, PROMPT, steps, warmup)
+        for slot in slots:
+            engine.release(slot)
+        return ms, launches
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms, launches = decode_point(args.batch, args.steps, args.warmup)
+    clocks = sampler.stop()
+    value = args.batch * 1000.0 / ms
+    context = PROMPT + args.warmup + args.steps // 2
+    step_bytes = weight_bytes + args.batch * context * cache_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    e2e_s, h2d, d2h = time_e2e(engine, args.batch, args.steps, args.warmup)
+    prefill_ms = time_prefill(engine)
+    flops = prefill_flops(cfg, args.layers, PROMPT)
+    points = {}
+    if not args.no_points:
+        for batch in (1, 64):
+            point_ms, _ = decode_point(batch, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
+
+    line = {
+        "metric": "decode tokens/s (2B-class MiniCPM5 Llama, batch %d, 2,048-token prompts, bf16, one B200)" % args.batch,
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {"model": "MiniCPM5-Llama-2B-class", "layers": args.layers, "layers_of_config": 40,
+                   "hidden": 2048, "heads": 16, "kv_heads": 2, "head_dim": 128, "intermediate": 6144,
+                   "vocab": 73448, "tied_head": True, "global_batch": args.batch, "seq_len": PROMPT,
+                   "context_length": cfg["max_position_embeddings"], "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (4.1 GB weights + cache per step)", "peaks": peak["source"]},
+        "e2e": {"value": round(args.batch / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches),
+        "prefill": {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

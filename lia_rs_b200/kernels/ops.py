@@ -71,7 +71,12 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = 0      # kernels launched through this module since import (a benchmark's own count)
+
+
 def _check(code: int, what: str):
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, code)}")
 

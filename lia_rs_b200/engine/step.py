@@ -157,7 +157,8 @@ class StepRuntime:
             self._error_host[0] = 0
             self.error_flag.zero_()
             raise StepError({1: "a token id outside the vocabulary reached the embedding kernel",
-                             2: "a token's block table entry has no page"}.get(code, f"device error {code}"))
+                             2: "a token's block table entry has no page",
+                             3: "a kernel gave up waiting on an mbarrier"}.get(code, f"device error {code}"))
 
     # ---- attention ----
     def attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):

@@ -46,6 +46,8 @@ class _Signatures:
                      c_int, c_int, c_float, c_void_p]
     lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                   c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
 
 
@@ -123,6 +125,42 @@ def gemm_simt(mode, a, w, out, alpha: float = 1.0):
     _check(lib().lia_gemm_simt(mode, _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
                                w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0), M, N, K, alpha,
                                _stream()), "gemm_simt")
+
+
+_SCRATCH_FLOATS = 16 << 20          # 64 MB of split-K scratch per device, allocated at first use
+_scratch = {}
+_sm_count = {}
+
+
+def _device_scratch(device):
+    key = torch.device(device).index or 0
+    if key not in _scratch:
+        _scratch[key] = torch.empty(_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+        _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _scratch[key], _sm_count[key]
+
+
+def gemm_tc_accepts(mode, a, w, out) -> bool:
+    """Whether the tcgen05 kernel takes this product: bfloat16 operands, K and the row strides
+    multiples of 8 elements (TMA needs 16-byte rows), 16-byte aligned bases."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores; see csrc/gemm_tc.cu.  Products
+    with few tiles split K and use this device's scratch, so calls on one device must not overlap."""
+    M, K = a.shape
+    N = out.shape[1]
+    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    scratch, sms = _device_scratch(a.device)
+    _check(lib().lia_gemm_tc(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                             out.stride(0), M, N, K, alpha, _p(scratch), scratch.numel(), sms, _p(error_flag),
+                             _stream()), "gemm_tc")
 
 
 def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale):

@@ -17,8 +17,7 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 
 
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
-    fast = getattr(ops, "gemm_tc", None)
-    if fast is not None and a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
-        fast(mode, a, w, out, alpha)
+    if a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
+        ops.gemm_tc(mode, a, w, out, alpha)
     else:
         ops.gemm_simt(mode, a, w, out, alpha)

@@ -217,3 +217,43 @@ def test_select_tokens_greedy_ties_and_gumbel_matches_the_host_rule():
                         torch.arange(4000, dtype=torch.int64, device=DEV))
     freq = torch.bincount(picks.long(), minlength=3).double() / 4000
     assert torch.allclose(freq.cpu(), torch.tensor([1 / 8, 2 / 8, 5 / 8], dtype=torch.float64), atol=0.03)
+
+
+@pytest.mark.parametrize("M", [1, 8, 40, 64, 100, 300, 1000])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96)])
+def test_gemm_tc_all_epilogues_against_64_bit(M, N, K):
+    """The tcgen05 product at sizes that are no multiple of its tiles, with and without split K."""
+    o = ops()
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert o.gemm_tc_accepts(o.GEMM_STORE, a, w, torch.empty(M, N, device=DEV))
+    exact = a.double() @ w.double().T
+    scale = max(1.0, float(exact.abs().max()))
+    out = torch.full((M, N), 7.0, device=DEV)
+    o.gemm_tc(o.GEMM_STORE, a, w[:N], out, 0.25, flag)
+    assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(K / 64)
+    half = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_tc(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
+    assert float((half.double() - exact[:, :N]).abs().max()) <= 2.0 ** -8 * scale
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    o.gemm_tc(o.GEMM_ACCUM, a, w[:N], acc, 1.5, flag)
+    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(K / 64)
+    act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_tc(o.GEMM_SWIGLU, a, w, act, 1.0, flag)
+    gate, up = exact[:, :N], exact[:, N:]
+    want = up * gate / (1 + torch.exp(-gate))
+    assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+
+
+def test_gemm_tc_refuses_what_tma_cannot_address():
+    o = ops()
+    a = torch.randn(4, 100, device=DEV).to(torch.bfloat16)          # K = 100: rows of 200 bytes
+    w = torch.randn(16, 100, device=DEV).to(torch.bfloat16)
+    assert not o.gemm_tc_accepts(o.GEMM_STORE, a, w, torch.empty(4, 16, device=DEV))
+    with pytest.raises(o.KernelError, match="refuses"):
+        o.gemm_tc(o.GEMM_STORE, a, w, torch.empty(4, 16, device=DEV))

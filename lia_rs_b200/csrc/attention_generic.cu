@@ -19,13 +19,16 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          const T* __restrict__ v_pages, const int* __restrict__ positions,
                          const int* __restrict__ slots, const int* __restrict__ block_table,
-                         int table_stride, T* __restrict__ out, int n_tokens, int nq, int nkv, int d,
+                         int table_stride, const int* __restrict__ rows, T* __restrict__ out, int n_tokens,
+                         int nq, int nkv, int d,
                          int page_size, int window, float scale) {
     __shared__ float q_shared[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
     if (item >= (long long)n_tokens * nq) return;
-    const int t = (int)(item / nq), h = (int)(item % nq);
+    const int t = rows ? rows[item / nq] : (int)(item / nq);
+    const int h = (int)(item % nq);
+    if (t < 0) return;
     const int slot = slots[t];
     if (slot < 0) return;
     const int pos = positions[t];
@@ -83,10 +86,12 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 }
 }  // namespace
 
-// q, out [n_tokens, nq, d]; k_pages, v_pages [num_pages, page_size, nkv, d]; all of `dtype`.
+// q, out [tokens, nq, d]; k_pages, v_pages [num_pages, page_size, nkv, d]; all of `dtype`.
+// `rows` (optional) lists the n_tokens batch indices to compute; without it tokens 0..n_tokens-1.
 LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const void* v_pages, int dtype,
                                      const int* positions, const int* slots, const int* block_table,
-                                     int table_stride, void* out, int n_tokens, int nq, int nkv, int d,
+                                     int table_stride, const int* rows, void* out, int n_tokens, int nq,
+                                     int nkv, int d,
                                      int page_size, int window, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || d > MAX_D || d % 16 || page_size <= 0)
@@ -97,11 +102,11 @@ LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const v
     if (dtype == LIA_F32)
         attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, slots, block_table,
-            table_stride, (float*)out, n_tokens, nq, nkv, d, page_size, window, scale);
+            table_stride, rows, (float*)out, n_tokens, nq, nkv, d, page_size, window, scale);
     else if (dtype == LIA_BF16)
         attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, positions,
-            slots, block_table, table_stride, (__nv_bfloat16*)out, n_tokens, nq, nkv, d, page_size, window,
+            slots, block_table, table_stride, rows, (__nv_bfloat16*)out, n_tokens, nq, nkv, d, page_size, window,
             scale);
     else
         return LIA_ERR_DTYPE;

@@ -44,7 +44,7 @@ class StepContext:
         self.runtime = runtime
         self.n_tokens, self.n_out = n_tokens, n_out
         self.segments = segments                      # [(slot, start, count, offset in the batch)]
-        self.tokens, self.positions, self.slots, self.out_rows = meta
+        self.tokens, self.positions, self.slots, self.out_rows, self.decode_rows, self.prefill_rows = meta
         self.error_flag = runtime.error_flag
         self.decode_only = all(count == 1 for _, _, count, _ in segments)
         self.max_context = max((start + count for _, start, count, _ in segments), default=0)
@@ -75,8 +75,9 @@ class StepRuntime:
         self.max_batch_tokens = int(max_batch_tokens)
         self.device = torch.device(device)
         cap = self.max_batch_tokens
-        self._meta_host = torch.zeros(4 * cap, dtype=torch.int32, pin_memory=True)
-        self._meta_device = torch.zeros(4 * cap, dtype=torch.int32, device=self.device)
+        self._meta_host = torch.zeros(5 * cap, dtype=torch.int32, pin_memory=True)
+        self._meta_device = torch.zeros(5 * cap, dtype=torch.int32, device=self.device)
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._copy_event = torch.cuda.Event()
@@ -92,6 +93,14 @@ class StepRuntime:
             buf = torch.empty((max(rows, self.max_batch_tokens), width), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]
+
+    def scratch(self, name, numel, dtype):
+        """A flat scratch buffer of at least `numel` elements (grows, never shrinks)."""
+        buf = self._buffers.get((name, dtype))
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._buffers[(name, dtype)] = buf
+        return buf[:numel]
 
     def logits(self, rows, vocab):
         buf = self._logits_buffer
@@ -131,20 +140,25 @@ class StepRuntime:
             tokens.extend(entry.tokens)
             positions.extend(range(entry.start, entry.start + count))
             slots.extend([entry.slot] * count)
+        decode_rows = [offset for _, _, count, offset in segments if count == 1]
+        prefill_rows = [offset + i for _, _, count, offset in segments if count > 1 for i in range(count)]
         n, n_out = len(tokens), len(out_rows)
         if n > self.max_batch_tokens:
             raise StepError(f"{n} tokens in one step exceed max_batch_tokens={self.max_batch_tokens}")
         self._copy_event.synchronize()               # the staging buffer of the last step is free again
         self.raise_device_errors()
         host = self._meta_host
-        packed = torch.tensor(tokens + positions + slots + out_rows, dtype=torch.int32)
-        total = 3 * n + n_out
+        packed = torch.tensor(tokens + positions + slots + out_rows + decode_rows + prefill_rows,
+                              dtype=torch.int32)
+        total = 4 * n + n_out
         host[:total] = packed
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
         self.cache.flush()
         self._copy_event.record()
         dev = self._meta_device
-        meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:3 * n + n_out])
+        at = 3 * n + n_out
+        meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:at], dev[at:at + len(decode_rows)],
+                dev[at + len(decode_rows):at + n])
         self.h2d_bytes = total * 4
         return StepContext(self, n, n_out, segments, meta)
 
@@ -162,5 +176,31 @@ class StepRuntime:
 
     # ---- attention ----
     def attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):
-        ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
-                              nq, nkv, d, window, scale)
+        """Single decoded tokens go to the split-key tensor-core kernel when the cache is bfloat16
+        and the head size is one it is built for; everything else to the kernel for every size."""
+        if not (q.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS):
+            ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
+                                  nq, nkv, d, window, scale)
+            return
+        if ctx.decode_rows.numel():
+            split_len, n_splits = self.decode_split_plan(ctx, nq, nkv, window)
+            partial = None
+            if n_splits > 1:
+                partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
+            ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
+                                 kv.block_table, out, partial, nq, nkv, d, window, scale, split_len, n_splits)
+        if ctx.prefill_rows.numel():
+            ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
+                                  nq, nkv, d, window, scale, rows=ctx.prefill_rows)
+
+    def decode_split_plan(self, ctx, nq, nkv, window):
+        """(split_len, n_splits) for this step's decoded tokens: enough ranges of keys to give every
+        SM about two CTAs, each range a multiple of 64 keys."""
+        span = max(start + 1 for _, start, count, _ in ctx.segments if count == 1)
+        if window:
+            span = min(span, window)
+        groups = nkv * ((nq // nkv + 15) // 16)
+        ctas = max(1, ctx.decode_rows.numel() * groups)
+        wanted = max(1, (2 * self.sm_count + ctas - 1) // ctas)
+        split_len = max(64, ((span + wanted - 1) // wanted + 63) // 64 * 64)
+        return split_len, (span + split_len - 1) // split_len

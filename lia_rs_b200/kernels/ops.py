@@ -44,8 +44,11 @@ class _Signatures:
                          c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_simt = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
                      c_int, c_int, c_float, c_void_p]
-    lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_int, c_int, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -163,15 +166,34 @@ def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
                              _stream()), "gemm_tc")
 
 
-def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale):
-    _cuda(q, k_pages, v_pages, positions, slots, block_table, out)
+def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale,
+                      rows=None):
+    """Attention for every token of the batch, or for the tokens whose batch indices `rows` lists."""
+    _cuda(q, k_pages, v_pages, positions, slots, block_table, out, rows)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
         raise KernelError("attention: q, cache and out must have one element type")
-    n = q.shape[0]
+    n = q.shape[0] if rows is None else rows.shape[0]
     _check(lib().lia_attention_generic(_p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(positions),
-                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), n, nq, nkv,
-                                       d, k_pages.shape[1], int(window or 0), scale, _stream()),
+                                       _p(slots), _p(block_table), block_table.shape[1], _p(rows), _p(out), n, nq,
+                                       nkv, d, k_pages.shape[1], int(window or 0), scale, _stream()),
            "attention_generic")
+
+
+DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention kernels are built for
+
+
+def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
+                     scale, split_len, n_splits):
+    """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
+    csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results."""
+    _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("attention_decode is a bfloat16 kernel")
+    _check(lib().lia_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(rows), rows.shape[0], _p(positions),
+                                      _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
+                                      0 if partial is None else partial.numel(), q.shape[0], nq, nkv, d,
+                                      k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _stream()),
+           "attention_decode")
 
 
 def select_tokens(logits, out, temperature=None, seeds=None, positions=None):

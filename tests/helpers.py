@@ -71,9 +71,9 @@ _PLAIN_CACHE = {}
 
 
 def rounds_probabilities(head_dim: int) -> bool:
-    """The bfloat16 path's tensor-core attention kernels (head sizes 64 and 128) feed 16-bit
+    """The bfloat16 path's tensor-core attention kernels (head sizes 32, 64 and 128) feed 16-bit
     probabilities to the tensor cores; the kernel for every other head size keeps them in 32-bit."""
-    return False
+    return head_dim in (32, 64, 128)
 
 
 def plain_logits(model: dict, tokens, dtype: str = "float32") -> torch.Tensor:

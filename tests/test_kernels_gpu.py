@@ -257,3 +257,49 @@ def test_gemm_tc_refuses_what_tma_cannot_address():
     assert not o.gemm_tc_accepts(o.GEMM_STORE, a, w, torch.empty(4, 16, device=DEV))
     with pytest.raises(o.KernelError, match="refuses"):
         o.gemm_tc(o.GEMM_STORE, a, w, torch.empty(4, 16, device=DEV))
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window,split_len", [
+    (128, 16, 2, 16, None, 128), (128, 16, 2, 16, None, 4096), (64, 16, 2, 4, None, 64), (32, 3, 1, 16, 100, 64),
+    (64, 40, 2, 8, None, 192), (128, 32, 2, 32, 700, 256), (32, 8, 8, 16, None, 64)])
+def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len):
+    """Tensor-core decode attention: groups of up to 16 query heads per kv head, ranges of keys merged,
+    a far key that dominates, the window's edge, scrambled pages, rows that are skipped."""
+    torch.manual_seed(d + nq)
+    T = 1500
+    k = torch.randn(T, nkv, d, device=DEV) * 0.5
+    v = torch.randn(T, nkv, d, device=DEV)
+    positions = [0, 1, 62, 63, 64, 127, 128, 700, 1498, 1499]
+    q = torch.randn(len(positions), nq, d, device=DEV) * 0.5
+    far = 3 if not window else 1499 - window + 1
+    k[far] = 0
+    k[far, :, 0] = 6.0
+    q[-1, :, 0] = 4.0 * math.sqrt(d)
+    if window:
+        k[far - 1, :, 1] = 50.0
+        q[-1, :, 1] = 4.0 * math.sqrt(d)
+    q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    blocks = (T + page_size - 1) // page_size
+    num_pages = blocks + 5
+    order = np.random.default_rng(1).permutation(num_pages)[:blocks]
+    kp, table = paged(k, page_size, num_pages, order)
+    vp, _ = paged(v, page_size, num_pages, order)
+    bt = torch.full((2, blocks + 1), -1, dtype=torch.int32)
+    bt[1, :blocks] = table
+    n = len(positions)
+    rows = torch.tensor([0, 1, 2, 3, -1, 5, 6, 7, 8, 9], dtype=torch.int32, device=DEV)     # row 4 is skipped
+    out = torch.full((n, nq * d), 7.0, device=DEV, dtype=torch.bfloat16)
+    span = min(1500, window) if window else 1500
+    n_splits = (span + split_len - 1) // split_len
+    partial = torch.empty(n * nq * n_splits * (d + 1), device=DEV) if n_splits > 1 else None
+    scale = 1 / math.sqrt(d)
+    ops().attention_decode(q.view(n, nq * d), kp, vp, rows, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                           torch.ones(n, dtype=torch.int32, device=DEV), bt.to(DEV), out, partial, nq, nkv, d, window,
+                           scale, split_len, n_splits)
+    want = reference_attention(q, k, v, positions, window, scale)
+    got = out.view(n, nq, d).double()
+    keep = [i for i in range(n) if i != 4]
+    error = float((got[keep] - want[keep]).abs().max())
+    assert error <= 1.6e-2 * max(1.0, float(want.abs().max())), error
+    assert float((out[4].float() - 7.0).abs().max()) == 0
+    assert float((got[-1, 0] - v[far, 0].double()).abs().max()) < 0.05

@@ -44,7 +44,9 @@ class StepContext:
         self.runtime = runtime
         self.n_tokens, self.n_out = n_tokens, n_out
         self.segments = segments                      # [(slot, start, count, offset in the batch)]
-        self.tokens, self.positions, self.slots, self.out_rows, self.decode_rows, self.prefill_rows = meta
+        (self.tokens, self.positions, self.slots, self.out_rows, self.decode_rows, self.prefill_rows,
+         self.prefill_segments) = meta
+        self.n_prefill_segments = sum(1 for _, _, count, _ in segments if count > 1)
         self.error_flag = runtime.error_flag
         self.decode_only = all(count == 1 for _, _, count, _ in segments)
         self.max_context = max((start + count for _, start, count, _ in segments), default=0)
@@ -75,8 +77,8 @@ class StepRuntime:
         self.max_batch_tokens = int(max_batch_tokens)
         self.device = torch.device(device)
         cap = self.max_batch_tokens
-        self._meta_host = torch.zeros(5 * cap, dtype=torch.int32, pin_memory=True)
-        self._meta_device = torch.zeros(5 * cap, dtype=torch.int32, device=self.device)
+        self._meta_host = torch.zeros(7 * cap, dtype=torch.int32, pin_memory=True)
+        self._meta_device = torch.zeros(7 * cap, dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
@@ -148,9 +150,10 @@ class StepRuntime:
         self._copy_event.synchronize()               # the staging buffer of the last step is free again
         self.raise_device_errors()
         host = self._meta_host
-        packed = torch.tensor(tokens + positions + slots + out_rows + decode_rows + prefill_rows,
-                              dtype=torch.int32)
-        total = 4 * n + n_out
+        prefill_segments = [x for _, start, count, offset in segments if count > 1 for x in (offset, start, count)]
+        packed = torch.tensor(tokens + positions + slots + out_rows + decode_rows + prefill_rows
+                              + prefill_segments, dtype=torch.int32)
+        total = 4 * n + n_out + len(prefill_segments)
         host[:total] = packed
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
         self.cache.flush()
@@ -158,7 +161,7 @@ class StepRuntime:
         dev = self._meta_device
         at = 3 * n + n_out
         meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:at], dev[at:at + len(decode_rows)],
-                dev[at + len(decode_rows):at + n])
+                dev[at + len(decode_rows):at + n], dev[at + n:total])
         self.h2d_bytes = total * 4
         return StepContext(self, n, n_out, segments, meta)
 
@@ -176,8 +179,9 @@ class StepRuntime:
 
     # ---- attention ----
     def attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):
-        """Single decoded tokens go to the split-key tensor-core kernel when the cache is bfloat16
-        and the head size is one it is built for; everything else to the kernel for every size."""
+        """With a bfloat16 cache and a head size the tensor-core kernels are built for, single decoded
+        tokens go to the split-key kernel and prompt portions to the prefill kernel; everything else
+        goes to the kernel for every size."""
         if not (q.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS):
             ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
                                   nq, nkv, d, window, scale)
@@ -189,9 +193,15 @@ class StepRuntime:
                 partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
             ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
                                  kv.block_table, out, partial, nq, nkv, d, window, scale, split_len, n_splits)
-        if ctx.prefill_rows.numel():
-            ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
-                                  nq, nkv, d, window, scale, rows=ctx.prefill_rows)
+        if ctx.n_prefill_segments:
+            per_tile = ops.attention_prefill_tokens_per_tile(nq // nkv)
+            if per_tile:
+                tiles = sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1)
+                ops.attention_prefill(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments,
+                                      tiles, ctx.slots, kv.block_table, out, nq, nkv, d, window, scale)
+            else:
+                ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
+                                      nq, nkv, d, window, scale, rows=ctx.prefill_rows)
 
     def decode_split_plan(self, ctx, nq, nkv, window):
         """(split_len, n_splits) for this step's decoded tokens: enough ranges of keys to give every

@@ -51,6 +51,8 @@ class _Signatures:
                             c_float, c_int, c_int, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
+    lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
 
 
@@ -194,6 +196,23 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
                                       0 if partial is None else partial.numel(), q.shape[0], nq, nkv, d,
                                       k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _stream()),
            "attention_decode")
+
+
+def attention_prefill_tokens_per_tile(group: int) -> int:
+    """Tokens of a portion that one CTA of the prefill kernel takes (0: group size not supported)."""
+    return 64 // group if 1 <= group <= 64 else 0
+
+
+def attention_prefill(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
+                      window, scale):
+    """Tensor-core attention (bfloat16) for the prompt portions listed in `segments`
+    ([n_segments, 3] int32: first batch index, first position, count); see csrc/attention_prefill.cu."""
+    _cuda(q, k_pages, v_pages, segments, slots, block_table, out)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("attention_prefill is a bfloat16 kernel")
+    _check(lib().lia_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
+                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
+                                       k_pages.shape[1], int(window or 0), scale, _stream()), "attention_prefill")
 
 
 def select_tokens(logits, out, temperature=None, seeds=None, positions=None):

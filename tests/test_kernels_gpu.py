@@ -303,3 +303,56 @@ def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len):
     assert error <= 1.6e-2 * max(1.0, float(want.abs().max())), error
     assert float((out[4].float() - 7.0).abs().max()) == 0
     assert float((got[-1, 0] - v[far, 0].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window", [(128, 16, 2, 16, None), (64, 16, 2, 4, None), (32, 3, 1, 16, 40),
+                                                       (64, 10, 2, 8, 150), (128, 4, 4, 32, None), (32, 64, 1, 16, None)])
+def test_attention_prefill_portions(d, nq, nkv, page_size, window):
+    """Tensor-core prefill attention: portions that start and end anywhere (at 0, inside a page, one that
+    continues an earlier portion), groups that do not divide 64, a far key that dominates, the window's
+    edge, scrambled pages, two requests in one launch."""
+    torch.manual_seed(d + nq)
+    T = 700
+    scale = 1 / math.sqrt(d)
+    # request in slot 1: 700 tokens, this step brings [437, 700); request in slot 0: 150 tokens, whole
+    ka, va = torch.randn(T, nkv, d, device=DEV) * 0.5, torch.randn(T, nkv, d, device=DEV)
+    kb, vb = torch.randn(150, nkv, d, device=DEV) * 0.5, torch.randn(150, nkv, d, device=DEV)
+    qa, qb = torch.randn(T - 437, nq, d, device=DEV) * 0.5, torch.randn(150, nq, d, device=DEV) * 0.5
+    far = 3 if not window else 699 - window + 1
+    ka[far] = 0
+    ka[far, :, 0] = 6.0
+    qa[-1, :, 0] = 4.0 * math.sqrt(d)
+    if window:
+        ka[far - 1, :, 1] = 50.0
+        qa[-1, :, 1] = 4.0 * math.sqrt(d)
+    bf = lambda x: x.to(torch.bfloat16)
+    ka, va, kb, vb, qa, qb = map(bf, (ka, va, kb, vb, qa, qb))
+    blocks_a, blocks_b = (T + page_size - 1) // page_size, (150 + page_size - 1) // page_size
+    num_pages = blocks_a + blocks_b + 4
+    order = np.random.default_rng(2).permutation(num_pages)
+    kp = torch.zeros(num_pages, page_size, nkv, d, device=DEV, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    bt = torch.full((2, blocks_a + 1), -1, dtype=torch.int32)
+    for slot, (kk, vv, blocks, base) in enumerate([(kb, vb, blocks_b, 0), (ka, va, blocks_a, blocks_b)]):
+        for b in range(blocks):
+            page = int(order[base + b])
+            bt[slot, b] = page
+            chunk = slice(b * page_size, min((b + 1) * page_size, kk.shape[0]))
+            kp[page, :chunk.stop - chunk.start] = kk[chunk]
+            vp[page, :chunk.stop - chunk.start] = vv[chunk]
+    q = torch.cat([qb, qa]).contiguous()
+    n = q.shape[0]
+    slots = torch.tensor([0] * 150 + [1] * (T - 437), dtype=torch.int32, device=DEV)
+    segments = torch.tensor([[0, 0, 150], [150, 437, T - 437]], dtype=torch.int32, device=DEV)
+    per_tile = ops().attention_prefill_tokens_per_tile(nq // nkv)
+    tiles = (150 + per_tile - 1) // per_tile + (T - 437 + per_tile - 1) // per_tile
+    out = torch.zeros(n, nq * d, device=DEV, dtype=torch.bfloat16)
+    ops().attention_prefill(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), out, nq, nkv, d,
+                            window, scale)
+    want_b = reference_attention(qb, kb, vb, list(range(150)), window, scale)
+    want_a = reference_attention(qa, ka, va, list(range(437, T)), window, scale)
+    got = out.view(n, nq, d).double()
+    limit = 1.6e-2 * max(1.0, float(want_a.abs().max()), float(want_b.abs().max()))
+    assert float((got[:150] - want_b).abs().max()) <= limit
+    assert float((got[150:] - want_a).abs().max()) <= limit
+    assert float((got[-1, 0] - va[far, 0].double()).abs().max()) < 0.05

@@ -134,7 +134,10 @@ attention_decode_kernel(Params p) {
             for (int r = 0; r < 2; ++r) {
                 tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
                 tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-                const float new_max = fmaxf(row_max[r], tile_max[r]);     // finite: key0 < key_end
+                // The reference point of the exponentials is a whole number (in base-2 logarithms), so the
+                // 16-bit probabilities have the same mantissas whatever tile, warp or range a key falls
+                // in, and rescaling by `correction` is exact.
+                const float new_max = fmaxf(row_max[r], ceilf(tile_max[r]));     // finite: key0 < key_end
                 correction[r] = exp2f(row_max[r] - new_max);
                 row_max[r] = new_max;
                 row_sum[r] *= correction[r];

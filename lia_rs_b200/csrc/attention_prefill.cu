@@ -168,7 +168,8 @@ attention_prefill_kernel(PrefillParams p) {
         for (int r = 0; r < 2; ++r) {
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-            const float new_max = fmaxf(row_max[r], tile_max[r]);
+            // whole-number reference point: see attention_decode.cu
+            const float new_max = fmaxf(row_max[r], ceilf(tile_max[r]));
             // a row that has seen no key yet keeps maximum -inf; exponentials are taken against 0 then
             safe_max[r] = new_max == -INFINITY ? 0.f : new_max;
             correction[r] = exp2f(row_max[r] - safe_max[r]);

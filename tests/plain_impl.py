@@ -92,8 +92,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window, store=N
             out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, kh, :]
         else:
             # the serving path feeds 16-bit probabilities to the tensor cores and divides by the
-            # 32-bit sum afterwards
-            p = torch.exp(scores - scores.max(dim=-1, keepdim=True).values)
+            # 32-bit sum afterwards; it takes the exponentials in base 2 against a whole-number
+            # reference point, so that the 16-bit mantissas do not depend on how the keys are tiled
+            log2_scores = scores * math.log2(math.e)
+            p = torch.exp2(log2_scores - torch.ceil(log2_scores.max(dim=-1, keepdim=True).values))
             out[:, h, :] = (store(p) @ v[:, kh, :]) / p.sum(dim=-1, keepdim=True)
     return out
 

@@ -402,3 +402,63 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, (float*)out, ldo, s, alpha, 1, error_flag, stream);
     return launch<GEMM_SWIGLU, __nv_bfloat16>(mw, mx, (__nv_bfloat16*)out, ldo, s, alpha, 1, error_flag, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same product for callers that must not allocate: see gemm_tc_noalloc.h for who they are and for
+// the contract.  The split-K scratch is a static array in the library image instead of a caller's buffer.
+#include <mutex>
+
+#include "gemm_tc_noalloc.h"
+
+namespace {
+constexpr long long NOALLOC_FLOATS = LIA_GEMM_NOALLOC_SCRATCH_BYTES / sizeof(float);
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float noalloc_scratch[NOALLOC_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_address[NOALLOC_MAX_DEVICES] = {};
+std::mutex noalloc_mutex;
+
+// Device address of the static array on the current device; looked up once per device.
+int noalloc_scratch_address(float** address) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NOALLOC_MAX_DEVICES) return LIA_ERR_DRIVER;
+    std::lock_guard<std::mutex> lock(noalloc_mutex);
+    if (!noalloc_address[device]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, noalloc_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return LIA_ERR_DRIVER;
+        }
+        noalloc_address[device] = (float*)p;
+    }
+    *address = noalloc_address[device];
+    return LIA_OK;
+}
+}  // namespace
+
+// The split plan lia_gemm_tc makes when its scratch is large enough, restated so that the need is known
+// before anything is launched.
+LIA_EXPORT long long lia_gemm_tc_noalloc_scratch_floats(int mode, int M, int N, int K, int sm_count) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int n_total = mode == GEMM_SWIGLU ? 2 * N : N;
+    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tile = pick_n_tile(M, false);
+    const long long tiles = (long long)((n_total + TILE_F - 1) / TILE_F) * ((M + n_tile - 1) / n_tile);
+    if (!(tiles < sm_count && M <= 256)) return 0;
+    int splits = (int)min((long long)16, (2LL * sm_count + tiles - 1) / tiles);
+    splits = min(splits, max(1, kblocks / 4));
+    if (splits <= 1) return 0;
+    return (long long)splits * M * n_total;
+}
+
+LIA_EXPORT int lia_gemm_tc_noalloc(int mode, const void* X, int ldx, const void* W, int ldw, void* out,
+                                   int out_dtype, int ldo, int M, int N, int K, float alpha, int sm_count,
+                                   int* error_flag, cudaStream_t stream) {
+    if (lia_gemm_tc_noalloc_scratch_floats(mode, M, N, K, sm_count) > NOALLOC_FLOATS) return LIA_ERR_SCRATCH;
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc != LIA_OK) return rc;
+    return lia_gemm_tc(mode, X, ldx, W, ldw, out, out_dtype, ldo, M, N, K, alpha, scratch, NOALLOC_FLOATS,
+                       sm_count, error_flag, stream);
+}

@@ -142,7 +142,7 @@ def time_decode(engine, slots, start, steps, warmup):
     for k in range(total):
         if k == warmup:
             torch.cuda.synchronize()
-            launches = ops.LAUNCHES
+            launches = engine.stats["kernels"]
             begin.record()
         entries = [StepEntry(slot, [int(feed[k, j])], start + k, [0]) for j, slot in enumerate(slots)]
         logits = engine.step(entries)
@@ -150,7 +150,8 @@ def time_decode(engine, slots, start, steps, warmup):
     end.record()
     torch.cuda.synchronize()
     engine.synchronize()
-    return begin.elapsed_time(end) / steps, (ops.LAUNCHES - launches) // steps
+    # kernels of the model's step (counted at the launch sites; a graph replay adds its kernel nodes) + selection
+    return begin.elapsed_time(end) / steps, (engine.stats["kernels"] - launches) // steps + 1
 
 
 def time_e2e(engine, batch, steps, warmup):

@@ -31,6 +31,15 @@ struct Params {
     float scale_log2;                // softmax scale * log2(e)
 };
 
+// Keys per range for a token that sees `span` keys: the given length, or (split_len 0) the span cut into
+// n_splits ranges of a multiple of 64 keys.  The second rule depends on the token's own span and on
+// n_splits alone, so a launch captured in a CUDA graph serves every context length.
+__device__ __forceinline__ int range_length(const Params& p, int span) {
+    if (p.split_len > 0) return p.split_len;
+    const int per = (span + p.n_splits - 1) / p.n_splits;
+    return (per + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
+}
+
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(Params p) {
@@ -48,8 +57,9 @@ attention_decode_kernel(Params p) {
     const int heads = min(16, kvh * group + group - h0);
     const int pos = p.positions[t];
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int key_begin = first + blockIdx.z * p.split_len;
-    const int key_end = min(pos + 1, key_begin + p.split_len);
+    const int split_len = range_length(p, pos + 1 - first);
+    const int key_begin = first + blockIdx.z * split_len;
+    const int key_end = min(pos + 1, key_begin + split_len);
     if (key_begin >= key_end) return;
     const int* table = p.block_table + (size_t)slot * p.table_stride;
 
@@ -231,7 +241,8 @@ __global__ void attention_merge_kernel(Params p) {
     const int h = blockIdx.y;
     const int pos = p.positions[t];
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int used = min(p.n_splits, (pos + 1 - first + p.split_len - 1) / p.split_len);
+    const int split_len = range_length(p, pos + 1 - first);
+    const int used = min(p.n_splits, (pos + 1 - first + split_len - 1) / split_len);
     const float* base = p.partial + ((size_t)t * p.nq + h) * p.n_splits * (D + 1);
     float top = -INFINITY;
     for (int s = 0; s < used; ++s) top = fmaxf(top, base[(size_t)s * (D + 1) + D]);
@@ -260,10 +271,10 @@ int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
     const int group = p.nq / p.nkv;
     dim3 grid(n_rows, p.nkv * ((group + 15) / 16), p.n_splits);
     attention_decode_kernel<D><<<grid, WARPS * 32, smem, stream>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return LIA_ERR_LAUNCH;
+    if (lia_check_launch() != LIA_OK) return LIA_ERR_LAUNCH;
     if (p.n_splits > 1) {
         attention_merge_kernel<D><<<dim3(n_rows, p.nq), D < 128 ? D : 128, 0, stream>>>(p);
-        if (cudaGetLastError() != cudaSuccess) return LIA_ERR_LAUNCH;
+        if (lia_check_launch() != LIA_OK) return LIA_ERR_LAUNCH;
     }
     return LIA_OK;
 }
@@ -276,14 +287,15 @@ LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, i
 
 // Decode attention for the tokens listed in `rows` (indices into the step's batch), bfloat16 only,
 // head_dim 32, 64 or 128 (other sizes: LIA_ERR_SIZE; the caller falls back to the generic kernel).
-// `n_splits` ranges of `split_len` keys each must cover the longest visible span among the rows.
+// `n_splits` ranges of `split_len` keys each must cover the longest visible span among the rows;
+// split_len 0 lets every row cut its own span into n_splits ranges (see range_length).
 LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* rows,
                                     int n_rows, const int* positions, const int* slots, const int* block_table,
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len <= 0 || split_len % TILE_KEYS || n_splits <= 0 ||
+    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
         return LIA_ERR_SIZE;
     if (n_splits > 1 && (!partial || partial_floats < lia_attention_decode_scratch_floats(n_tokens, nq, d, n_splits)))

@@ -24,7 +24,45 @@
 #define LIA_F32 0
 #define LIA_BF16 1
 
+// Kernels launched by this library since it was loaded (every launcher calls lia_check_launch once per
+// kernel).  Read through lia_kernel_launches(); a benchmark's own count of its launches.
+#include <atomic>
+inline std::atomic<long long> lia_launch_counter{0};
+
 static inline int lia_check_launch() {
+    lia_launch_counter.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
+}
+
+// Programmatic dependent launch.  A kernel launched through lia_launch may begin while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it touches anything that
+// kernel wrote or read (weights and other constants may be fetched earlier), and may call
+// pdl_launch_dependents() once it no longer matters when the next kernel starts.  Both are no-ops in
+// a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1: launches carry the programmatic-serialization attribute (default); 0: ordinary launches.
+inline std::atomic<int> lia_pdl_enabled{1};
+
+template <typename... KArgs, typename... Args>
+static inline int lia_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = lia_pdl_enabled.load(std::memory_order_relaxed) ? 1 : 0;
+    lia_launch_counter.fetch_add(1, std::memory_order_relaxed);
+    if (cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...) != cudaSuccess) {
+        cudaGetLastError();
+        return LIA_ERR_LAUNCH;
+    }
     return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
 }
 

@@ -1,26 +1,38 @@
-// Matrix product on the 5th-generation tensor cores (tcgen05), operands by TMA, accumulator in TMEM:
+// Matrix product on the 5th-generation tensor cores (tcgen05), operands by TMA, accumulators in TMEM:
 //     acc[t, f] = sum_k X[t, k] * W[f, k]       X [M, K] bf16 activations, W [N, K] bf16 weights
-// The weight rows are the MMA's M dimension (128 per CTA) and the tokens its N dimension (16..256),
-// so that one kernel serves a prompt portion of thousands of tokens and a decode batch of a few:
-// a small batch costs a narrow N, not a padded M.
+// The weight rows are the MMA's M dimension (128 per tile) and the tokens its N dimension (16..256), so
+// that one kernel serves a prompt portion of thousands of tokens and a decode batch of a few: a small
+// batch costs a narrow N, not a padded M.
 //
-// One CTA computes one tile [128 features x n_tile tokens] over a range of K:
-//   warp 0      allocates TMEM, then one lane issues the TMA loads: per 64-wide K block one box of W
-//               (two for the fused gate/up product) and one box of X, 128-byte swizzled, into a ring
-//               of shared-memory stages guarded by full/empty mbarriers;
-//   warp 1      one lane issues tcgen05.mma (M 128, N n_tile, K 16, four per stage) into TMEM and
-//               commits each stage's mbarrier when its operands have been read;
-//   warps 2..5  read the accumulator with tcgen05.ld (each warp its 32 TMEM lanes = 32 features) and
-//               apply the epilogue.  Lanes of a warp hold consecutive features of one token, so every
-//               store is a contiguous run of the output row.
+// The kernel is persistent: at most one CTA per SM, each walking a list of work units
+// (tile, K range) round-robin.  Inside a CTA the warps have fixed roles and never wait for one another
+// except through mbarriers:
+//   warp 0      one lane issues the TMA loads: per 64-wide K block one box of W (two for the fused
+//               gate/up product) and one box of X, 128-byte swizzled, into a ring of shared-memory
+//               stages.  The ring runs on across units, so the memory pipeline never drains.
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma (M 128, N n_tile, K 16, four per stage)
+//               into one of TWO accumulator buffers in TMEM and commits each stage's mbarrier when its
+//               operands have been read, and the buffer's mbarrier when the unit is complete.
+//   warps 2..5  the epilogue: they read a finished buffer with tcgen05.ld (each warp its 32 TMEM lanes
+//               = 32 features) while the MMA warp already fills the other buffer.
 // Epilogues: STORE out = alpha*acc; ACCUM out += alpha*acc (32-bit residual stream);
-// SWIGLU out = up * gate/(1+exp(-gate)) with gate and up accumulated side by side in TMEM;
-// PARTIAL: the raw accumulator of one K range goes to scratch [split][M][N] and a second kernel adds
-// the ranges in a fixed order and applies the epilogue.  Splitting K is how a decode batch, whose
-// products have few tiles, still puts a CTA on every SM and streams the weights at memory speed.
+// SWIGLU out = up * gate/(1+exp(-gate)) with gate and up accumulated side by side in TMEM.
+// With many tokens the tile goes through shared memory and leaves by TMA (bulk store, or bulk
+// reduce-add for ACCUM, which adds in L2 and never reads the old value into the SM); with few tokens it
+// is stored directly.
 //
-// Every wait on an mbarrier is bounded: when the bound is hit the kernel raises the error flag,
-// waits (bounded) for its TMA copies in flight, frees its TMEM and returns.
+// Few tokens mean few tiles, so K is cut into ranges to give every SM work (that is how a decode batch
+// streams the weights at memory speed).  Each unit then writes its raw accumulator to scratch
+// [range][M][n_total] and bumps its tile's counter; the CTA that arrives last adds the ranges in
+// ascending order (so the sum does not depend on who was last), applies the epilogue and puts the
+// counter back to zero.  No CTA ever waits for another one.
+//
+// The kernel is launched with programmatic dependent launch: it may start while the kernel before it
+// in the stream is still draining.  Weights do not depend on that kernel, so the first ring of W boxes
+// is requested at once; everything else waits at griddepcontrol.wait.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the role raises the error flag and leaves
+// its loop; the CTA then waits (bounded) for its copies in flight, frees its TMEM and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -28,15 +40,16 @@
 #define GEMM_STORE 0
 #define GEMM_ACCUM 1
 #define GEMM_SWIGLU 2
-#define GEMM_PARTIAL 3
 
 namespace {
 constexpr int BLOCK_K = 64;          // bf16 elements per K block: 128 bytes, one swizzle row
-constexpr int TILE_F = 128;          // features per CTA: the MMA's M
+constexpr int TILE_F = 128;          // features per tile: the MMA's M
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;      // polls of mbarrier.try_wait (each suspends up to ~1 us)
-constexpr int MAX_STAGES = 8;
-constexpr int SMEM_LIMIT = 200 * 1024;
+constexpr int MAX_STAGES = 12;
+constexpr int SMEM_BYTES = 226 * 1024;         // dynamic shared memory asked for (a CTA may have 227 KB; 1 KB is static)
+constexpr int STAGING_TOKENS = 32;             // tokens per TMA store of the epilogue
+constexpr int COUNTER_WORDS = 4096;            // tile counters at the head of the scratch
 
 // ---- PTX wrappers ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -46,6 +59,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
@@ -67,6 +83,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -81,6 +112,7 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// 16 consecutive columns of this warp's 32 TMEM lanes: thread = lane (feature), v[c] = column (token).
 __device__ __forceinline__ void tmem_load16(uint32_t addr, float* v) {
     uint32_t r[16];
     asm volatile(
@@ -113,44 +145,80 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n) {
 
 struct Shape {
     int M, N, K;              // tokens, output features (per half for SWIGLU), reduction length
-    int n_tile;               // tokens per CTA: 16..256, a multiple of 16
+    int n_total;              // rows of W: N, or 2N for SWIGLU
+    int n_tile;               // tokens per tile: 16..256, a multiple of 16
     int stages;
     int kblocks;              // ceil(K / 64)
-    int kblocks_per_split;
-    int up_row_offset;        // SWIGLU: row of W where the up half starts
-    int tmem_cols;
+    int splits;               // K ranges per tile
+    int f_tiles, t_tiles;
+    int acc_cols;             // TMEM columns of one accumulator buffer
+    int tmem_cols;            // TMEM columns allocated (both buffers, a power of two >= 32)
+    int via_tma;              // 1: the epilogue leaves through shared memory and TMA
+    int ldo;
+    float alpha;
+    float* partial;           // [splits][M][n_total]
+    int* counters;            // [f_tiles * t_tiles], zero between launches
+    int* error_flag;
 };
+
+// The k-th unit of this CTA: which tile, which K blocks.
+struct Unit {
+    int f0, t0, tile, split, kb_begin, kb_end;
+};
+__device__ __forceinline__ Unit unit_at(const Shape& s, int index) {
+    Unit u;
+    u.tile = index / s.splits;
+    u.split = index - u.tile * s.splits;
+    const int ft = u.tile % s.f_tiles, tt = u.tile / s.f_tiles;
+    u.f0 = ft * TILE_F;
+    u.t0 = tt * s.n_tile;
+    u.kb_begin = (int)((long long)u.split * s.kblocks / s.splits);
+    u.kb_end = (int)((long long)(u.split + 1) * s.kblocks / s.splits);
+    return u;
+}
+
+template <int MODE, typename TO>
+__device__ __forceinline__ void apply_epilogue(TO* dst, float acc, float up, float alpha) {
+    if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc);
+    else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc);
+    else *dst = from_float<TO>(up * (acc / (1.0f + __expf(-acc))));
+}
 
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TO* __restrict__ out, int ldo, Shape s, float alpha, int* __restrict__ error_flag) {
+               const __grid_constant__ CUtensorMap map_o, TO* __restrict__ out, Shape s) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_bar;
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
+    __shared__ int last_flag;
 
     constexpr int A_TILES = (MODE == GEMM_SWIGLU) ? 2 : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * TILE_F, t0 = blockIdx.y * s.n_tile;
-    const int kb_begin = blockIdx.z * s.kblocks_per_split;
-    const int kb_end = min(s.kblocks, kb_begin + s.kblocks_per_split);
-    const int iterations = kb_end - kb_begin;
     const uint32_t a_bytes = TILE_F * BLOCK_K * 2, b_bytes = (uint32_t)s.n_tile * BLOCK_K * 2;
     const uint32_t stage_bytes = A_TILES * a_bytes + b_bytes;
     // dynamic shared memory is aligned to 1024 bytes by hand (the swizzle pattern repeats every 1024)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t staging_base = smem_base + (uint32_t)s.stages * stage_bytes;     // 2 x [32 tokens][128 features]
+    const int units = s.f_tiles * s.t_tiles * s.splits;
+    const int first_unit = blockIdx.x, stride = gridDim.x;
 
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int i = 0; i < s.stages; ++i) {
-                mbar_init(smem_u32(&full_bar[i]), 1);
-                mbar_init(smem_u32(&empty_bar[i]), 1);
-            }
-            mbar_init(smem_u32(&acc_bar), 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < s.stages; ++i) {
+            mbar_init(smem_u32(&full_bar[i]), 1);
+            mbar_init(smem_u32(&empty_bar[i]), 1);
         }
-        __syncwarp();
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&acc_full[i]), 1);
+            mbar_init(smem_u32(&acc_empty[i]), 4);         // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (s.via_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_o) : "memory");
+    }
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                      "r"((uint32_t)s.tmem_cols)
                      : "memory");
@@ -160,115 +228,231 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    pdl_launch_dependents();
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        int issued = 0;
+        // The first ring of W boxes is asked for before the kernel ahead of this one has finished: the
+        // weights do not depend on it.  X does, so its boxes wait.
         bool ok = true;
-        for (int it = 0; it < iterations; ++it) {
-            const int st = it % s.stages;
-            const uint32_t phase = (uint32_t)(it / s.stages) & 1u;
-            if (!mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u)) { ok = false; break; }
-            const uint32_t full = smem_u32(&full_bar[st]);
-            const uint32_t dst = smem_base + (uint32_t)st * stage_bytes;
-            const int k = (kb_begin + it) * BLOCK_K;
-            mbar_expect_tx(full, stage_bytes);
-            tma_load_2d(dst, &map_w, k, f0, full);
-            if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, k, s.up_row_offset + f0, full);
-            tma_load_2d(dst + A_TILES * a_bytes, &map_x, k, t0, full);
-            issued = it + 1;
+        int issued = 0, ahead = 0;
+        {
+            int it = 0;
+            for (int index = first_unit; index < units && it < s.stages; index += stride) {
+                const Unit u = unit_at(s, index);
+                for (int kb = u.kb_begin; kb < u.kb_end && it < s.stages; ++kb, ++it) {
+                    const uint32_t full = smem_u32(&full_bar[it]);
+                    const uint32_t dst = smem_base + (uint32_t)it * stage_bytes;
+                    mbar_expect_tx(full, stage_bytes);
+                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
+                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
+                }
+            }
+            ahead = it;
+        }
+        pdl_wait();
+        int it = 0;
+        for (int index = first_unit; index < units && ok; index += stride) {
+            const Unit u = unit_at(s, index);
+            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
+                const int st = it % s.stages;
+                const uint32_t full = smem_u32(&full_bar[st]);
+                const uint32_t dst = smem_base + (uint32_t)st * stage_bytes;
+                if (it >= ahead) {
+                    const uint32_t phase = (uint32_t)(it / s.stages) & 1u;
+                    if (!mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u)) { ok = false; break; }
+                    mbar_expect_tx(full, stage_bytes);
+                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
+                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
+                }
+                tma_load_2d(dst + A_TILES * a_bytes, &map_x, kb * BLOCK_K, u.t0, full);
+                issued = it + 1;
+            }
         }
         if (!ok) {
-            if (error_flag) atomicExch(error_flag, 3);
+            if (s.error_flag) atomicExch(s.error_flag, 3);
             // wait, bounded, for the copies that were issued and may still be in flight
-            for (int it = max(0, issued - s.stages); it < issued; ++it)
-                mbar_wait(smem_u32(&full_bar[it % s.stages]), (uint32_t)(it / s.stages) & 1u);
+            for (int i = max(0, issued - s.stages); i < issued; ++i)
+                mbar_wait(smem_u32(&full_bar[i % s.stages]), (uint32_t)(i / s.stages) & 1u);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         const uint32_t idesc = instr_desc(TILE_F, s.n_tile);
         bool ok = true;
-        for (int it = 0; it < iterations; ++it) {
-            const int st = it % s.stages;
-            const uint32_t phase = (uint32_t)(it / s.stages) & 1u;
-            if (!mbar_wait(smem_u32(&full_bar[st]), phase)) { ok = false; break; }
+        int it = 0, n_unit = 0;
+        for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
+            const Unit u = unit_at(s, index);
+            const int buf = n_unit & 1;
+            if (!mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)n_unit >> 1) & 1u) ^ 1u)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
-            const uint32_t b_addr = a_addr + A_TILES * a_bytes;
+            const uint32_t acc = tmem_base + (uint32_t)(buf * s.acc_cols);
+            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
+                const int st = it % s.stages;
+                if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
+                const uint32_t b_addr = a_addr + A_TILES * a_bytes;
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / 16; ++k) {
-                const uint64_t db = smem_desc(b_addr + k * 32);
-                const uint32_t accumulate = (it > 0 || k > 0) ? 1u : 0u;
-                tc_mma(tmem_base, smem_desc(a_addr + k * 32), db, idesc, accumulate);
-                if (A_TILES == 2) tc_mma(tmem_base + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                for (int k = 0; k < BLOCK_K / 16; ++k) {
+                    const uint64_t db = smem_desc(b_addr + k * 32);
+                    const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
+                    tc_mma(acc, smem_desc(a_addr + k * 32), db, idesc, accumulate);
+                    if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                }
+                tc_commit(smem_u32(&empty_bar[st]));      // the stage is free when these MMAs have read it
             }
-            tc_commit(smem_u32(&empty_bar[st]));      // the stage is free when these MMAs have read it
+            if (ok) tc_commit(smem_u32(&acc_full[buf]));  // the accumulator is complete
         }
-        if (ok) tc_commit(smem_u32(&acc_bar));        // the accumulator is complete
-        else if (error_flag) atomicExch(error_flag, 3);
+        if (!ok && s.error_flag) atomicExch(s.error_flag, 3);
     } else if (warp >= 2) {
         // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 ----
         const int group = warp & 3;
-        const int f = f0 + group * 32 + lane;
-        bool ok = iterations > 0 ? mbar_wait(smem_u32(&acc_bar), 0) : true;
-        if (!ok && lane == 0 && error_flag) atomicExch(error_flag, 3);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(group * 32) << 16);
-            for (int c0 = 0; c0 < s.n_tile; c0 += 16) {
-                if (t0 + c0 >= s.M) break;                    // uniform over the warp
-                float acc[16], up[16];
-                if (iterations > 0) {
+        const int epi_thread = threadIdx.x - 64;          // 0..127
+        pdl_wait();
+        bool ok = true;
+        int n_unit = 0, chunk_count = 0;
+        for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
+            const Unit u = unit_at(s, index);
+            const int buf = n_unit & 1;
+            const int f = u.f0 + group * 32 + lane;
+            const bool empty_range = u.kb_end <= u.kb_begin;           // cannot happen (splits <= kblocks)
+            if (!empty_range && !mbar_wait(smem_u32(&acc_full[buf]), ((uint32_t)n_unit >> 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(group * 32) << 16) + (uint32_t)(buf * s.acc_cols);
+
+            if (s.splits > 1) {
+                // raw accumulator to scratch [split][t][n_total]
+                float* plane = s.partial + (size_t)u.split * s.M * s.n_total;
+                for (int c0 = 0; c0 < s.n_tile; c0 += 16) {
+                    if (u.t0 + c0 >= s.M) break;
+                    float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
-                } else {
+                    if (f < s.N) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) acc[c] = up[c] = 0.f;
-                }
-                if (f < s.N) {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int t = t0 + c0 + c;
-                        if (t >= s.M) break;
-                        if (MODE == GEMM_PARTIAL) {
-                            out[((size_t)blockIdx.z * s.M + t) * (size_t)ldo + f] = from_float<TO>(acc[c]);
-                        } else {
-                            TO* dst = out + (size_t)t * ldo + f;
-                            if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc[c]);
-                            else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc[c]);
-                            else *dst = from_float<TO>(up[c] * (acc[c] / (1.0f + __expf(-acc[c]))));
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = u.t0 + c0 + c;
+                            if (t >= s.M) break;
+                            plane[(size_t)t * s.n_total + f] = acc[c];
+                            if (MODE == GEMM_SWIGLU) plane[(size_t)t * s.n_total + s.N + f] = up[c];
                         }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+                // the last unit of the tile to arrive adds the ranges in ascending order
+                __threadfence();
+                epilogue_sync();
+                if (epi_thread == 0) {
+                    const int seen = atomicAdd(&s.counters[u.tile], 1);
+                    last_flag = (seen == s.splits - 1);
+                    if (seen == s.splits - 1) s.counters[u.tile] = 0;
+                }
+                epilogue_sync();
+                if (last_flag) {
+                    __threadfence();
+                    if (f < s.N) {
+                        const int rows = min(s.n_tile, s.M - u.t0);
+                        for (int c0 = 0; c0 < rows; c0 += 8) {
+                            float acc[8], up[8];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) acc[c] = up[c] = 0.f;
+                            // four ranges at a time: all their loads are in flight before the first sum
+                            for (int sp0 = 0; sp0 < s.splits; sp0 += 4) {
+                                float v[4][8], w[4][8];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float* src = s.partial + ((size_t)(sp0 + j) * s.M + u.t0 + c0) * s.n_total + f;
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c) {
+                                        const bool there = sp0 + j < s.splits && c0 + c < rows;
+                                        v[j][c] = there ? __ldcg(src + (size_t)c * s.n_total) : 0.f;
+                                        if (MODE == GEMM_SWIGLU) w[j][c] = there ? __ldcg(src + (size_t)c * s.n_total + s.N) : 0.f;
+                                    }
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c) {
+                                        acc[c] += v[j][c];
+                                        if (MODE == GEMM_SWIGLU) up[c] += w[j][c];
+                                    }
+                            }
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                if (c0 + c < rows)
+                                    apply_epilogue<MODE, TO>(out + (size_t)(u.t0 + c0 + c) * s.ldo + f, acc[c], up[c], s.alpha);
+                        }
+                    }
+                }
+                epilogue_sync();      // last_flag is read by all before the next unit rewrites it
+            } else if (s.via_tma) {
+                // through shared memory, 32 tokens at a time, out by TMA
+                for (int c0 = 0; c0 < s.n_tile; c0 += STAGING_TOKENS) {
+                    if (u.t0 + c0 >= s.M) break;
+                    float acc[32], up[32];
+                    tmem_load16(lane_addr + (uint32_t)c0, acc);
+                    tmem_load16(lane_addr + (uint32_t)(c0 + 16), acc + 16);
+                    if (MODE == GEMM_SWIGLU) {
+                        tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                        tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0 + 16), up + 16);
+                    }
+                    const int sbuf = chunk_count & 1;
+                    ++chunk_count;
+                    // the store that last read this staging buffer must be done reading it
+                    if (epi_thread == 0) tma_wait_read<1>();
+                    epilogue_sync();
+                    TO* stage = reinterpret_cast<TO*>(smem_raw + (staging_base - smem_u32(smem_raw))) +
+                                (size_t)sbuf * STAGING_TOKENS * TILE_F;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        float v;
+                        if (MODE == GEMM_SWIGLU) v = up[c] * (acc[c] / (1.0f + __expf(-acc[c])));
+                        else v = s.alpha * acc[c];
+                        stage[c * TILE_F + group * 32 + lane] = from_float<TO>(v);
+                    }
+                    fence_async_smem();
+                    epilogue_sync();
+                    if (epi_thread == 0) {
+                        const uint32_t src = staging_base + (uint32_t)(sbuf * STAGING_TOKENS * TILE_F * sizeof(TO));
+                        if (MODE == GEMM_ACCUM) tma_reduce_add_2d(&map_o, src, u.f0, u.t0 + c0);
+                        else tma_store_2d(&map_o, src, u.f0, u.t0 + c0);
+                        tma_commit_group();
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+            } else {
+                for (int c0 = 0; c0 < s.n_tile; c0 += 16) {
+                    if (u.t0 + c0 >= s.M) break;                    // uniform over the warp
+                    float acc[16], up[16];
+                    tmem_load16(lane_addr + (uint32_t)c0, acc);
+                    if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                    if (f < s.N) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = u.t0 + c0 + c;
+                            if (t >= s.M) break;
+                            apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
             }
         }
+        if (!ok && lane == 0 && s.error_flag) atomicExch(s.error_flag, 3);
+        if (s.via_tma && epi_thread == 0) tma_wait_all();     // shared memory must outlive the stores that read it
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)s.tmem_cols) : "memory");
     }
-}
-
-// Adds the K ranges in ascending order and applies the epilogue.  partial [splits][M][n_total].
-template <int MODE, typename TO>
-__global__ void splitk_epilogue_kernel(const float* __restrict__ partial, int splits, int M, int n_total, int N,
-                                       TO* __restrict__ out, int ldo, float alpha) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)M * N) return;
-    const int t = (int)(i / N), f = (int)(i % N);
-    const size_t plane = (size_t)M * n_total;
-    float acc = 0.f, up = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-        const float* row = partial + sp * plane + (size_t)t * n_total;
-        acc += row[f];
-        if (MODE == GEMM_SWIGLU) up += row[N + f];
-    }
-    TO* dst = out + (size_t)t * ldo + f;
-    if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc);
-    else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc);
-    else *dst = from_float<TO>(up * (acc / (1.0f + __expf(-acc))));
 }
 
 // ---- host side ----
@@ -306,11 +490,20 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int
     return r == CUDA_SUCCESS ? LIA_OK : LIA_ERR_DRIVER;
 }
 
-int pick_n_tile(int M, bool swiglu_fused) {
-    const int cap = swiglu_fused ? 128 : 256;      // two accumulators side by side must fit 512 columns and the ring
-    int n = 16;
-    while (n < M && n < cap) n *= 2;
-    return n;
+// The output [M, N] (row stride ldo elements) for the epilogue's stores: boxes of [32 tokens, 128 features],
+// no swizzle; what lies outside the matrix is not written.
+int make_out_map(CUtensorMap* map, void* base, int out_dtype, int M, int N, int ldo) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return LIA_ERR_DRIVER;
+    const int esize = out_dtype == LIA_F32 ? 4 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)ldo * esize};
+    cuuint32_t box[2] = {TILE_F, STAGING_TOKENS};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, out_dtype == LIA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                    dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LIA_OK : LIA_ERR_DRIVER;
 }
 
 int pow2_at_least(int x) {
@@ -319,88 +512,112 @@ int pow2_at_least(int x) {
     return p;
 }
 
-template <int MODE, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, TO* out, int ldo, const Shape& s, float alpha, int splits,
-           int* error_flag, cudaStream_t stream) {
-    const int a_tiles = MODE == GEMM_SWIGLU ? 2 : 1;
-    const size_t smem = (size_t)s.stages * (a_tiles * TILE_F * BLOCK_K * 2 + s.n_tile * BLOCK_K * 2) + 1024;
-    static size_t configured = 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT + 1024) != cudaSuccess)
-            return LIA_ERR_LAUNCH;
-        configured = SMEM_LIMIT + 1024;
+// How the product is cut: tokens per tile, K ranges per tile.  A function of the sizes and of the SM
+// count alone, so the same product is always cut the same way.
+struct Plan {
+    int n_tile, splits, f_tiles, t_tiles;
+};
+
+Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_floats) {
+    const bool swiglu = mode == GEMM_SWIGLU;
+    const int n_total = swiglu ? 2 * N : N;
+    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    Plan p;
+    p.f_tiles = (N + TILE_F - 1) / TILE_F;
+    const int cap = swiglu ? 128 : 256;          // two accumulators side by side, twice, must fit 512 columns
+    if (M <= cap / 2 || swiglu) {
+        p.n_tile = 16;
+        while (p.n_tile < M && p.n_tile < cap) p.n_tile *= 2;
+    } else {
+        // many tokens: 256 or 128 per tile, whichever leaves the SMs less idle in the last round
+        long long best = -1;
+        p.n_tile = 256;
+        for (int n = 256; n >= 128; n /= 2) {
+            const long long tiles = (long long)p.f_tiles * ((M + n - 1) / n);
+            const long long rounds = (tiles + sm_count - 1) / sm_count;
+            const long long cost = rounds * (n + 24);                   // + a tile's fixed cost
+            if (best < 0 || cost < best) { best = cost; p.n_tile = n; }
+        }
     }
-    dim3 grid((s.N + TILE_F - 1) / TILE_F, (s.M + s.n_tile - 1) / s.n_tile, splits);
-    gemm_tc_kernel<MODE, TO><<<grid, THREADS, smem, stream>>>(mw, mx, out, ldo, s, alpha, error_flag);
-    return lia_check_launch();
+    p.t_tiles = (M + p.n_tile - 1) / p.n_tile;
+    p.splits = 1;
+    const long long tiles = (long long)p.f_tiles * p.t_tiles;
+    if (tiles < sm_count && tiles <= COUNTER_WORDS && scratch_floats > COUNTER_WORDS) {
+        // cost in K-block times of the longest CTA: rounds * (blocks per range + fixed) + the last arriver's sum
+        double best = 0;
+        for (int sp = 1; sp <= kblocks && sp <= 32; ++sp) {
+            if (sp > 1 && (long long)sp * M * n_total > scratch_floats - COUNTER_WORDS) break;
+            const long long rounds = (tiles * sp + sm_count - 1) / sm_count;
+            const double cost = rounds * ((kblocks + sp - 1) / sp + 2.0) + (sp > 1 ? 1.0 + 0.25 * sp : 0.0);
+            if (sp == 1 || cost < best) { best = cost; p.splits = sp; }
+        }
+    }
+    return p;
+}
+
+template <int MODE, typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, TO* out, const Shape& s, int grid,
+           cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<MODE, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+            return LIA_ERR_LAUNCH;
+        configured = true;
+    }
+    return lia_launch(gemm_tc_kernel<MODE, TO>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, mw, mx, mo, out, s);
 }
 }  // namespace
 
 // mode: GEMM_STORE | GEMM_ACCUM | GEMM_SWIGLU.  X [M, K] bf16 (row stride ldx), W [N, K] (SWIGLU: [2N, K],
 // gate rows then up rows) bf16 (row stride ldw), out [M, N] f32 or bf16 (row stride ldo).
-// `scratch` (32-bit, `scratch_floats` long) is used when K is split; `sm_count` is the number of SMs to fill.
+// `scratch` (32-bit words, `scratch_floats` long) is used when K is split: its first 4096 words are tile
+// counters that must be zero before the first call and are zero again after every call; the rest holds
+// partial sums.  `sm_count` is the number of SMs to fill.
 // Refuses (LIA_ERR_SIZE / LIA_ERR_ALIGN) what it cannot compute: K or a row stride that is not a multiple
 // of 8 elements, pointers that are not 16-byte aligned.
 LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                            int ldo, int M, int N, int K, float alpha, float* scratch, long long scratch_floats,
                            int sm_count, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LIA_OK;
-    if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N) return LIA_ERR_SIZE;
+    if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N || sm_count <= 0) return LIA_ERR_SIZE;
     if (mode != GEMM_STORE && mode != GEMM_ACCUM && mode != GEMM_SWIGLU) return LIA_ERR_SIZE;
     if (mode == GEMM_ACCUM && out_dtype != LIA_F32) return LIA_ERR_DTYPE;
     if (out_dtype != LIA_F32 && out_dtype != LIA_BF16) return LIA_ERR_DTYPE;
     const bool swiglu = mode == GEMM_SWIGLU;
-    const int n_total = swiglu ? 2 * N : N;
-    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const Plan plan = make_plan(mode, M, N, K, sm_count, scratch ? scratch_floats : 0);
 
-    // How many K ranges: enough CTAs to fill the SMs when the product has few tiles.
-    int n_tile = pick_n_tile(M, false);
-    const long long tiles = (long long)((n_total + TILE_F - 1) / TILE_F) * ((M + n_tile - 1) / n_tile);
-    int splits = 1;
-    if (tiles < sm_count && M <= 256 && scratch) {
-        splits = (int)min((long long)16, (2LL * sm_count + tiles - 1) / tiles);
-        splits = min(splits, max(1, kblocks / 4));               // at least 4 K blocks per range
-        while (splits > 1 && (long long)splits * M * n_total > scratch_floats) --splits;
-    }
     Shape s;
-    s.M = M; s.K = K; s.kblocks = kblocks; s.up_row_offset = N;
-    CUtensorMap mw, mx;
+    s.M = M; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
+    s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
+    s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    s.acc_cols = swiglu ? 2 * plan.n_tile : plan.n_tile;
+    s.tmem_cols = pow2_at_least(2 * s.acc_cols);
+    s.ldo = ldo; s.alpha = alpha; s.error_flag = error_flag;
+    s.counters = reinterpret_cast<int*>(scratch);
+    s.partial = scratch ? scratch + COUNTER_WORDS : nullptr;
+    const int esize = out_dtype == LIA_F32 ? 4 : 2;
+    // the epilogue leaves by TMA when there are enough tokens to make it worth it and the output can be addressed
+    s.via_tma = (plan.splits == 1 && M >= 64 && ((uintptr_t)out & 15u) == 0 && ((long long)ldo * esize) % 16 == 0) ? 1 : 0;
+    const int staging = s.via_tma ? 2 * STAGING_TOKENS * TILE_F * esize : 0;
+    const int stage_bytes = (swiglu ? 2 : 1) * TILE_F * BLOCK_K * 2 + plan.n_tile * BLOCK_K * 2;
+    s.stages = max(2, min(MAX_STAGES, (SMEM_BYTES - 1024 - staging) / stage_bytes));
+
+    CUtensorMap mw, mx, mo;
     int rc;
-    if (splits > 1) {
-        s.N = n_total; s.n_tile = n_tile;
-        s.kblocks_per_split = (kblocks + splits - 1) / splits;
-        splits = (kblocks + s.kblocks_per_split - 1) / s.kblocks_per_split;
-        s.tmem_cols = pow2_at_least(n_tile);
-        const int stage_bytes = TILE_F * BLOCK_K * 2 + n_tile * BLOCK_K * 2;
-        s.stages = max(2, min(MAX_STAGES, SMEM_LIMIT / stage_bytes));
-        if ((rc = make_map(&mw, W, n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
-        if ((rc = make_map(&mx, X, M, K, ldx, n_tile)) != LIA_OK) return rc;
-        rc = launch<GEMM_PARTIAL, float>(mw, mx, scratch, n_total, s, 1.0f, splits, error_flag, stream);
-        if (rc != LIA_OK) return rc;
-        const size_t count = (size_t)M * N;
-        const int threads = 256;
-        const unsigned blocks = (unsigned)((count + threads - 1) / threads);
-#define LIA_EPI(MODE, TO) splitk_epilogue_kernel<MODE, TO><<<blocks, threads, 0, stream>>>(scratch, splits, M, n_total, N, (TO*)out, ldo, alpha)
-        if (mode == GEMM_STORE && out_dtype == LIA_F32) LIA_EPI(GEMM_STORE, float);
-        else if (mode == GEMM_STORE) LIA_EPI(GEMM_STORE, __nv_bfloat16);
-        else if (mode == GEMM_ACCUM) LIA_EPI(GEMM_ACCUM, float);
-        else if (out_dtype == LIA_F32) LIA_EPI(GEMM_SWIGLU, float);
-        else LIA_EPI(GEMM_SWIGLU, __nv_bfloat16);
-#undef LIA_EPI
-        return lia_check_launch();
+    if ((rc = make_map(&mw, W, s.n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
+    if ((rc = make_map(&mx, X, M, K, ldx, plan.n_tile)) != LIA_OK) return rc;
+    if (s.via_tma) {
+        if ((rc = make_out_map(&mo, out, out_dtype, M, N, ldo)) != LIA_OK) return rc;
+    } else {
+        mo = mx;
     }
-    n_tile = pick_n_tile(M, swiglu);
-    s.N = N; s.n_tile = n_tile; s.kblocks_per_split = kblocks;
-    s.tmem_cols = pow2_at_least(swiglu ? 2 * n_tile : n_tile);
-    const int stage_bytes = (swiglu ? 2 : 1) * TILE_F * BLOCK_K * 2 + n_tile * BLOCK_K * 2;
-    s.stages = max(2, min(MAX_STAGES, SMEM_LIMIT / stage_bytes));
-    if ((rc = make_map(&mw, W, n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
-    if ((rc = make_map(&mx, X, M, K, ldx, n_tile)) != LIA_OK) return rc;
-    if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, (float*)out, ldo, s, alpha, 1, error_flag, stream);
-    if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, (__nv_bfloat16*)out, ldo, s, alpha, 1, error_flag, stream);
-    if (mode == GEMM_ACCUM) return launch<GEMM_ACCUM, float>(mw, mx, (float*)out, ldo, s, alpha, 1, error_flag, stream);
-    if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, (float*)out, ldo, s, alpha, 1, error_flag, stream);
-    return launch<GEMM_SWIGLU, __nv_bfloat16>(mw, mx, (__nv_bfloat16*)out, ldo, s, alpha, 1, error_flag, stream);
+    const long long units = (long long)plan.f_tiles * plan.t_tiles * plan.splits;
+    const int grid = (int)min((long long)sm_count, units);
+    if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+    if (mode == GEMM_ACCUM) return launch<GEMM_ACCUM, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    return launch<GEMM_SWIGLU, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -413,6 +630,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
 namespace {
 constexpr long long NOALLOC_FLOATS = LIA_GEMM_NOALLOC_SCRATCH_BYTES / sizeof(float);
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+// Zero when the library is loaded, which is what the tile counters at its head need.
 static __device__ __align__(256) float noalloc_scratch[NOALLOC_FLOATS];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
@@ -437,19 +655,12 @@ int noalloc_scratch_address(float** address) {
 }
 }  // namespace
 
-// The split plan lia_gemm_tc makes when its scratch is large enough, restated so that the need is known
-// before anything is launched.
+// Words of scratch the product of these sizes uses when nothing limits it (0: it does not split K).
 LIA_EXPORT long long lia_gemm_tc_noalloc_scratch_floats(int mode, int M, int N, int K, int sm_count) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
-    const int n_total = mode == GEMM_SWIGLU ? 2 * N : N;
-    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-    const int n_tile = pick_n_tile(M, false);
-    const long long tiles = (long long)((n_total + TILE_F - 1) / TILE_F) * ((M + n_tile - 1) / n_tile);
-    if (!(tiles < sm_count && M <= 256)) return 0;
-    int splits = (int)min((long long)16, (2LL * sm_count + tiles - 1) / tiles);
-    splits = min(splits, max(1, kblocks / 4));
-    if (splits <= 1) return 0;
-    return (long long)splits * M * n_total;
+    if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return 0;
+    const Plan plan = make_plan(mode, M, N, K, sm_count, 1LL << 60);
+    if (plan.splits <= 1) return 0;
+    return (long long)plan.splits * M * (mode == GEMM_SWIGLU ? 2 * N : N) + COUNTER_WORDS;
 }
 
 LIA_EXPORT int lia_gemm_tc_noalloc(int mode, const void* X, int ldx, const void* W, int ldw, void* out,

@@ -19,12 +19,16 @@
 //    looks up the array's device address with cudaGetSymbolAddress while that device is current and keeps
 //    it; make that first call before any stream capture begins, because the lookup may load the module.
 //  * A product whose split-K partial sums would not fit the array is refused with LIA_ERR_SCRATCH (-6)
-//    and nothing is launched.  The need is splits * M * n_total floats, n_total = N (2N for SWIGLU);
-//    lia_gemm_tc_noalloc_scratch_floats() returns it for given sizes so a caller can ask beforehand.
-//    Products that need no split (many tokens, or enough tiles to fill the SMs) use no scratch.
-//  * All calls share the one array of a device, and it keeps what the last call left there.  Nothing in
-//    it has to start at zero: every partial sum that is read was written by the same call first.  Two
-//    calls that overlap on one GPU (different streams, or different threads) race on it: keep calls to
+//    and nothing is launched.  The need is 4096 words of tile counters + splits * M * n_total floats,
+//    n_total = N (2N for SWIGLU); lia_gemm_tc_noalloc_scratch_floats() returns it for given sizes so a
+//    caller can ask beforehand.  Products that need no split (many tokens, or enough tiles to fill the
+//    SMs) use no scratch.
+//  * All calls share the one array of a device, and it keeps what the last call left there.  Partial
+//    sums need no clearing: every one that is read was written by the same call first.  The tile
+//    counters at the head of the array must be zero when a call starts: they are zero when the library
+//    is loaded, and the kernel itself puts each one back to zero when the last K range of its tile has
+//    arrived, so a call that ran to its end leaves them ready for the next.  Two calls that overlap on
+//    one GPU (different streams, or different threads) race on counters and sums alike: keep calls to
 //    this entry point on one device in one stream order.
 //  * Return codes are those of lia_gemm_tc (0 = launched) plus LIA_ERR_SCRATCH.
 #pragma once

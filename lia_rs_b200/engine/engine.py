@@ -27,11 +27,12 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
-                 max_context: int = None, _random=None):
+                 max_context: int = None, cuda_graphs: bool = True, _random=None):
         """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
         `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
         `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
-        request (default: the model's max_position_embeddings)."""
+        request (default: the model's max_position_embeddings); `cuda_graphs`: capture decode steps
+        (every entry a single token) in CUDA graphs, one per batch size, and replay them."""
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be one of {sorted(_DTYPES)}")
         if not torch.cuda.is_available():
@@ -62,7 +63,9 @@ class Engine:
                                   self.page_size, self.max_seqs, self.max_context, self.runtime.compute_dtype,
                                   self.device)
         self.runtime_step = StepRuntime(self.cache, self.spec.vocab_size, self.max_batch_tokens, self.device)
-        self.stats = {"steps": 0, "tokens": 0}
+        self.stats = {"steps": 0, "tokens": 0, "kernels": 0, "graph_replays": 0}
+        self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
+        self._graphs = {}              # (tokens, wanted) -> None (seen once) | (graph, logits, kernels, generation)
 
     @classmethod
     def random(cls, config, seed: int = 0, **options) -> "Engine":
@@ -103,10 +106,43 @@ class Engine:
             return self.runtime_step.logits(0, self.spec.vocab_size)
         with torch.cuda.device(self.device):
             ctx = self.runtime_step.begin(entries)
-            logits = self.model.forward(ctx)
+            if self.cuda_graphs and ctx.decode_only:
+                logits = self._replay(ctx)
+            else:
+                logits = self._launch(ctx)
             self.runtime_step.finish()
         self.stats["steps"] += 1
         self.stats["tokens"] += ctx.n_tokens
+        return logits
+
+    def _launch(self, ctx) -> torch.Tensor:
+        before = ops.kernel_launches()
+        logits = self.model.forward(ctx)
+        self.stats["kernels"] += ops.kernel_launches() - before
+        return logits
+
+    def _replay(self, ctx) -> torch.Tensor:
+        """A decode step through its CUDA graph.  The step's metadata (token ids, positions, slots,
+        wanted rows) and the block tables already lie in fixed device buffers, so a graph captured for
+        (tokens, wanted) serves every later step of that shape.  The first step of a shape runs launch
+        by launch (it allocates the workspace); the second is captured; a reallocation of any buffer
+        makes the captured graphs stale."""
+        key = (ctx.n_tokens, ctx.n_out)
+        entry = self._graphs.get(key, False)
+        if entry is False:
+            self._graphs[key] = None
+            return self._launch(ctx)
+        if entry is None or entry[3] != self.runtime_step.generation:
+            graph = torch.cuda.CUDAGraph()
+            before = ops.kernel_launches()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            entry = (graph, logits, ops.kernel_launches() - before, self.runtime_step.generation)
+            self._graphs[key] = entry
+        graph, logits, kernels, _ = entry
+        graph.replay()
+        self.stats["kernels"] += kernels
+        self.stats["graph_replays"] += 1
         return logits
 
     # ---- token selection ----

@@ -85,6 +85,7 @@ class StepRuntime:
         self._copy_event = torch.cuda.Event()
         self._buffers = {}
         self._logits_buffer = None
+        self.generation = 0            # grows whenever a buffer is (re)allocated: captured graphs are stale then
 
     # ---- memory ----
     def workspace(self, name, shape, dtype):
@@ -94,6 +95,7 @@ class StepRuntime:
         if buf is None or buf.shape[0] < rows:
             buf = torch.empty((max(rows, self.max_batch_tokens), width), dtype=dtype, device=self.device)
             self._buffers[key] = buf
+            self.generation += 1
         return buf[:rows]
 
     def scratch(self, name, numel, dtype):
@@ -102,6 +104,7 @@ class StepRuntime:
         if buf is None or buf.numel() < numel:
             buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._buffers[(name, dtype)] = buf
+            self.generation += 1
         return buf[:numel]
 
     def logits(self, rows, vocab):
@@ -109,6 +112,7 @@ class StepRuntime:
         if buf is None or buf.shape[0] < rows or buf.shape[1] != vocab:
             buf = torch.empty((max(rows, self.cache.max_slots), vocab), dtype=torch.float32, device=self.device)
             self._logits_buffer = buf
+            self.generation += 1
         return buf[:rows]
 
     # ---- a step's metadata ----
@@ -187,12 +191,12 @@ class StepRuntime:
                                   nq, nkv, d, window, scale)
             return
         if ctx.decode_rows.numel():
-            split_len, n_splits = self.decode_split_plan(ctx, nq, nkv, window)
+            n_splits = self.decode_splits(ctx.decode_rows.numel(), nq, nkv)
             partial = None
             if n_splits > 1:
                 partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
             ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
-                                 kv.block_table, out, partial, nq, nkv, d, window, scale, split_len, n_splits)
+                                 kv.block_table, out, partial, nq, nkv, d, window, scale, 0, n_splits)
         if ctx.n_prefill_segments:
             per_tile = ops.attention_prefill_tokens_per_tile(nq // nkv)
             if per_tile:
@@ -203,14 +207,11 @@ class StepRuntime:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
                                       nq, nkv, d, window, scale, rows=ctx.prefill_rows)
 
-    def decode_split_plan(self, ctx, nq, nkv, window):
-        """(split_len, n_splits) for this step's decoded tokens: enough ranges of keys to give every
-        SM about two CTAs, each range a multiple of 64 keys."""
-        span = max(start + 1 for _, start, count, _ in ctx.segments if count == 1)
-        if window:
-            span = min(span, window)
+    def decode_splits(self, rows, nq, nkv):
+        """Into how many ranges the decode attention cuts each token's keys: enough to give every SM
+        about two CTAs.  It depends on the number of decoded tokens in the step alone (each token then
+        cuts its own span, on the device), so a captured step serves every context length."""
         groups = nkv * ((nq // nkv + 15) // 16)
-        ctas = max(1, ctx.decode_rows.numel() * groups)
-        wanted = max(1, (2 * self.sm_count + ctas - 1) // ctas)
-        split_len = max(64, ((span + wanted - 1) // wanted + 63) // 64 * 64)
-        return split_len, (span + split_len - 1) // split_len
+        ctas = max(1, rows * groups)
+        wanted = (2 * self.sm_count + ctas - 1) // ctas
+        return max(1, min(wanted, 64, (self.cache.max_context + 63) // 64))

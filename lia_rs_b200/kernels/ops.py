@@ -51,6 +51,8 @@ class _Signatures:
                             c_float, c_int, c_int, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
+    lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                       c_void_p, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -78,12 +80,17 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-LAUNCHES = 0      # kernels launched through this module since import (a benchmark's own count)
+def kernel_launches() -> int:
+    """Kernels this library has launched since it was loaded, counted at the launch sites in C.  A
+    replay of a captured CUDA graph runs its kernels again without passing a launch site: the engine
+    adds those (`Engine.stats['kernels']`)."""
+    fn = lib().lia_kernel_launches
+    fn.restype = ctypes.c_longlong
+    fn.argtypes = []
+    return int(fn())
 
 
 def _check(code: int, what: str):
-    global LAUNCHES
-    LAUNCHES += 1
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, code)}")
 
@@ -132,7 +139,7 @@ def gemm_simt(mode, a, w, out, alpha: float = 1.0):
                                _stream()), "gemm_simt")
 
 
-_SCRATCH_FLOATS = 16 << 20          # 64 MB of split-K scratch per device, allocated at first use
+_SCRATCH_FLOATS = 16 << 20          # 64 MB of split-K scratch per device, allocated (zeroed) at first use
 _scratch = {}
 _sm_count = {}
 
@@ -140,7 +147,8 @@ _sm_count = {}
 def _device_scratch(device):
     key = torch.device(device).index or 0
     if key not in _scratch:
-        _scratch[key] = torch.empty(_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+        # zeroed: the first words are tile counters that every product leaves at zero again
+        _scratch[key] = torch.zeros(_SCRATCH_FLOATS, dtype=torch.float32, device=device)
         _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _scratch[key], _sm_count[key]
 
@@ -168,6 +176,30 @@ def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
                              _stream()), "gemm_tc")
 
 
+SKINNY_MAX_TOKENS = 32
+
+
+def gemm_skinny_accepts(mode, a, w, out) -> bool:
+    """Whether the few-token kernel takes this product: bfloat16 operands, at most 32 tokens, K and the
+    row strides multiples of 8 elements, 16-byte aligned bases (bulk copies and 16-byte loads)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    M, K = a.shape
+    return (M <= SKINNY_MAX_TOKENS and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T for M <= 32 tokens: each CTA streams 16 rows of w over
+    the whole of K; see csrc/gemm_skinny.cu."""
+    M, K = a.shape
+    N = out.shape[1]
+    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                                 out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
+
+
 def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale,
                       rows=None):
     """Attention for every token of the batch, or for the tokens whose batch indices `rows` lists."""
@@ -187,7 +219,8 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
-    csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results."""
+    csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
+    `split_len` 0: every row cuts its own visible span into `n_splits` ranges."""
     _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_decode is a bfloat16 kernel")

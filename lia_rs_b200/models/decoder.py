@@ -120,6 +120,8 @@ class DecoderModel:
             self.head = self.embedding
         else:
             self.head = prepare_weight(tensors[spec.head_name].to(device), runtime)
+        # decode steps may be captured in CUDA graphs only if every part launches the same way each step
+        self.graph_safe = all(layer.graph_safe for layer in self.layers) and bool(self.final_norm.graph_safe)
 
     def forward(self, ctx) -> torch.Tensor:
         """Run the step described by `ctx`; returns 32-bit logits [ctx.n_out, vocab] (device)."""

@@ -22,6 +22,8 @@ from .linear import ACCUM, STORE, linear, prepare_weight
 
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
+    graph_safe = True
+
     @staticmethod
     def tensor_specs(params, prefix):
         h, nq, nkv, d = params["hidden"], params["heads"], params["kv_heads"], params["head_dim"]
@@ -49,6 +51,7 @@ class GQAttention(Mixer):
         position = params["position"]
         self.position = lookup(POSITION_ENCODINGS, position.kind, "position encoding")(
             position.params, tensors, prefix, runtime)
+        self.graph_safe = bool(self.position.graph_safe)
 
     def forward(self, ctx, x, residual, scale, kv=None, state=None):
         rt, n = self.runtime, x.shape[0]

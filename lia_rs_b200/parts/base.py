@@ -63,7 +63,16 @@ class Runtime:
 
 class Part:
     """Base of all parts.  `tensor_specs` declares the checkpoint tensors (names relative to
-    `prefix`); `__init__` receives them already on the device, in their storage element type."""
+    `prefix`); `__init__` receives them already on the device, in their storage element type.
+
+    `graph_safe`: the part's `forward` launches the same kernels with the same arguments in every step
+    that has the same number of tokens and of wanted rows; whatever differs between such steps
+    (token ids, positions, slots, pages) it reads on the device, from `ctx.tokens`, `ctx.positions`,
+    `ctx.slots` and the block tables, never on the host.  Only when every part of a model says so are
+    its decode steps captured in CUDA graphs and replayed; a part that looks at `ctx.segments` in
+    Python, or allocates, leaves this False and the model runs launch by launch."""
+
+    graph_safe = False
 
     @staticmethod
     def tensor_specs(params: dict, prefix: str) -> list:
@@ -109,7 +118,10 @@ class FeedForward(Part):
 
 
 class Arrangement:
-    """How one layer wires its parts around the residual stream."""
+    """How one layer wires its parts around the residual stream.  `graph_safe` as for `Part`: true
+    when all its parts are."""
+
+    graph_safe = False
 
     @staticmethod
     def tensor_specs(layer_spec, prefix: str) -> list:

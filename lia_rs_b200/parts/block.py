@@ -44,6 +44,7 @@ class PreNormBlock(Arrangement):
         self.norm2 = lookup(NORMS, spec.norm.kind, "norm")(spec.norm.params, tensors, prefix + n["norm2"], runtime)
         self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
             spec.feed_forward.params, tensors, prefix + n["feed_forward"], runtime)
+        self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
     def forward(self, ctx, residual, kv=None, state=None):
         x = ctx.buffer("block.x", tuple(residual.shape), self.runtime.compute_dtype)

@@ -14,6 +14,8 @@ from .linear import ACCUM, SWIGLU, linear, prepare_weight
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     @staticmethod
     def tensor_specs(params, prefix):
         h, i = params["hidden"], params["intermediate"]

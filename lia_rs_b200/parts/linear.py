@@ -1,8 +1,9 @@
 """Matrix products of the parts: out (op)= alpha * a @ w^T with an epilogue.
 
 `prepare_weight` brings a checkpoint matrix to the compute element type once, at load.
-`linear` chooses the kernel: the tcgen05 kernel for bfloat16 when the shape allows it, else the
-product on the 32-bit pipes (always, for the 32-bit path)."""
+`linear` chooses the kernel.  bfloat16: up to 32 tokens the kernel that streams the weights once with
+no meeting of CTAs (csrc/gemm_skinny.cu), beyond that the tcgen05 kernel (csrc/gemm_tc.cu), when the
+shape allows them; else, and always for the 32-bit path, the product on the 32-bit pipes."""
 from __future__ import annotations
 
 import torch
@@ -17,7 +18,9 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 
 
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
-    if a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
+    if a.dtype == torch.bfloat16 and ops.gemm_skinny_accepts(mode, a, w, out):
+        ops.gemm_skinny(mode, a, w, out, alpha)
+    elif a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
         ops.gemm_tc(mode, a, w, out, alpha)
     else:
         ops.gemm_simt(mode, a, w, out, alpha)

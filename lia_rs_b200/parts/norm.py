@@ -8,6 +8,8 @@ from .base import Norm, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     @staticmethod
     def tensor_specs(params, prefix):
         return [TensorSpec(prefix + "weight", (params["hidden"],), kind="norm")]

@@ -12,6 +12,8 @@ from .base import PositionEncoding, register_position_encoding
 
 @register_position_encoding("rotary")
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, params, tensors, prefix, runtime):
         super().__init__(params, tensors, prefix, runtime)
         self.rotary_dim = int(params["rotary_dim"])
@@ -30,6 +32,8 @@ class RotaryEncoding(PositionEncoding):
 
 @register_position_encoding("none")
 class NoEncoding(PositionEncoding):
+    graph_safe = True
+
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d):
         self.runtime.ops.rope_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,
                                        kv.v_pages, nq, nkv, d, 0, None, write_kv=kv.writes,

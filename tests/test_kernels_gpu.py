@@ -250,6 +250,44 @@ def test_gemm_tc_all_epilogues_against_64_bit(M, N, K):
     assert flag.item() == 0
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(40, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (77, 16384), (301, 7000)])
+def test_gemm_skinny_all_epilogues_against_64_bit(M, N, K):
+    """The few-token product: widths that are no multiple of its 16 rows, K shorter than a chunk, K that
+    ends inside a group of 32, and K long enough that the ring of stages is used again."""
+    o = ops()
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert o.gemm_skinny_accepts(o.GEMM_STORE, a, w, torch.empty(M, N, device=DEV))
+    exact = a.double() @ w.double().T
+    scale = max(1.0, float(exact.abs().max()))
+    out = torch.full((M, N), 7.0, device=DEV)
+    o.gemm_skinny(o.GEMM_STORE, a, w[:N], out, 0.25, flag)
+    assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(K / 64)
+    half = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_skinny(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
+    assert float((half.double() - exact[:, :N]).abs().max()) <= 2.0 ** -8 * scale
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    o.gemm_skinny(o.GEMM_ACCUM, a, w[:N], acc, 1.5, flag)
+    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(K / 64)
+    act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_skinny(o.GEMM_SWIGLU, a, w, act, 1.0, flag)
+    gate, up = exact[:, :N], exact[:, N:]
+    want = up * gate / (1 + torch.exp(-gate))
+    assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    # a token's result does not depend on how many other tokens are in the batch
+    alone = torch.empty(1, N, device=DEV)
+    o.gemm_skinny(o.GEMM_STORE, a[M - 1:M].contiguous(), w[:N], alone, 0.25, flag)
+    assert torch.equal(alone[0], out[M - 1])
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+    with pytest.raises(o.KernelError, match="refuses"):
+        o.gemm_skinny(o.GEMM_STORE, torch.zeros(33, K, device=DEV, dtype=torch.bfloat16), w[:N], torch.empty(33, N, device=DEV))
+
+
 def test_gemm_tc_refuses_what_tma_cannot_address():
     o = ops()
     a = torch.randn(4, 100, device=DEV).to(torch.bfloat16)          # K = 100: rows of 200 bytes

@@ -77,7 +77,7 @@ def test_no_alloc_refuses_what_its_array_cannot_hold():
     from lia_rs_b200.kernels import ops
     fn, need = entry_points()
     sms = torch.cuda.get_device_properties(DEV).multi_processor_count
-    M, N, K = 256, 6144, 2048                                      # 7 ranges x 256 x 6144 floats > 8 MiB
+    M, N, K = 128, 12288, 2048                                     # two ranges or more x 128 x 12288 floats > 8 MiB
     assert need(ops.GEMM_STORE, M, N, K, sms) > SCRATCH_FLOATS
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = torch.randn(N, K, device=DEV).to(torch.bfloat16)

@@ -216,6 +216,8 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
+    parser.add_argument("--no-graphs", action="store_true",
+                        help="launch decode steps kernel by kernel instead of replaying CUDA graphs (for profilers)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -239,7 +241,8 @@ def main() -> int:
     total_steps = args.steps + args.warmup
     pool = largest * ((PROMPT + total_steps + 8 + 63) // 64 * 64) + PROMPT
     engine = Engine.random(config, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=largest,
-                           max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
+                           max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"],
+                           cuda_graphs=not args.no_graphs)
     weight_bytes, cache_bytes_per_token = model_bytes(cfg, args.layers)
 
     def decode_point(batch, steps, warmup):

@@ -9,6 +9,8 @@ template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                  float* __restrict__ out, int n_tokens, int hidden, int vocab,
                                  float scale, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const int token = tokens[t];
@@ -27,14 +29,12 @@ LIA_EXPORT int lia_embedding(const int* tokens, const void* table, int table_dty
     if (hidden <= 0 || vocab <= 0) return LIA_ERR_SIZE;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == LIA_BF16)
-        embedding_kernel<<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out,
-                                                           n_tokens, hidden, vocab, scale, error_flag);
-    else if (table_dtype == LIA_F32)
-        embedding_kernel<<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, n_tokens,
-                                                           hidden, vocab, scale, error_flag);
-    else
-        return LIA_ERR_DTYPE;
-    return lia_check_launch();
+        return lia_launch(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+                          (const __nv_bfloat16*)table, out, n_tokens, hidden, vocab, scale, error_flag);
+    if (table_dtype == LIA_F32)
+        return lia_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table,
+                          out, n_tokens, hidden, vocab, scale, error_flag);
+    return LIA_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -42,11 +42,88 @@ LIA_EXPORT int lia_embedding(const int* tokens, const void* table, int table_dty
 // Sum of squares, mean, eps and the reciprocal root are 32-bit; the order of the additions
 // depends on `hidden` alone, not on the number of rows.  `rows_index` (optional) gathers:
 // output row r is computed from input row rows_index[r] (negative index -> zeros).
+//
+// One warp owns one row and keeps it in registers between the sum and the scaling (rows of up to
+// 4096 elements whose width is a multiple of 4): 16-byte loads, all in flight at once, no block
+// barrier.  Other widths take the block-per-row kernel below.
+template <typename TO> __device__ __forceinline__ void store4(TO* dst, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = v;
+}
+template <typename TW> __device__ __forceinline__ float4 load4(const TW* src);
+template <> __device__ __forceinline__ float4 load4<float>(const float* src) { return *reinterpret_cast<const float4*>(src); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* src) {
+    const uint2 v = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+
+template <typename TW, typename TO, int VPL>      // VPL: float4 per lane; the row has at most 128 * VPL elements
+__global__ void rmsnorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
+                                    const TW* __restrict__ weight, TO* __restrict__ out, int rows,
+                                    int hidden, float eps, float out_scale) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int quads = hidden >> 2;
+    float4 w[VPL];                                   // the weights wait for no one
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = lane + i * 32;
+        w[i] = q < quads ? load4<TW>(weight + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    const int src = rows_index ? rows_index[r] : r;
+    TO* dst = out + (size_t)r * hidden;
+    if (src < 0) {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int q = lane + i * 32;
+            if (q < quads) store4<TO>(dst + 4 * q, 0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
+    const float* row = x + (size_t)src * hidden;
+    float4 v[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = lane + i * 32;
+        v[i] = q < quads ? *reinterpret_cast<const float4*>(row + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        sum = fmaf(v[i].x, v[i].x, sum);
+        sum = fmaf(v[i].y, v[i].y, sum);
+        sum = fmaf(v[i].z, v[i].z, sum);
+        sum = fmaf(v[i].w, v[i].w, sum);
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sqrtf(sum / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = lane + i * 32;
+        if (q < quads)
+            store4<TO>(dst + 4 * q, v[i].x * inv * w[i].x * out_scale, v[i].y * inv * w[i].y * out_scale,
+                       v[i].z * inv * w[i].z * out_scale, v[i].w * inv * w[i].w * out_scale);
+    }
+}
+
 template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
                                const TW* __restrict__ weight, TO* __restrict__ out, int rows,
                                int hidden, float eps, float out_scale) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     if (r >= rows) return;
     const int src = rows_index ? rows_index[r] : r;
@@ -67,22 +144,40 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
         dst[i] = from_float<TO>(row[i] * inv * to_float(weight[i]) * out_scale);
 }
 
+template <typename TW, typename TO>
+int launch_rmsnorm(const float* x, const int* rows_index, const void* weight, void* out, int rows, int hidden,
+                   float eps, float out_scale, cudaStream_t stream) {
+    const bool vector = hidden % 4 == 0 && hidden <= 4096 && ((uintptr_t)x & 15u) == 0 && ((uintptr_t)weight & 15u) == 0 &&
+                        ((uintptr_t)out & 15u) == 0;
+    if (!vector)
+        return lia_launch(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(hidden >= 1024 ? 256 : 128), 0, stream, x, rows_index,
+                          (const TW*)weight, (TO*)out, rows, hidden, eps, out_scale);
+    const int warps = rows >= 256 ? 4 : 1;             // few rows: one warp per CTA, spread over the SMs
+    const dim3 grid((rows + warps - 1) / warps), block(warps * 32);
+#define LIA_NORM_WARP(VPL)                                                                                          \
+    return lia_launch(rmsnorm_warp_kernel<TW, TO, VPL>, grid, block, 0, stream, x, rows_index, (const TW*)weight, \
+                      (TO*)out, rows, hidden, eps, out_scale)
+    if (hidden <= 512) LIA_NORM_WARP(4);
+    if (hidden <= 1024) LIA_NORM_WARP(8);
+    if (hidden <= 2048) LIA_NORM_WARP(16);
+    LIA_NORM_WARP(32);
+#undef LIA_NORM_WARP
+}
+
 LIA_EXPORT int lia_rmsnorm(const float* x, const int* rows_index, const void* weight, int weight_dtype,
                            void* out, int out_dtype, int rows, int hidden, float eps, float out_scale,
                            cudaStream_t stream) {
     if (rows <= 0) return LIA_OK;
     if (hidden <= 0) return LIA_ERR_SIZE;
-    const int threads = hidden >= 1024 ? 256 : 128;
-#define LIA_NORM(TW, TO)                                                                          \
-    rmsnorm_kernel<TW, TO><<<rows, threads, 0, stream>>>(x, rows_index, (const TW*)weight, (TO*)out, \
-                                                         rows, hidden, eps, out_scale)
-    if (weight_dtype == LIA_BF16 && out_dtype == LIA_BF16) LIA_NORM(__nv_bfloat16, __nv_bfloat16);
-    else if (weight_dtype == LIA_BF16 && out_dtype == LIA_F32) LIA_NORM(__nv_bfloat16, float);
-    else if (weight_dtype == LIA_F32 && out_dtype == LIA_BF16) LIA_NORM(float, __nv_bfloat16);
-    else if (weight_dtype == LIA_F32 && out_dtype == LIA_F32) LIA_NORM(float, float);
-    else return LIA_ERR_DTYPE;
-#undef LIA_NORM
-    return lia_check_launch();
+    if (weight_dtype == LIA_BF16 && out_dtype == LIA_BF16)
+        return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, rows_index, weight, out, rows, hidden, eps, out_scale, stream);
+    if (weight_dtype == LIA_BF16 && out_dtype == LIA_F32)
+        return launch_rmsnorm<__nv_bfloat16, float>(x, rows_index, weight, out, rows, hidden, eps, out_scale, stream);
+    if (weight_dtype == LIA_F32 && out_dtype == LIA_BF16)
+        return launch_rmsnorm<float, __nv_bfloat16>(x, rows_index, weight, out, rows, hidden, eps, out_scale, stream);
+    if (weight_dtype == LIA_F32 && out_dtype == LIA_F32)
+        return launch_rmsnorm<float, float>(x, rows_index, weight, out, rows, hidden, eps, out_scale, stream);
+    return LIA_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -104,6 +199,8 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
                                TC* __restrict__ v_pages, int n_tokens, int nq, int nkv, int d,
                                int rotary_dim, const float* __restrict__ inv_freq, int page_size,
                                int num_pages, int write_kv, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const int slot = slots[t];
@@ -165,13 +262,12 @@ LIA_EXPORT int lia_rope_kv_write(const float* qkv, const int* positions, const i
         (rotary_dim & 1) || (rotary_dim > 0 && !inv_freq))
         return LIA_ERR_SIZE;
     const int threads = 256;
-#define LIA_ROPE(T)                                                                                 \
-    rope_kv_kernel<T, T><<<n_tokens, threads, 0, stream>>>(                                         \
-        qkv, positions, slots, block_table, table_stride, (T*)q_out, (T*)k_pages, (T*)v_pages,      \
-        n_tokens, nq, nkv, d, rotary_dim, inv_freq, page_size, num_pages, write_kv, error_flag)
+#define LIA_ROPE(T)                                                                                          \
+    return lia_launch(rope_kv_kernel<T, T>, dim3(n_tokens), dim3(threads), 0, stream, qkv, positions, slots, \
+                      block_table, table_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, nq, nkv, d,  \
+                      rotary_dim, inv_freq, page_size, num_pages, write_kv, error_flag)
     if (dtype == LIA_BF16) LIA_ROPE(__nv_bfloat16);
-    else if (dtype == LIA_F32) LIA_ROPE(float);
-    else return LIA_ERR_DTYPE;
+    if (dtype == LIA_F32) LIA_ROPE(float);
 #undef LIA_ROPE
-    return lia_check_launch();
+    return LIA_ERR_DTYPE;
 }

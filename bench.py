@@ -163,7 +163,7 @@ def time_e2e(engine, batch, steps, warmup):
     vocab = engine.spec.vocab_size
     scheduler = Scheduler(engine, max_batch_tokens=engine.max_batch_tokens)
     for i in range(batch):
-        scheduler.add(i, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], max_tokens=steps + warmup + 4)
+        scheduler.add(i, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], max_tokens=steps + warmup + batch + 4)
     while any(not r.generated for r in scheduler.live()) or scheduler.queue:
         scheduler.step()
     for _ in range(warmup):

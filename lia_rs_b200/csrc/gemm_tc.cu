@@ -33,115 +33,20 @@
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the role raises the error flag and leaves
 // its loop; the CTA then waits (bounded) for its copies in flight, frees its TMEM and returns.
-#include <cuda.h>
+#include "tcgen05.cuh"
 
-#include "common.cuh"
+using namespace tc5;
 
 #define GEMM_STORE 0
 #define GEMM_ACCUM 1
 #define GEMM_SWIGLU 2
 
 namespace {
-constexpr int BLOCK_K = 64;          // bf16 elements per K block: 128 bytes, one swizzle row
-constexpr int TILE_F = 128;          // features per tile: the MMA's M
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;      // polls of mbarrier.try_wait (each suspends up to ~1 us)
 constexpr int MAX_STAGES = 12;
 constexpr int SMEM_BYTES = 226 * 1024;         // dynamic shared memory asked for (a CTA may have 227 KB; 1 KB is static)
 constexpr int STAGING_TOKENS = 32;             // tokens per TMA store of the epilogue
 constexpr int COUNTER_WORDS = 4096;            // tile counters at the head of the scratch
-
-// ---- PTX wrappers ----
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void tma_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 16 consecutive columns of this warp's 32 TMEM lanes: thread = lane (feature), v[c] = column (token).
-__device__ __forceinline__ void tmem_load16(uint32_t addr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled, with
-// groups of 8 rows 1024 bytes apart: start address, leading offset 1 (unused with a swizzle), stride
-// offset 1024 bytes, descriptor version 1, layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// Instruction descriptor: 32-bit accumulator, bf16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 struct Shape {
     int M, N, K;              // tokens, output features (per half for SWIGLU), reduction length
@@ -455,57 +360,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
-// ---- host side ----
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess &&
-            status == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A [rows, cols] bf16 matrix with row stride `ld` elements; boxes of [box_rows, 64], 128-byte swizzle,
-// out-of-range elements read as zero.
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return LIA_ERR_DRIVER;
-    if (((uintptr_t)base & 15u) || (ld % 8)) return LIA_ERR_ALIGN;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {BLOCK_K, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LIA_OK : LIA_ERR_DRIVER;
-}
-
-// The output [M, N] (row stride ldo elements) for the epilogue's stores: boxes of [32 tokens, 128 features],
-// no swizzle; what lies outside the matrix is not written.
-int make_out_map(CUtensorMap* map, void* base, int out_dtype, int M, int N, int ldo) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return LIA_ERR_DRIVER;
-    const int esize = out_dtype == LIA_F32 ? 4 : 2;
-    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)ldo * esize};
-    cuuint32_t box[2] = {TILE_F, STAGING_TOKENS};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, out_dtype == LIA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
-                    dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LIA_OK : LIA_ERR_DRIVER;
-}
-
 int pow2_at_least(int x) {
     int p = 32;
     while (p < x) p *= 2;
@@ -607,7 +461,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     if ((rc = make_map(&mw, W, s.n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
     if ((rc = make_map(&mx, X, M, K, ldx, plan.n_tile)) != LIA_OK) return rc;
     if (s.via_tma) {
-        if ((rc = make_out_map(&mo, out, out_dtype, M, N, ldo)) != LIA_OK) return rc;
+        if ((rc = make_out_map(&mo, out, out_dtype, M, N, ldo, STAGING_TOKENS)) != LIA_OK) return rc;
     } else {
         mo = mx;
     }

@@ -51,6 +51,9 @@ class _Signatures:
                             c_float, c_int, c_int, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
+    lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                        c_int, c_void_p, c_void_p]
+    lia_gemm_cluster_splits = [c_int, c_int, c_int, c_int, c_int]
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -174,6 +177,27 @@ def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
     _check(lib().lia_gemm_tc(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                              out.stride(0), M, N, K, alpha, _p(scratch), scratch.numel(), sms, _p(error_flag),
                              _stream()), "gemm_tc")
+
+
+def gemm_cluster_accepts(mode, a, w, out) -> bool:
+    """Whether the cluster kernel takes this product: what the tcgen05 kernel takes, and so few output
+    tiles that at least two CTAs of a cluster can share each one's K."""
+    if not gemm_tc_accepts(mode, a, w, out):
+        return False
+    _, sms = _device_scratch(a.device)
+    return lib().lia_gemm_cluster_splits(mode, a.shape[0], out.shape[1], a.shape[1], sms) >= 2
+
+
+def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores with K cut over the CTAs of a
+    thread-block cluster, partial sums meeting in distributed shared memory; see csrc/gemm_cluster.cu."""
+    M, K = a.shape
+    N = out.shape[1]
+    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _, sms = _device_scratch(a.device)
+    _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                                  out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
 
 
 SKINNY_MAX_TOKENS = 32

@@ -2,8 +2,9 @@
 
 `prepare_weight` brings a checkpoint matrix to the compute element type once, at load.
 `linear` chooses the kernel.  bfloat16: up to 32 tokens the kernel that streams the weights once with
-no meeting of CTAs (csrc/gemm_skinny.cu), beyond that the tcgen05 kernel (csrc/gemm_tc.cu), when the
-shape allows them; else, and always for the 32-bit path, the product on the 32-bit pipes."""
+no meeting of CTAs (csrc/gemm_skinny.cu); beyond that, while the product has too few output tiles to
+fill the SMs, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu); then the persistent
+tcgen05 kernel (csrc/gemm_tc.cu), when the shape allows them; else, and always for the 32-bit path, the product on the 32-bit pipes."""
 from __future__ import annotations
 
 import torch
@@ -20,6 +21,8 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
     if a.dtype == torch.bfloat16 and ops.gemm_skinny_accepts(mode, a, w, out):
         ops.gemm_skinny(mode, a, w, out, alpha)
+    elif a.dtype == torch.bfloat16 and ops.gemm_cluster_accepts(mode, a, w, out):
+        ops.gemm_cluster(mode, a, w, out, alpha)
     elif a.dtype == torch.bfloat16 and ops.gemm_tc_accepts(mode, a, w, out):
         ops.gemm_tc(mode, a, w, out, alpha)
     else:

@@ -288,6 +288,49 @@ def test_gemm_skinny_all_epilogues_against_64_bit(M, N, K):
         o.gemm_skinny(o.GEMM_STORE, torch.zeros(33, K, device=DEV, dtype=torch.bfloat16), w[:N], torch.empty(33, N, device=DEV))
 
 
+@pytest.mark.parametrize("M", [1, 16, 33, 40, 64, 100, 128, 200, 300])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (2048, 2048), (6144, 2048)])
+def test_gemm_cluster_all_epilogues_against_64_bit(M, N, K):
+    """The product that cuts K over a cluster: token counts that are no multiple of 16, widths that are no
+    multiple of 128, K shorter than the cluster is wide, K long enough that the ring is used again."""
+    o = ops()
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    exact = a.double() @ w.double().T
+    scale = max(1.0, float(exact.abs().max()))
+    if o.gemm_cluster_accepts(o.GEMM_STORE, a, w[:N], torch.empty(M, N, device=DEV)):
+        out = torch.full((M, N), 7.0, device=DEV)
+        o.gemm_cluster(o.GEMM_STORE, a, w[:N], out, 0.25, flag)
+        assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(K / 64)
+        again = torch.full((M, N), 7.0, device=DEV)
+        o.gemm_cluster(o.GEMM_STORE, a, w[:N], again, 0.25, flag)
+        assert torch.equal(out, again)                  # the ranges are added in a fixed order
+        half = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        o.gemm_cluster(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
+        assert float((half.double() - exact[:, :N]).abs().max()) <= 2.0 ** -8 * scale
+        base = torch.randn(M, N, device=DEV)
+        acc = base.clone()
+        o.gemm_cluster(o.GEMM_ACCUM, a, w[:N], acc, 1.5, flag)
+        assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(K / 64)
+        # a view with a row stride that rules out 16-byte stores
+        wide = torch.full((M, N + 3), 7.0, device=DEV)
+        o.gemm_cluster(o.GEMM_STORE, a, w[:N], wide[:, 1:N + 1], 0.25, flag)
+        assert torch.equal(wide[:, 1:N + 1], out) and float(wide[:, 0].min()) == 7.0 and float(wide[:, N + 1:].min()) == 7.0
+    else:
+        with pytest.raises(o.KernelError, match="refuses"):
+            o.gemm_cluster(o.GEMM_STORE, a, w[:N], torch.empty(M, N, device=DEV), 0.25, flag)
+    if o.gemm_cluster_accepts(o.GEMM_SWIGLU, a, w, torch.empty(M, N, device=DEV, dtype=torch.bfloat16)):
+        act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        o.gemm_cluster(o.GEMM_SWIGLU, a, w, act, 1.0, flag)
+        gate, up = exact[:, :N], exact[:, N:]
+        want = up * gate / (1 + torch.exp(-gate))
+        assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+
+
 def test_gemm_tc_refuses_what_tma_cannot_address():
     o = ops()
     a = torch.randn(4, 100, device=DEV).to(torch.bfloat16)          # K = 100: rows of 200 bytes

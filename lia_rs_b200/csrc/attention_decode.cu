@@ -26,10 +26,13 @@ struct Params {
     const int* slots;                // [tokens]
     const int* block_table;          // [slots, table_stride]
     __nv_bfloat16* out;              // [tokens, nq, D]
-    float* partial;                  // [tokens, nq, n_splits, D + 1]: normalised output, then log2-sum-exp
-    int table_stride, nq, nkv, page_size, window, split_len, n_splits;
+    float* partial;                  // [tokens, nq, n_splits, D] normalised outputs, then [tokens, nq, n_splits] log2-sum-exps
+    int* counters;                   // [n_rows, gridDim.y], zero between launches; null: ranges are merged by a second kernel
+    int n_tokens, table_stride, nq, nkv, page_size, page_shift, window, split_len, n_splits;
     float scale_log2;                // softmax scale * log2(e)
 };
+
+constexpr int MAX_FUSED_SPLITS = 128;     // ranges that the last CTA of a token can merge (its weights lie in shared memory)
 
 // Keys per range for a token that sees `span` keys: the given length, or (split_len 0) the span cut into
 // n_splits ranges of a multiple of 64 keys.  The second rule depends on the token's own span and on
@@ -40,12 +43,29 @@ __device__ __forceinline__ int range_length(const Params& p, int span) {
     return (per + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^n for a whole number n <= 0 (or -infinity), exactly.
+__device__ __forceinline__ float exp2_whole(float n) {
+    return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
+}
+
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(Params p) {
     using T = Tile<D>;
+    constexpr int CHUNKS = T::CHUNKS;                 // 16-byte pieces per key row = lanes that share a row
+    constexpr int ROWS_PER_PASS = WARPS * 32 / CHUNKS; // rows that one cp.async of every thread covers
+    constexpr int PASSES = TILE_KEYS / ROWS_PER_PASS;
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    pdl_launch_dependents();
+    // The step's metadata and the keys of earlier steps depend on no kernel of this step; only q and the
+    // newest key do, so everything up to pdl_wait() below overlaps the kernel ahead.
     const int t = p.rows[blockIdx.x];
     if (t < 0) return;
     const int slot = p.slots[t];
@@ -63,6 +83,43 @@ attention_decode_kernel(Params p) {
     if (key_begin >= key_end) return;
     const int* table = p.block_table + (size_t)slot * p.table_stride;
 
+    // ---- loading a tile: CHUNKS lanes share a key row; lane j of them looks up the row of pass j ----
+    const uint32_t smem_base = smem_u32(smem);
+    const int sub = lane / CHUNKS, piece = lane % CHUNKS;
+    const int row_base = warp * (32 / CHUNKS) + sub;                 // this thread's row in pass 0
+    const uint32_t piece_offset = T::offset(row_base, piece);        // later passes: + ROWS_PER_PASS rows, same swizzle
+    static_assert(ROWS_PER_PASS % 8 == 0 && PASSES <= CHUNKS, "the swizzle repeats every 8 rows; one lane per pass");
+    auto load_tile = [&](int stage, int key0) {
+        const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES + piece_offset, vs = ks + T::BYTES;
+        int my_row = -1;
+        if (piece < PASSES) {
+            const int key = key0 + row_base + piece * ROWS_PER_PASS;
+            if (key < key_end) {
+                const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+                my_row = table[page] * p.page_size + (key - page * p.page_size);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const int row = __shfl_sync(0xffffffffu, my_row, sub * CHUNKS + i);
+            const bool valid = row >= 0;
+            const size_t src = ((size_t)(valid ? row : 0) * p.nkv + kvh) * D + piece * 8;
+            cp_async_16(ks + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.k_pages + src, valid);
+            cp_async_16(vs + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.v_pages + src, valid);
+        }
+    };
+
+    const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles) {
+            if (key_begin + (s + 1) * TILE_KEYS > pos) pdl_wait();       // the tile holds the key this step wrote
+            load_tile(s, key_begin + s * TILE_KEYS);
+        }
+        cp_async_commit();
+    }
+    pdl_wait();
+
     // ---- Q fragments: rows = heads (row r -> head h0 + r), zero beyond `heads` ----
     uint32_t qf[D / 16][4];
     {
@@ -78,32 +135,13 @@ attention_decode_kernel(Params p) {
         }
     }
 
-    const uint32_t smem_base = smem_u32(smem);
-    auto load_tile = [&](int stage, int key0) {
-        const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES, vs = ks + T::BYTES;
-        for (int id = tid; id < TILE_KEYS * T::CHUNKS; id += WARPS * 32) {
-            const int r = id / T::CHUNKS, c = id % T::CHUNKS;
-            const int key = key0 + r;
-            const bool valid = key < key_end;
-            size_t row = 0;
-            if (valid) row = (size_t)table[key / p.page_size] * p.page_size + key % p.page_size;
-            const size_t src = (row * p.nkv + kvh) * D + c * 8;
-            cp_async_16(ks + T::offset(r, c), p.k_pages + src, valid);
-            cp_async_16(vs + T::offset(r, c), p.v_pages + src, valid);
-        }
-    };
-
-    const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles) load_tile(s, key_begin + s * TILE_KEYS);
-        cp_async_commit();
-    }
-
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+    // shared-memory offsets of this lane's ldmatrix rows inside a tile (the tile's base is added per stage)
+    const int lm = lane >> 3;
+    const int k_row = warp * 16 + (lm >> 1) * 8 + (lane & 7), v_row = warp * 16 + (lm & 1) * 8 + (lane & 7);
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         cp_async_wait<STAGES - 2>();
@@ -121,24 +159,22 @@ attention_decode_kernel(Params p) {
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                const int m = lane >> 3;
-                const int row = warp * 16 + (m >> 1) * 8 + (lane & 7);
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(ks + T::offset(row, kk * 2 + (m & 1)), b0, b1, b2, b3);
+                ldmatrix_x4(ks + T::offset(k_row, kk * 2 + (lm & 1)), b0, b1, b2, b3);
                 mma_bf16(s[0], qf[kk], b0, b1);
                 mma_bf16(s[1], qf[kk], b2, b3);
             }
-            // ---- scale, mask, running maximum and sum ----
-            float tile_max[2] = {-INFINITY, -INFINITY};
+            // ---- mask (only the range's last keys need it), running maximum and sum ----
+            if (key0 + 16 > key_end) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
-                    const float v = key < key_end ? s[nt][i] * p.scale_log2 : -INFINITY;
-                    s[nt][i] = v;
-                    tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
-                }
+                    for (int i = 0; i < 4; ++i)
+                        if (key0 + nt * 8 + (lane & 3) * 2 + (i & 1) >= key_end) s[nt][i] = -INFINITY;
+            }
+            float tile_max[2];
+            tile_max[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            tile_max[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
             float correction[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -146,9 +182,9 @@ attention_decode_kernel(Params p) {
                 tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
                 // The reference point of the exponentials is a whole number (in base-2 logarithms), so the
                 // 16-bit probabilities have the same mantissas whatever tile, warp or range a key falls
-                // in, and rescaling by `correction` is exact.
-                const float new_max = fmaxf(row_max[r], ceilf(tile_max[r]));     // finite: key0 < key_end
-                correction[r] = exp2f(row_max[r] - new_max);
+                // in, and rescaling by `correction` (a power of two) is exact.
+                const float new_max = fmaxf(row_max[r], ceilf(tile_max[r] * p.scale_log2));   // finite: key0 < key_end
+                correction[r] = exp2_whole(row_max[r] - new_max);
                 row_max[r] = new_max;
                 row_sum[r] *= correction[r];
             }
@@ -159,7 +195,7 @@ attention_decode_kernel(Params p) {
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        e[nt][i] = exp2f(s[nt][i] - row_max[i >> 1]);
+                        e[nt][i] = ex2_approx(fmaf(s[nt][i], p.scale_log2, -row_max[i >> 1]));
                         row_sum[i >> 1] += e[nt][i];
                     }
                 pf[0] = pack_bf16(e[0][0], e[0][1]);
@@ -167,15 +203,17 @@ attention_decode_kernel(Params p) {
                 pf[2] = pack_bf16(e[1][0], e[1][1]);
                 pf[3] = pack_bf16(e[1][2], e[1][3]);
             }
-            // ---- O = O * correction + P V ----
+            // ---- O = O * correction + P V (the maximum is a whole number and seldom moves) ----
+            if (__any_sync(0xffffffffu, correction[0] != 1.f || correction[1] != 1.f)) {
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j) {
+                    o[j][0] *= correction[0]; o[j][1] *= correction[0]; o[j][2] *= correction[1]; o[j][3] *= correction[1];
+                }
+            }
 #pragma unroll
             for (int j = 0; j < D / 8; j += 2) {
-                o[j][0] *= correction[0]; o[j][1] *= correction[0]; o[j][2] *= correction[1]; o[j][3] *= correction[1];
-                o[j + 1][0] *= correction[0]; o[j + 1][1] *= correction[0]; o[j + 1][2] *= correction[1]; o[j + 1][3] *= correction[1];
-                const int m = lane >> 3;
-                const int row = warp * 16 + (m & 1) * 8 + (lane & 7);
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vs + T::offset(row, j + (m >> 1)), b0, b1, b2, b3);
+                ldmatrix_x4_trans(vs + T::offset(v_row, j + (lm >> 1)), b0, b1, b2, b3);
                 mma_bf16(o[j], pf, b0, b1);
                 mma_bf16(o[j + 1], pf, b2, b3);
             }
@@ -216,7 +254,7 @@ attention_decode_kernel(Params p) {
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             const float mw = merge_m[w * 16 + r];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - top);
+            const float f = exp2_whole(mw - top);                     // both are whole numbers (or -infinity)
             total += f * merge_l[w * 16 + r];
             value += f * merge_o[((size_t)w * 16 + r) * D + dcol];
         }
@@ -225,16 +263,74 @@ attention_decode_kernel(Params p) {
         if (p.n_splits == 1) {
             p.out[((size_t)t * p.nq + h) * D + dcol] = __float2bfloat16_rn(result);
         } else {
-            float* dst = p.partial + (((size_t)t * p.nq + h) * p.n_splits + blockIdx.z) * (D + 1);
-            dst[dcol] = result;
-            if (dcol == 0) dst[D] = top + log2f(total);
+            const size_t at = ((size_t)t * p.nq + h) * p.n_splits + blockIdx.z;
+            p.partial[at * D + dcol] = result;
+            if (dcol == 0) p.partial[(size_t)p.n_tokens * p.nq * p.n_splits * D + at] = top + log2f(total);
         }
+    }
+    if (p.n_splits == 1 || !p.counters) return;
+
+    // ---- the CTA of this token and head group that finishes last combines the ranges, in ascending
+    //      order, so the result does not depend on which CTA that is ----
+    const int used = min(p.n_splits, (pos + 1 - first + split_len - 1) / split_len);
+    int* counter = p.counters + blockIdx.x * gridDim.y + blockIdx.y;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int seen = atomicAdd(counter, 1);
+        last_flag = seen == used - 1;
+        if (seen == used - 1) *counter = 0;
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    float* weight = reinterpret_cast<float*>(smem);                   // [16][used], then [16] totals
+    float* totals = weight + 16 * used;
+    const float* lse = p.partial + (size_t)p.n_tokens * p.nq * p.n_splits * D;
+    for (int r = warp; r < heads; r += WARPS) {
+        const float* base = lse + ((size_t)t * p.nq + h0 + r) * p.n_splits;
+        float top = -INFINITY;
+        for (int s = lane; s < used; s += 32) top = fmaxf(top, __ldcg(base + s));
+        top = warp_max(top);
+        float total = 0.f;
+        for (int s = lane; s < used; s += 32) {
+            const float f = exp2f(__ldcg(base + s) - top);
+            weight[r * used + s] = f;
+            total += f;
+        }
+        total = warp_sum(total);                  // the order of this sum depends on `used` alone
+        if (lane == 0) totals[r] = total;
+    }
+    __syncthreads();
+    // 16 bytes per load, eight ranges in flight per thread: the last CTA's reads are the tail of the step
+    for (int idx = tid; idx < heads * (D / 4); idx += WARPS * 32) {
+        const int r = idx / (D / 4), c4 = idx % (D / 4);
+        const float4* base = reinterpret_cast<const float4*>(p.partial + ((size_t)t * p.nq + h0 + r) * p.n_splits * D) + c4;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s0 = 0; s0 < used; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[j] = s0 + j < used ? __ldcg(base + (size_t)(s0 + j) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = s0 + j < used ? weight[r * used + s0 + j] : 0.f;
+                acc[0] += w * v[j].x; acc[1] += w * v[j].y; acc[2] += w * v[j].z; acc[3] += w * v[j].w;
+            }
+        }
+        const float inv = 1.0f / totals[r];
+        uint2 packed;
+        packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+        packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(p.out + ((size_t)t * p.nq + h0 + r) * D + c4 * 4) = packed;
     }
 }
 
 // Combine the ranges of one (token, head): out = sum_s 2^(lse_s - L) o_s / sum_s 2^(lse_s - L).
 template <int D>
 __global__ void attention_merge_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = p.rows[blockIdx.x];
     if (t < 0) return;
     if (p.slots[t] < 0) return;
@@ -243,15 +339,16 @@ __global__ void attention_merge_kernel(Params p) {
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
     const int split_len = range_length(p, pos + 1 - first);
     const int used = min(p.n_splits, (pos + 1 - first + split_len - 1) / split_len);
-    const float* base = p.partial + ((size_t)t * p.nq + h) * p.n_splits * (D + 1);
+    const size_t at = ((size_t)t * p.nq + h) * p.n_splits;
+    const float* lse = p.partial + (size_t)p.n_tokens * p.nq * p.n_splits * D + at;
     float top = -INFINITY;
-    for (int s = 0; s < used; ++s) top = fmaxf(top, base[(size_t)s * (D + 1) + D]);
+    for (int s = 0; s < used; ++s) top = fmaxf(top, lse[s]);
     for (int dcol = threadIdx.x; dcol < D; dcol += blockDim.x) {
         float total = 0.f, value = 0.f;
         for (int s = 0; s < used; ++s) {
-            const float f = exp2f(base[(size_t)s * (D + 1) + D] - top);
+            const float f = exp2f(lse[s] - top);
             total += f;
-            value += f * base[(size_t)s * (D + 1) + dcol];
+            value += f * p.partial[(at + s) * D + dcol];
         }
         p.out[((size_t)t * p.nq + h) * D + dcol] = __float2bfloat16_rn(value / total);
     }
@@ -261,7 +358,8 @@ template <int D>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
     const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES;
     const size_t merge = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
-    const size_t smem = ring > merge ? ring : merge;
+    const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
+    const size_t smem = ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -270,13 +368,11 @@ int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
     }
     const int group = p.nq / p.nkv;
     dim3 grid(n_rows, p.nkv * ((group + 15) / 16), p.n_splits);
-    attention_decode_kernel<D><<<grid, WARPS * 32, smem, stream>>>(p);
-    if (lia_check_launch() != LIA_OK) return LIA_ERR_LAUNCH;
-    if (p.n_splits > 1) {
-        attention_merge_kernel<D><<<dim3(n_rows, p.nq), D < 128 ? D : 128, 0, stream>>>(p);
-        if (lia_check_launch() != LIA_OK) return LIA_ERR_LAUNCH;
-    }
-    return LIA_OK;
+    int rc = lia_launch(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream, p);
+    if (rc != LIA_OK) return rc;
+    if (p.n_splits > 1 && !p.counters)
+        rc = lia_launch(attention_merge_kernel<D>, dim3(n_rows, p.nq), dim3(D < 128 ? D : 128), 0, stream, p);
+    return rc;
 }
 }  // namespace
 
@@ -292,7 +388,7 @@ LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, i
 LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* rows,
                                     int n_rows, const int* positions, const int* slots, const int* block_table,
                                     int table_stride, void* out, float* partial, long long partial_floats,
-                                    int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
+                                    int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
@@ -300,11 +396,16 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
         return LIA_ERR_SIZE;
     if (n_splits > 1 && (!partial || partial_floats < lia_attention_decode_scratch_floats(n_tokens, nq, d, n_splits)))
         return LIA_ERR_SIZE;
+    if (n_splits > 1 && ((uintptr_t)partial & 15u)) return LIA_ERR_ALIGN;
     Params p;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.rows = rows; p.positions = positions; p.slots = slots; p.block_table = block_table;
     p.out = (__nv_bfloat16*)out; p.partial = partial;
-    p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
+    p.counters = n_splits <= MAX_FUSED_SPLITS ? counters : nullptr;
+    p.page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if (page_size == (1 << b)) p.page_shift = b;
+    p.n_tokens = n_tokens; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
     p.split_len = split_len; p.n_splits = n_splits; p.scale_log2 = scale * LOG2E;
     if (d == 128) return launch_decode<128>(p, n_rows, stream);
     if (d == 64) return launch_decode<64>(p, n_rows, stream);

@@ -65,7 +65,7 @@ class Engine:
         self.runtime_step = StepRuntime(self.cache, self.spec.vocab_size, self.max_batch_tokens, self.device)
         self.stats = {"steps": 0, "tokens": 0, "kernels": 0, "graph_replays": 0}
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
-        self._graphs = {}              # (tokens, wanted) -> None (seen once) | (graph, logits, kernels, generation)
+        self._graphs = {}              # (tokens, wanted, context bucket) -> None (seen once) | (graph, logits, kernels, generation)
 
     @classmethod
     def random(cls, config, seed: int = 0, **options) -> "Engine":
@@ -124,10 +124,10 @@ class Engine:
     def _replay(self, ctx) -> torch.Tensor:
         """A decode step through its CUDA graph.  The step's metadata (token ids, positions, slots,
         wanted rows) and the block tables already lie in fixed device buffers, so a graph captured for
-        (tokens, wanted) serves every later step of that shape.  The first step of a shape runs launch
+        (tokens, wanted, context bucket) serves every later step of that shape and bucket.  The first step of a shape runs launch
         by launch (it allocates the workspace); the second is captured; a reallocation of any buffer
         makes the captured graphs stale."""
-        key = (ctx.n_tokens, ctx.n_out)
+        key = (ctx.n_tokens, ctx.n_out, ctx.context_bucket)
         entry = self._graphs.get(key, False)
         if entry is False:
             self._graphs[key] = None

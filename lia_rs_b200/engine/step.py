@@ -50,6 +50,9 @@ class StepContext:
         self.error_flag = runtime.error_flag
         self.decode_only = all(count == 1 for _, _, count, _ in segments)
         self.max_context = max((start + count for _, start, count, _ in segments), default=0)
+        # the longest context of the step, rounded up to a power of two (at least 1024): kernels that cut
+        # their work by context length do it by this, and a captured step is replayed within one bucket
+        self.context_bucket = 1 << max(10, (max(self.max_context, 1) - 1).bit_length())
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         """A buffer [rows, width] of the workspace; the same name, width and type give the same
@@ -106,6 +109,15 @@ class StepRuntime:
             self._buffers[(name, dtype)] = buf
             self.generation += 1
         return buf[:numel]
+
+    def counters(self, count):
+        """`count` int32 words that are zero and that every kernel using them leaves zero."""
+        buf = self._buffers.get("counters")
+        if buf is None or buf.numel() < count:
+            buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=self.device)
+            self._buffers["counters"] = buf
+            self.generation += 1
+        return buf[:count]
 
     def logits(self, rows, vocab):
         buf = self._logits_buffer
@@ -191,12 +203,13 @@ class StepRuntime:
                                   nq, nkv, d, window, scale)
             return
         if ctx.decode_rows.numel():
-            n_splits = self.decode_splits(ctx.decode_rows.numel(), nq, nkv)
-            partial = None
+            n_splits = self.decode_splits(ctx.decode_rows.numel(), nq, nkv, ctx.context_bucket)
+            partial = counters = None
             if n_splits > 1:
                 partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
+                counters = self.counters(ctx.decode_rows.numel() * nkv * ((nq // nkv + 15) // 16))
             ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
-                                 kv.block_table, out, partial, nq, nkv, d, window, scale, 0, n_splits)
+                                 kv.block_table, out, partial, nq, nkv, d, window, scale, 0, n_splits, counters)
         if ctx.n_prefill_segments:
             per_tile = ops.attention_prefill_tokens_per_tile(nq // nkv)
             if per_tile:
@@ -207,11 +220,13 @@ class StepRuntime:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
                                       nq, nkv, d, window, scale, rows=ctx.prefill_rows)
 
-    def decode_splits(self, rows, nq, nkv):
-        """Into how many ranges the decode attention cuts each token's keys: enough to give every SM
-        about two CTAs.  It depends on the number of decoded tokens in the step alone (each token then
-        cuts its own span, on the device), so a captured step serves every context length."""
+    def decode_splits(self, rows, nq, nkv, context_bucket):
+        """Into how many ranges the decode attention cuts each token's keys: as many as fill the two
+        CTAs that an SM holds, in one round; no more than 32 (the last CTA of a token reads them all)
+        and none shorter than 256 keys at the step's longest context.  It depends on the number of
+        decoded tokens and on the context bucket alone (each token then cuts its own span, on the
+        device), so a captured step serves every step of its shape and bucket."""
         groups = nkv * ((nq // nkv + 15) // 16)
         ctas = max(1, rows * groups)
-        wanted = (2 * self.sm_count + ctas - 1) // ctas
-        return max(1, min(wanted, 64, (self.cache.max_context + 63) // 64))
+        wanted = (2 * self.sm_count) // ctas
+        return max(1, min(wanted, 32, context_bucket // 256))

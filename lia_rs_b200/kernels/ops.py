@@ -47,7 +47,7 @@ class _Signatures:
     lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                            c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_int, c_int, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
@@ -241,16 +241,22 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
-                     scale, split_len, n_splits):
+                     scale, split_len, n_splits, counters=None):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
-    `split_len` 0: every row cuts its own visible span into `n_splits` ranges."""
-    _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial)
+    `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
+    least rows * kv_heads * ceil(group / 16) words, zero before the first call; every call leaves them
+    zero) lets the CTA that finishes a token last combine its ranges; without them (or with more than
+    128 ranges) a second kernel does."""
+    _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters)
+    if counters is not None and (counters.dtype != torch.int32
+                                 or counters.numel() < rows.shape[0] * nkv * ((nq // nkv + 15) // 16)):
+        raise KernelError("attention_decode: counters must be int32, one per row and head group")
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_decode is a bfloat16 kernel")
     _check(lib().lia_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(rows), rows.shape[0], _p(positions),
                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
-                                      0 if partial is None else partial.numel(), q.shape[0], nq, nkv, d,
+                                      0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
                                       k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _stream()),
            "attention_decode")
 

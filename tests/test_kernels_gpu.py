@@ -342,8 +342,9 @@ def test_gemm_tc_refuses_what_tma_cannot_address():
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,split_len", [
     (128, 16, 2, 16, None, 128), (128, 16, 2, 16, None, 4096), (64, 16, 2, 4, None, 64), (32, 3, 1, 16, 100, 64),
-    (64, 40, 2, 8, None, 192), (128, 32, 2, 32, 700, 256), (32, 8, 8, 16, None, 64)])
-def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len):
+    (64, 40, 2, 8, None, 192), (128, 32, 2, 32, 700, 256), (32, 8, 8, 16, None, 64), (64, 6, 3, 12, None, 128)])
+@pytest.mark.parametrize("fused", [True, False])
+def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len, fused):
     """Tensor-core decode attention: groups of up to 16 query heads per kv head, ranges of keys merged,
     a far key that dominates, the window's edge, scrambled pages, rows that are skipped."""
     torch.manual_seed(d + nq)
@@ -374,9 +375,15 @@ def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len):
     n_splits = (span + split_len - 1) // split_len
     partial = torch.empty(n * nq * n_splits * (d + 1), device=DEV) if n_splits > 1 else None
     scale = 1 / math.sqrt(d)
-    ops().attention_decode(q.view(n, nq * d), kp, vp, rows, torch.tensor(positions, dtype=torch.int32, device=DEV),
-                           torch.ones(n, dtype=torch.int32, device=DEV), bt.to(DEV), out, partial, nq, nkv, d, window,
-                           scale, split_len, n_splits)
+    # fused: the CTA that finishes a token last merges its ranges (counters zero before, zero after)
+    counters = torch.zeros(n * nkv * ((nq // nkv + 15) // 16), dtype=torch.int32, device=DEV) if fused else None
+    for _ in range(2 if fused else 1):
+        out.fill_(7.0)
+        ops().attention_decode(q.view(n, nq * d), kp, vp, rows, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                               torch.ones(n, dtype=torch.int32, device=DEV), bt.to(DEV), out, partial, nq, nkv, d, window,
+                               scale, split_len, n_splits, counters)
+    if fused:
+        assert int(counters.abs().max()) == 0
     want = reference_attention(q, k, v, positions, window, scale)
     got = out.view(n, nq, d).double()
     keep = [i for i in range(n) if i != 4]

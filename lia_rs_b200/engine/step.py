@@ -119,6 +119,16 @@ class StepRuntime:
             self.generation += 1
         return buf[:count]
 
+    def stack_barrier(self):
+        """Two 64-bit words of grid-barrier state for the persistent decode kernel: zero at first, kept
+        consistent by every launch that ends well, zeroed again after a device error."""
+        buf = self._buffers.get("stack.barrier")
+        if buf is None:
+            buf = torch.zeros(2, dtype=torch.int64, device=self.device)
+            self._buffers["stack.barrier"] = buf
+            self.generation += 1
+        return buf
+
     def logits(self, rows, vocab):
         buf = self._logits_buffer
         if buf is None or buf.shape[0] < rows or buf.shape[1] != vocab:
@@ -189,6 +199,9 @@ class StepRuntime:
         if code:
             self._error_host[0] = 0
             self.error_flag.zero_()
+            for name in ("stack.barrier", "counters"):       # a kernel that gave up may have left these mid-count
+                if name in self._buffers:
+                    self._buffers[name].zero_()
             raise StepError({1: "a token id outside the vocabulary reached the embedding kernel",
                              2: "a token's block table entry has no page",
                              3: "a kernel gave up waiting on an mbarrier"}.get(code, f"device error {code}"))

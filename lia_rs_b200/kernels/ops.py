@@ -56,6 +56,12 @@ class _Signatures:
     lia_gemm_cluster_splits = [c_int, c_int, c_int, c_int, c_int]
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
+    lia_decode_stack_set_layer = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
+    lia_decode_stack_accepts = [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]
+    lia_decode_stack = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float,
+                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_int, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -287,3 +293,45 @@ def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
         raise KernelError("select_tokens: temperature needs seeds and positions")
     _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
                                    _p(positions), _p(out), rows, _stream()), "select_tokens")
+
+
+def decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits) -> bool:
+    """Whether the persistent decode kernel (csrc/decode_stack.cu) takes these sizes."""
+    return bool(lib().lia_decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits))
+
+
+def decode_stack_layers(records, device) -> torch.Tensor:
+    """The device array of per-layer records for `decode_stack`.  Each record is a dict with the tensors
+    norm1, norm2, wqkv, wo, wgu, wd, k_pages, v_pages, block_table and the numbers window, writes."""
+    fn = lib().lia_decode_stack_layer_bytes
+    fn.restype, fn.argtypes = c_int, []
+    size = int(fn())
+    host = (ctypes.c_ubyte * (size * len(records)))()
+    for index, r in enumerate(records):
+        _cuda(r["norm1"], r["norm2"], r["wqkv"], r["wo"], r["wgu"], r["wd"], r["k_pages"], r["v_pages"], r["block_table"])
+        if r["norm1"].dtype != r["norm2"].dtype or r["norm1"].dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("decode_stack: norm weights must both be bfloat16 or both 32-bit")
+        _check(lib().lia_decode_stack_set_layer(
+            ctypes.addressof(host), index, _p(r["norm1"]), _p(r["norm2"]), 1 if r["norm1"].dtype == torch.float32 else 0,
+            _p(r["wqkv"]), _p(r["wo"]), _p(r["wgu"]), _p(r["wd"]), _p(r["k_pages"]), _p(r["v_pages"]),
+            _p(r["block_table"]), r["block_table"].shape[1], r["k_pages"].shape[1], r["k_pages"].shape[0],
+            int(r["window"] or 0), 1 if r["writes"] else 0), "decode_stack_set_layer")
+    return torch.frombuffer(bytearray(host), dtype=torch.uint8).to(device)
+
+
+def decode_stack(layers, n_layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, nq, nkv, d,
+                 intermediate, rotary_dim, inv_freq, eps, residual_scale, attn_scale, n_splits, grid, error_flag=None):
+    """All `n_layers` pre-norm layers of a decode step in one persistent cooperative kernel; see
+    csrc/decode_stack.cu.  `h` [tokens, hidden] 32-bit is the residual stream, updated in place."""
+    _cuda(layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, inv_freq, error_flag)
+    tokens, hidden = h.shape
+    if h.dtype != torch.float32 or qkv.dtype != torch.float32 or attn.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
+        raise KernelError("decode_stack: 32-bit residual and q|k|v, bfloat16 attention output and activation")
+    if (qkv.shape != (tokens, (nq + 2 * nkv) * d) or attn.shape != (tokens, nq * d) or act.shape != (tokens, intermediate)
+            or partial.numel() < tokens * nq * n_splits * (d + 1) or counters.numel() < tokens * nkv
+            or barrier.numel() < 2 or barrier.dtype != torch.int64 or counters.dtype != torch.int32):
+        raise KernelError("decode_stack: a scratch buffer has the wrong shape or type")
+    _check(lib().lia_decode_stack(_p(layers), n_layers, tokens, hidden, nq, nkv, d, intermediate, rotary_dim,
+                                  _p(inv_freq), eps, residual_scale, attn_scale, _p(h), _p(qkv), _p(attn), _p(act),
+                                  _p(partial), n_splits, _p(counters), _p(positions), _p(slots), _p(barrier),
+                                  _p(error_flag), grid, _stream()), "decode_stack")

@@ -53,6 +53,13 @@ class GQAttention(Mixer):
             position.params, tensors, prefix, runtime)
         self.graph_safe = bool(self.position.graph_safe)
 
+    def stack_record(self):
+        position = self.position.stack_record()
+        if position is None:
+            return None
+        return dict(kind="gqa_attention", wqkv=self.w_qkv, wo=self.w_o, heads=self.nq, kv_heads=self.nkv,
+                    head_dim=self.d, window=self.window, attn_scale=self.scale, **position)
+
     def forward(self, ctx, x, residual, scale, kv=None, state=None):
         rt, n = self.runtime, x.shape[0]
         nq, nkv, d = self.nq, self.nkv, self.d

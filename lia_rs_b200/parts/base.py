@@ -82,6 +82,12 @@ class Part:
         self.params = params
         self.runtime = runtime
 
+    def stack_record(self):
+        """What a fused kernel over a whole stack of layers needs of this part (its kind, its prepared
+        tensors and constants), or None when the part can only be run through `forward`.  A part that
+        does not offer a record simply keeps its layer, and so the model, on the part-by-part path."""
+        return None
+
 
 class Norm(Part):
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows_index=None, out_scale: float = 1.0):
@@ -132,6 +138,11 @@ class Arrangement:
 
     def forward(self, ctx, residual: torch.Tensor, kv=None, state=None):
         raise NotImplementedError
+
+    def stack_record(self):
+        """The layer as one record for a fused kernel over a stack of layers (see `Part.stack_record`),
+        or None."""
+        return None
 
 
 MIXERS: dict = {}

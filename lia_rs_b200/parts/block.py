@@ -46,6 +46,14 @@ class PreNormBlock(Arrangement):
             spec.feed_forward.params, tensors, prefix + n["feed_forward"], runtime)
         self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
+    def stack_record(self):
+        parts = [self.norm1.stack_record(), self.mixer.stack_record(), self.norm2.stack_record(),
+                 self.feed_forward.stack_record()]
+        if any(part is None for part in parts):
+            return None
+        return dict(kind="prenorm", norm1=parts[0], mixer=parts[1], norm2=parts[2], feed_forward=parts[3],
+                    residual_scale=self.scale)
+
     def forward(self, ctx, residual, kv=None, state=None):
         x = ctx.buffer("block.x", tuple(residual.shape), self.runtime.compute_dtype)
         self.norm1.forward(ctx, residual, x)

@@ -24,6 +24,9 @@ class RotaryEncoding(PositionEncoding):
         inv = 1.0 / (theta ** (2.0 * i / self.rotary_dim))
         self.inv_freq = inv.to(torch.float32).to(runtime.device)
 
+    def stack_record(self):
+        return dict(rotary_dim=self.rotary_dim, inv_freq=self.inv_freq)
+
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d):
         self.runtime.ops.rope_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,
                                        kv.v_pages, nq, nkv, d, self.rotary_dim, self.inv_freq,
@@ -33,6 +36,9 @@ class RotaryEncoding(PositionEncoding):
 @register_position_encoding("none")
 class NoEncoding(PositionEncoding):
     graph_safe = True
+
+    def stack_record(self):
+        return dict(rotary_dim=0, inv_freq=None)
 
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d):
         self.runtime.ops.rope_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,

@@ -10,10 +10,12 @@ import torch
 
 import plain_impl
 
-# Three tiny configurations of the architecture that differ in every size and option: head counts and
+# Tiny configurations of the architecture that differ in every size and option: head counts and
 # groups (2:1, multi-query 3:1, 2:1 with a head size that is no power of two), widths, layers,
 # vocabulary, theta, eps, tied or untied head, MiniCPM's scalars present or absent, page size, and
-# (tiny-C) a sliding window on one of two layers, which gives the cache two groups of pages.
+# (tiny-C, tiny-E) a sliding window on one of two layers, which gives the cache two groups of pages.
+# tiny-D and tiny-E have the head sizes (64, 128) that the persistent decode kernel is built for, so
+# their decode steps run through it; the others decode part by part.
 TINY = {
     "tiny-A": dict(
         config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=64,
@@ -37,6 +39,21 @@ TINY = {
                     layer_types=["sliding_attention", "full_attention"], initializer_range=0.03,
                     hidden_act="silu", torch_dtype="bfloat16"),
         seed=7, page_size=4, sharpen=5.0),
+    "tiny-D": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=128,
+                    intermediate_size=264, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=64, vocab_size=500, max_position_embeddings=512, rms_norm_eps=1e-5,
+                    rope_theta=10000.0, tie_word_embeddings=True, scale_emb=4, scale_depth=1.2,
+                    dim_model_base=64, initializer_range=0.04, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=5, page_size=16, sharpen=2.0),
+    "tiny-E": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=192,
+                    intermediate_size=328, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=1,
+                    head_dim=128, vocab_size=333, max_position_embeddings=512, rms_norm_eps=2e-6,
+                    rope_theta=300000.0, tie_word_embeddings=False, sliding_window=37,
+                    layer_types=["full_attention", "sliding_attention"], initializer_range=0.03,
+                    hidden_act="silu", torch_dtype="bfloat16"),
+        seed=9, page_size=8, sharpen=1.5),
 }
 
 # `sharpen`: q and k projections are scaled up so that attention is peaked: with the usual small

@@ -186,3 +186,33 @@ def test_trace_run_program(tiny_models, tmp_path, dtype):
     helpers.assert_close(read(0), ref_a[[0, 9]], dtype, "trace step 0")
     helpers.assert_close(read(1), ref_b[[7]], dtype, "trace step 1")
     helpers.assert_close(read(2), torch.cat([ref_b[[8]], ref_a[[20]]]), dtype, "trace step 2")
+
+
+@pytest.mark.parametrize("name", ["tiny-D", "tiny-E"])
+@pytest.mark.parametrize("batch", [1, 3, 8, 11, 16])
+def test_persistent_decode_kernel_against_parts(tiny_models, name, batch):
+    """Decode steps of 1 to 16 requests with contexts from a few tokens to hundreds (several ranges of
+    keys per token, the window's edge, pages used in scrambled order), through the persistent kernel
+    over all layers and through the part-by-part kernels: the same logits beyond rounding, and both
+    close to the plain implementation."""
+    from lia_rs_b200.engine import Engine
+    model = tiny_models[name]
+    vocab = model["config"]["vocab_size"]
+    lengths = [3 + (37 * i) % 290 for i in range(batch)]
+    prompts = [helpers.random_tokens(vocab, n + 6, 100 + i) for i, n in enumerate(lengths)]
+    results = {}
+    for stack in (True, False):
+        engine = Engine(model["dir"], dtype="bfloat16", page_size=model["page_size"], max_tokens=16 * 320, max_seqs=16,
+                        max_batch_tokens=512, decode_stack=stack)
+        replay = helpers.Replayer(engine)
+        for i, (tokens, n) in enumerate(zip(prompts, lengths)):
+            replay.step([(f"r{i}", tokens[:n], [])])
+        rows = []
+        for k in range(6):
+            rows.append(replay.step([(f"r{i}", [tokens[n + k]], [0]) for i, (tokens, n) in enumerate(zip(prompts, lengths))]))
+        results[stack] = np.stack(rows)                               # [6, batch, vocab]
+        assert (engine.model.stack_steps > 0) == stack
+    for i, (tokens, n) in enumerate(zip(prompts, lengths)):
+        reference = helpers.plain_logits(model, tokens, "bfloat16")[n:n + 6]
+        helpers.assert_close(results[True][:, i], reference, "bfloat16", f"{name} request {i} through the persistent kernel")
+        helpers.assert_close(results[False][:, i], reference, "bfloat16", f"{name} request {i} part by part")

@@ -48,6 +48,7 @@ constexpr int ATTN_STAGES = 2;
 constexpr int SIDE_BYTES = 68 * 1024;          // staged activations (phases A, D) or attention tiles + q (phase B)
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int MAX_SPLITS = 32;
+constexpr int MAX_LAYERS = 64;                 // layer records kept in shared memory (a record in global memory is a cold miss per use)
 
 struct LayerParams {
     const void* norm1;               // [hidden] bf16 or f32
@@ -77,6 +78,7 @@ struct StackParams {
     const int* slots;                // [M]
     unsigned long long* barrier;     // [0]: arrivals since the state was zeroed; [1]: arrivals before this launch
     int* error_flag;
+    long long* timeline;             // optional [n_layers][16]: CTA 0's clock (ns) at the start of a layer, after each phase's parts and after each barrier
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -137,6 +139,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ float exp2_whole(float n) {       // 2^n for a whole number n <= 0 (or -infinity), exactly
     return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
 }
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ unsigned long long load_acquire(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -149,7 +156,8 @@ struct Control {
     unsigned long long barrier_base;
     int abort_flag, last_flag;
     float inv_rms[MAX_TOKENS];
-    float sumsq[COMPUTE_WARPS][MAX_TOKENS];
+    int positions[MAX_TOKENS], slots[MAX_TOKENS];
+    float2* rotation;                                    // [tokens][rotary_dim / 2] (cos, sin) of position * inv_freq: the same in every layer       // the step's metadata, read once (a miss under load costs microseconds)
 };
 
 // One product's description, the same for the producer and the consumers.
@@ -164,8 +172,11 @@ __device__ __forceinline__ void my_rows(int N, int& begin, int& end) {
     end = (int)((long long)(blockIdx.x + 1) * N / gridDim.x);
 }
 
-// ---- producer: the ring runs on across products and layers ----
+// ---- producer warp: the ring runs on across products and layers.  Lane 0 waits for the stage and
+//      announces the bytes; then every row's copy is issued by a lane of its own (issuing a bulk copy
+//      takes a thread some 80 ns, whatever its size: one thread alone would not keep up with memory) ----
 __device__ void produce(const Product& g, uint8_t* ring, Control* ctl, uint32_t& it, bool& ok) {
+    const int lane = threadIdx.x & 31;
     int begin, end;
     my_rows(g.N, begin, end);
     const int per_block = g.swiglu ? ROWS / 2 : ROWS;
@@ -174,17 +185,24 @@ __device__ void produce(const Product& g, uint8_t* ring, Control* ctl, uint32_t&
         const int rows = min(per_block, end - b0);
         for (int c = 0; c < chunks; ++c, ++it) {
             const uint32_t st = it % RING;
-            if (it >= RING && !mbar_wait_or_abort(smem_u32(&ctl->empty_bar[st]), ((it / RING) & 1u) ^ 1u, &ctl->abort_flag)) { ok = false; return; }
             const int k0 = c * CHUNK_K;
             const uint32_t bytes = (uint32_t)min(CHUNK_K, g.K - k0) * 2u;
             const uint32_t full = smem_u32(&ctl->full_bar[st]);
             const uint32_t dst = smem_u32(ring) + st * STAGE_BYTES;
-            mbar_expect_tx(full, bytes * (uint32_t)(g.swiglu ? 2 * rows : rows));
-            for (int r = 0; r < rows; ++r)
-                bulk_copy(dst + (uint32_t)(r * PITCH), g.W + (size_t)(b0 + r) * g.ldw + k0, bytes, full);
-            if (g.swiglu)
-                for (int r = 0; r < rows; ++r)
-                    bulk_copy(dst + (uint32_t)((ROWS / 2 + r) * PITCH), g.W + (size_t)(g.N + b0 + r) * g.ldw + k0, bytes, full);
+            if (lane == 0) {
+                if (it >= RING && !mbar_wait_or_abort(smem_u32(&ctl->empty_bar[st]), ((it / RING) & 1u) ^ 1u, &ctl->abort_flag)) ok = false;
+                if (ok) mbar_expect_tx(full, bytes * (uint32_t)(g.swiglu ? 2 * rows : rows));
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) return;
+            // slot of the stage -> row of W: slots 0..15 are consecutive rows; for the gated product slots
+            // 0..7 are gate rows and 8..15 the matching up rows
+            if (lane < ROWS) {
+                const int r = g.swiglu ? (lane & 7) : lane;
+                const size_t w_row = g.swiglu ? (size_t)(lane < 8 ? 0 : g.N) + b0 + r : (size_t)b0 + r;
+                if (r < rows)
+                    bulk_copy(dst + (uint32_t)(lane * PITCH), g.W + w_row * g.ldw + k0, bytes, full);
+            }
         }
     }
 }
@@ -195,19 +213,18 @@ __device__ bool grid_sync(const StackParams& p, Control* ctl, uint32_t& n_barrie
     consumer_sync();
     if (threadIdx.x == 0 && !ctl->abort_flag) {
         const unsigned long long target = ctl->barrier_base + (unsigned long long)n_barrier * gridDim.x;
-        __threadfence();
-        atomicAdd(p.barrier, 1ULL);
+        // release: what this CTA's threads wrote (ordered before by the barrier above) is visible to whoever
+        // sees the count; acquire: what the others wrote is visible after the count is seen
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p.barrier), "l"(1ULL) : "memory");
         bool arrived = false;
         for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
             if (load_acquire(p.barrier) >= target) { arrived = true; break; }
-            if ((i & 63u) == 63u && p.error_flag && *((volatile int*)p.error_flag) != 0) break;
-            __nanosleep(32);
+            if ((i & 1023u) == 1023u && p.error_flag && *((volatile int*)p.error_flag) != 0) break;
         }
         if (!arrived) {
             ctl->abort_flag = 1;
             if (p.error_flag) atomicExch(p.error_flag, 3);
         }
-        __threadfence();
     }
     consumer_sync();
     return ctl->abort_flag == 0;
@@ -218,9 +235,9 @@ enum { EPI_STORE_SCALED = 0, EPI_ACCUM = 1, EPI_SWIGLU_SCALED = 2 };
 // ---- consumers: one product.  X comes from shared memory (x_smem, row pitch x_pitch bytes) or from
 //      global memory (x_global, row stride ldx elements).  8 warps share each chunk of K. ----
 template <int NT, int EPI>
-__device__ void consume(const StackParams& p, const Product& g, const uint8_t* ring, Control* ctl, float* sums,
+__device__ void consume(const StackParams& p, const Product& g, const uint8_t* ring, Control* ctl, float* sums_base,
                         const uint8_t* x_smem, int x_pitch, const __nv_bfloat16* x_global, int ldx,
-                        void* out, int ldo, uint32_t& it, bool& ok) {
+                        void* out, int ldo, uint32_t& it, uint32_t& n_block, bool& ok) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, t = lane & 3;
     int begin, end;
@@ -232,9 +249,14 @@ __device__ void consume(const StackParams& p, const Product& g, const uint8_t* r
         const int rows = min(per_block, end - b0);
         const bool row_lo = g.swiglu ? gq < rows : gq < rows;
         const bool row_hi = g.swiglu ? gq < rows : gq + 8 < rows;
-        float acc[NT][4];
+        // one accumulator per group of 32 k that the warp takes in a chunk: the tensor-core instructions of a
+        // chunk then do not wait for one another (a chain of eight costs more than the whole chunk's copies)
+        constexpr int CHAINS = CHUNK_K / 32 / COMPUTE_WARPS;
+        float part[CHAINS][NT][4];
 #pragma unroll
-        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int i = 0; i < CHAINS; ++i)
+#pragma unroll
+            for (int n = 0; n < NT; ++n) part[i][n][0] = part[i][n][1] = part[i][n][2] = part[i][n][3] = 0.f;
         for (int c = 0; c < chunks; ++c, ++it) {
             const uint32_t st = it % RING;
             const int k0 = c * CHUNK_K;
@@ -271,8 +293,8 @@ __device__ void consume(const StackParams& p, const Product& g, const uint8_t* r
                         }
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
-                            mma16816(acc[n], lo.x, hi.x, lo.y, hi.y, xf[i][n].x, xf[i][n].y);
-                            mma16816(acc[n], lo.z, hi.z, lo.w, hi.w, xf[i][n].z, xf[i][n].w);
+                            mma16816(part[i][n], lo.x, hi.x, lo.y, hi.y, xf[i][n].x, xf[i][n].y);
+                            mma16816(part[i][n], lo.z, hi.z, lo.w, hi.w, xf[i][n].z, xf[i][n].w);
                         }
                     }
                 }
@@ -280,7 +302,22 @@ __device__ void consume(const StackParams& p, const Product& g, const uint8_t* r
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->empty_bar[st]));
         }
-        // the eight warps' partial sums meet in shared memory, added in warp order
+        float acc[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float total = part[0][n][e];
+#pragma unroll
+                for (int i = 1; i < CHAINS; ++i) total += part[i][n][e];
+                acc[n][e] = total;
+            }
+        // the eight warps' partial sums meet in shared memory, added in warp order; with up to 8 tokens two
+        // buffers take turns, so one barrier per block is enough (the next block's barrier shields this
+        // block's readers); with more tokens there is room for one buffer only, and a second barrier
+        constexpr int SUMS_BUFFERS = NT == 1 ? 2 : 1;
+        float* sums = sums_base + (size_t)(n_block % SUMS_BUFFERS) * COMPUTE_WARPS * ROWS * SUMS_W;
+        ++n_block;
         float* mine = sums + (size_t)warp * ROWS * SUMS_W;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
@@ -317,42 +354,72 @@ __device__ void consume(const StackParams& p, const Product& g, const uint8_t* r
                 else *dst = __ldcg(dst) + p.residual_scale * total;
             }
         }
-        consumer_sync();       // the sums are free for the next block
+        if (SUMS_BUFFERS == 1) consumer_sync();
     }
 }
 
-// ---- phases A and D: stage bf16(x * w_norm) in shared memory, 1/sqrt(mean(x^2) + eps) per token ----
+// Where in the side region a norm's weight is kept while the staged activations use its front (null: no room).
+__device__ __forceinline__ uint8_t* norm_slot(const StackParams& p, int weight_f32, uint8_t* side, int pitch) {
+    const int bytes = p.H * (weight_f32 ? 4 : 2);
+    return (long long)p.M * pitch + bytes <= SIDE_BYTES ? side + SIDE_BYTES - bytes : nullptr;
+}
+// Ask for a norm's weight a phase before it is needed: it comes from HBM, and a miss issued while the
+// weights stream waits behind them for microseconds.  All consumer threads call this; stage_normed waits.
+__device__ void fetch_norm(const StackParams& p, const void* weight, int weight_f32, uint8_t* side, int pitch) {
+    uint8_t* slot = norm_slot(p, weight_f32, side, pitch);
+    if (slot) {
+        const int bytes = p.H * (weight_f32 ? 4 : 2);
+        for (int at = threadIdx.x * 16; at < bytes; at += CONSUMERS * 16)
+            cp_async_16(smem_u32(slot + at), reinterpret_cast<const uint8_t*>(weight) + at, true);
+    }
+    cp_async_commit();
+}
+
+// ---- phases A and D: stage bf16(x * w_norm) in shared memory, 1/sqrt(mean(x^2) + eps) per token.
+//      A warp owns a token: its loads are all in flight at once and the sum needs no other warp;
+//      the order of the additions depends on the width alone. ----
 __device__ void stage_normed(const StackParams& p, const void* weight, int weight_f32, uint8_t* side, int pitch, Control* ctl) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quads = p.H >> 2;
-    for (int token = 0; token < p.M; ++token) {
-        const float* row = p.h + (size_t)token * p.H;
+    const uint8_t* slot = norm_slot(p, weight_f32, side, pitch);
+    cp_async_wait<0>();                                  // fetch_norm's copies
+    consumer_sync();
+    if (slot) weight = slot;
+    for (int token = warp; token < p.M; token += COMPUTE_WARPS) {
+        const float4* row = reinterpret_cast<const float4*>(p.h + (size_t)token * p.H);
         float sum = 0.f;
-        for (int q = threadIdx.x; q < quads; q += CONSUMERS) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(row) + q);
-            float4 w;
-            if (weight_f32) {
-                w = reinterpret_cast<const float4*>(weight)[q];
-            } else {
-                const uint2 raw = reinterpret_cast<const uint2*>(weight)[q];
-                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                w = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+        for (int q0 = 0; q0 < quads; q0 += 32 * 8) {
+            float4 v[8], w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {               // the norm's weight and the row: sixteen loads in flight
+                const int q = q0 + j * 32 + lane;
+                if (q < quads) {
+                    if (weight_f32) {
+                        w[j] = reinterpret_cast<const float4*>(weight)[q];
+                    } else {
+                        const uint2 raw = reinterpret_cast<const uint2*>(weight)[q];
+                        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                        w[j] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+                    }
+                    v[j] = __ldcg(row + q);
+                } else {
+                    v[j] = w[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
-            sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum); sum = fmaf(v.z, v.z, sum); sum = fmaf(v.w, v.w, sum);
-            uint2 packed;
-            packed.x = pack_bf16(v.x * w.x, v.y * w.y);
-            packed.y = pack_bf16(v.z * w.z, v.w * w.w);
-            *reinterpret_cast<uint2*>(side + (size_t)token * pitch + (size_t)q * 8) = packed;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int q = q0 + j * 32 + lane;
+                if (q >= quads) continue;
+                sum = fmaf(v[j].x, v[j].x, sum); sum = fmaf(v[j].y, v[j].y, sum);
+                sum = fmaf(v[j].z, v[j].z, sum); sum = fmaf(v[j].w, v[j].w, sum);
+                uint2 packed;
+                packed.x = pack_bf16(v[j].x * w[j].x, v[j].y * w[j].y);
+                packed.y = pack_bf16(v[j].z * w[j].z, v[j].w * w[j].w);
+                *reinterpret_cast<uint2*>(side + (size_t)token * pitch + (size_t)q * 8) = packed;
+            }
         }
         sum = warp_sum(sum);
-        if (lane == 0) ctl->sumsq[warp][token] = sum;
-    }
-    consumer_sync();
-    if (threadIdx.x < p.M) {
-        float total = 0.f;
-#pragma unroll
-        for (int w = 0; w < COMPUTE_WARPS; ++w) total += ctl->sumsq[w][threadIdx.x];
-        ctl->inv_rms[threadIdx.x] = 1.0f / sqrtf(total / (float)p.H + p.eps);
+        if (lane == 0) ctl->inv_rms[token] = 1.0f / sqrtf(sum / (float)p.H + p.eps);
     }
     consumer_sync();
 }
@@ -365,11 +432,11 @@ __device__ void attend(const StackParams& p, const LayerParams& L, uint8_t* side
     constexpr int ROWS_PER_PASS = ATTN_WARPS * 32 / CHUNKS;
     constexpr int PASSES = TILE_KEYS / ROWS_PER_PASS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int slot = p.slots[token];
+    const int slot = ctl->slots[token];
     if (slot < 0) return;
     const int group = p.nq / p.nkv;                         // at most 16 (checked on the host)
     const int h0 = kvh * group;
-    const int pos = p.positions[token];
+    const int pos = ctl->positions[token];
     const int first = (L.window > 0 && pos - L.window + 1 > 0) ? pos - L.window + 1 : 0;
     const int span = pos + 1 - first;
     const int split_len = ((span + p.n_splits - 1) / p.n_splits + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
@@ -381,45 +448,8 @@ __device__ void attend(const StackParams& p, const LayerParams& L, uint8_t* side
     const int width = (p.nq + 2 * p.nkv) * D;
     const float* row = p.qkv + (size_t)token * width;
     const int half = p.rotary_dim / 2;
+    const float2* rotation = ctl->rotation + (size_t)token * half;
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(side + ATTN_STAGES * 2 * T::BYTES);      // [16][D]
-
-    // ---- rotary positions for this group's queries; the CTA of the last range also appends k and v ----
-    for (int w = tid; w < 16 * D; w += ATTN_WARPS * 32) q_s[w] = __float2bfloat16_rn(0.f);
-    attention_sync();
-    for (int w = tid; w < group * half; w += ATTN_WARPS * 32) {
-        const int r = w / half, i = w % half;
-        float sn, cs;
-        sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-        const float a = __ldcg(row + (h0 + r) * D + i), b = __ldcg(row + (h0 + r) * D + i + half);
-        q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
-        q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
-    }
-    for (int w = tid; w < group * (D - p.rotary_dim); w += ATTN_WARPS * 32) {
-        const int r = w / (D - p.rotary_dim), i = p.rotary_dim + w % (D - p.rotary_dim);
-        q_s[r * D + i] = __float2bfloat16_rn(__ldcg(row + (h0 + r) * D + i));
-    }
-    if (key_end == pos + 1 && L.write_kv) {
-        const int page_index = L.page_shift >= 0 ? pos >> L.page_shift : pos / L.page_size;
-        const int page = table[page_index];
-        if (page < 0 || page >= L.num_pages) {
-            if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
-        } else {
-            const size_t cache_row = (((size_t)page * L.page_size + (pos - page_index * L.page_size)) * p.nkv + kvh) * D;
-            const float* k = row + (p.nq + kvh) * D;
-            const float* v = row + (p.nq + p.nkv + kvh) * D;
-            for (int i = tid; i < half; i += ATTN_WARPS * 32) {
-                float sn, cs;
-                sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-                const float a = __ldcg(k + i), b = __ldcg(k + i + half);
-                L.k_pages[cache_row + i] = __float2bfloat16_rn(a * cs - b * sn);
-                L.k_pages[cache_row + i + half] = __float2bfloat16_rn(b * cs + a * sn);
-            }
-            for (int i = p.rotary_dim + tid; i < D; i += ATTN_WARPS * 32) L.k_pages[cache_row + i] = __float2bfloat16_rn(__ldcg(k + i));
-            for (int i = tid; i < D; i += ATTN_WARPS * 32) L.v_pages[cache_row + i] = __float2bfloat16_rn(__ldcg(v + i));
-            __threadfence();                                  // the row is read back below, past L1
-        }
-    }
-    attention_sync();
 
     // ---- tiles of 64 keys through two stages ----
     const uint32_t smem_base = smem_u32(side);
@@ -446,8 +476,56 @@ __device__ void attend(const StackParams& p, const LayerParams& L, uint8_t* side
         }
     };
     const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
-    load_tile(0, key_begin);
-    cp_async_commit();
+    // keys of earlier steps depend on nothing this step computes: the first tile is asked for before the
+    // positions are encoded, unless it holds the key that is appended below
+    const bool early = key_begin + TILE_KEYS <= pos;
+    if (early) {
+        load_tile(0, key_begin);
+        cp_async_commit();
+    }
+
+    // ---- rotary positions for this group's queries; the CTA of the last range also appends k and v ----
+    for (int w = tid; w < 16 * D; w += ATTN_WARPS * 32) q_s[w] = __float2bfloat16_rn(0.f);
+    attention_sync();
+    for (int w = tid; w < group * half; w += ATTN_WARPS * 32) {
+        const int r = w / half, i = w % half;
+        const float2 rot = rotation[i];
+        const float cs = rot.x, sn = rot.y;
+        const float a = __ldcg(row + (h0 + r) * D + i), b = __ldcg(row + (h0 + r) * D + i + half);
+        q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
+        q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+    }
+    for (int w = tid; w < group * (D - p.rotary_dim); w += ATTN_WARPS * 32) {
+        const int r = w / (D - p.rotary_dim), i = p.rotary_dim + w % (D - p.rotary_dim);
+        q_s[r * D + i] = __float2bfloat16_rn(__ldcg(row + (h0 + r) * D + i));
+    }
+    if (key_end == pos + 1 && L.write_kv) {
+        const int page_index = L.page_shift >= 0 ? pos >> L.page_shift : pos / L.page_size;
+        const int page = table[page_index];
+        if (page < 0 || page >= L.num_pages) {
+            if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+        } else {
+            const size_t cache_row = (((size_t)page * L.page_size + (pos - page_index * L.page_size)) * p.nkv + kvh) * D;
+            const float* k = row + (p.nq + kvh) * D;
+            const float* v = row + (p.nq + p.nkv + kvh) * D;
+            for (int i = tid; i < half; i += ATTN_WARPS * 32) {
+                const float2 rot = rotation[i];
+                const float cs = rot.x, sn = rot.y;
+                const float a = __ldcg(k + i), b = __ldcg(k + i + half);
+                L.k_pages[cache_row + i] = __float2bfloat16_rn(a * cs - b * sn);
+                L.k_pages[cache_row + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+            }
+            for (int i = p.rotary_dim + tid; i < D; i += ATTN_WARPS * 32) L.k_pages[cache_row + i] = __float2bfloat16_rn(__ldcg(k + i));
+            for (int i = tid; i < D; i += ATTN_WARPS * 32) L.v_pages[cache_row + i] = __float2bfloat16_rn(__ldcg(v + i));
+            __threadfence();                                  // the row is read back below, past L1
+        }
+    }
+    attention_sync();
+
+    if (!early) {
+        load_tile(0, key_begin);
+        cp_async_commit();
+    }
 
     uint32_t qf[D / 16][4];
     {
@@ -644,9 +722,16 @@ decode_stack_kernel(StackParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     uint8_t* side = smem + RING * STAGE_BYTES;
-    float* sums = reinterpret_cast<float*>(side + SIDE_BYTES);                       // [8][16][NT * 8 + 1]
-    Control* ctl = reinterpret_cast<Control*>(side + SIDE_BYTES + COMPUTE_WARPS * ROWS * (NT * 8 + 1) * 4);
+    float* sums = reinterpret_cast<float*>(side + SIDE_BYTES);                       // [2 or 1][8][16][NT * 8 + 1]
+    Control* ctl = reinterpret_cast<Control*>(side + SIDE_BYTES + (NT == 1 ? 2 : 1) * COMPUTE_WARPS * ROWS * (NT * 8 + 1) * 4);
+    LayerParams* layers = reinterpret_cast<LayerParams*>(reinterpret_cast<uint8_t*>(ctl) + ((sizeof(Control) + 15) / 16) * 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const int words = p.n_layers * (int)(sizeof(LayerParams) / 4);
+        const int* src = reinterpret_cast<const int*>(p.layers);
+        int* dst = reinterpret_cast<int*>(layers);
+        for (int i = threadIdx.x; i < words; i += THREADS) dst[i] = src[i];
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < RING; ++i) {
@@ -659,26 +744,38 @@ decode_stack_kernel(StackParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (threadIdx.x < p.M) {
+        ctl->positions[threadIdx.x] = p.positions[threadIdx.x];
+        ctl->slots[threadIdx.x] = p.slots[threadIdx.x];
+    }
+    float2* rotation = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(layers) + (size_t)MAX_LAYERS * sizeof(LayerParams));
+    if (threadIdx.x == 0) ctl->rotation = rotation;
+    for (int w = threadIdx.x; w < p.M * (p.rotary_dim / 2); w += THREADS) {
+        const int token = w / (p.rotary_dim / 2), i = w % (p.rotary_dim / 2);
+        float sn, cs;
+        sincosf((float)p.positions[token] * p.inv_freq[i], &sn, &cs);
+        rotation[w] = make_float2(cs, sn);
+    }
     __syncthreads();
     const int qkv_rows = (p.nq + 2 * p.nkv) * D;
 
     if (warp == COMPUTE_WARPS) {
         // ---- the producer: every weight of every layer, in the order of use ----
-        if (lane == 0) {
+        {
             uint32_t it = 0;
             bool ok = true;
-            for (int l = 0; l < p.n_layers && ok; ++l) {
-                const LayerParams& L = p.layers[l];
-                const Product a = {L.wqkv, qkv_rows, p.H, p.H, 0};
-                const Product c = {L.wo, p.H, p.nq * D, p.nq * D, 0};
-                const Product d = {L.wgu, p.I, p.H, p.H, 1};
-                const Product e = {L.wd, p.H, p.I, p.I, 0};
-                produce(a, ring, ctl, it, ok);
-                if (ok) produce(c, ring, ctl, it, ok);
-                if (ok) produce(d, ring, ctl, it, ok);
-                if (ok) produce(e, ring, ctl, it, ok);
-            }
-            if (!ok) {
+            const int n_products = 4 * p.n_layers;
+            auto product = [&](int index) {
+                const LayerParams& L = layers[index >> 2];
+                switch (index & 3) {
+                    case 0: return Product{L.wqkv, qkv_rows, p.H, p.H, 0};
+                    case 1: return Product{L.wo, p.H, p.nq * D, p.nq * D, 0};
+                    case 2: return Product{L.wgu, p.I, p.H, p.H, 1};
+                    default: return Product{L.wd, p.H, p.I, p.I, 0};
+                }
+            };
+            for (int index = 0; index < n_products && ok; ++index) produce(product(index), ring, ctl, it, ok);
+            if (!ok && lane == 0) {
                 // a consumer gave up (or a copy never came): wait, bounded, for the copies still in flight
                 if (!ctl->abort_flag && p.error_flag) atomicExch(p.error_flag, 3);
                 for (uint32_t i = it > RING ? it - RING : 0; i < it; ++i)
@@ -688,18 +785,24 @@ decode_stack_kernel(StackParams p) {
         return;
     }
 
-    uint32_t it = 0, n_barrier = 0;
+    uint32_t it = 0, n_barrier = 0, n_block = 0;
     bool ok = true;
     const int x_pitch = p.H * 2 + 64;
+    fetch_norm(p, layers[0].norm1, layers[0].norm_f32, side, x_pitch);
     for (int l = 0; l < p.n_layers; ++l) {
-        const LayerParams& L = p.layers[l];
+        const LayerParams& L = layers[l];
+        long long* mark = (p.timeline && blockIdx.x == 0 && threadIdx.x == 0) ? p.timeline + l * 16 : nullptr;
+        if (mark) mark[0] = global_ns();
         // ---- A: qkv = rmsnorm(x) Wqkv^T ----
         stage_normed(p, L.norm1, L.norm_f32, side, x_pitch, ctl);
+        if (mark) mark[1] = global_ns();
         {
             const Product a = {L.wqkv, qkv_rows, p.H, p.H, 0};
-            consume<NT, EPI_STORE_SCALED>(p, a, ring, ctl, sums, side, x_pitch, nullptr, 0, p.qkv, qkv_rows, it, ok);
+            consume<NT, EPI_STORE_SCALED>(p, a, ring, ctl, sums, side, x_pitch, nullptr, 0, p.qkv, qkv_rows, it, n_block, ok);
         }
+        if (mark) mark[2] = global_ns();
         if (!ok || !grid_sync(p, ctl, n_barrier)) break;
+        if (mark) mark[3] = global_ns();
         // ---- B: positions, cache append, attention ----
         if (warp < ATTN_WARPS) {
             const int items = p.M * p.nkv * p.n_splits;
@@ -708,26 +811,37 @@ decode_stack_kernel(StackParams p) {
                 attend<D>(p, L, side, ctl, token, kvh, split);
             }
         }
+        if (mark) mark[4] = global_ns();
         if (!grid_sync(p, ctl, n_barrier)) break;
+        if (mark) mark[5] = global_ns();
         // ---- C: x += s * attn Wo^T ----
+        fetch_norm(p, L.norm2, L.norm_f32, side, x_pitch);        // for phase D; the side region is free from here to there
         {
             const Product c = {L.wo, p.H, p.nq * D, p.nq * D, 0};
-            consume<NT, EPI_ACCUM>(p, c, ring, ctl, sums, nullptr, 0, p.attn, p.nq * D, p.h, p.H, it, ok);
+            consume<NT, EPI_ACCUM>(p, c, ring, ctl, sums, nullptr, 0, p.attn, p.nq * D, p.h, p.H, it, n_block, ok);
         }
+        if (mark) mark[6] = global_ns();
         if (!ok || !grid_sync(p, ctl, n_barrier)) break;
+        if (mark) mark[7] = global_ns();
         // ---- D: act = swiglu(rmsnorm(x) Wgu^T) ----
         stage_normed(p, L.norm2, L.norm_f32, side, x_pitch, ctl);
+        if (mark) mark[8] = global_ns();
         {
             const Product d = {L.wgu, p.I, p.H, p.H, 1};
-            consume<NT, EPI_SWIGLU_SCALED>(p, d, ring, ctl, sums, side, x_pitch, nullptr, 0, p.act, p.I, it, ok);
+            consume<NT, EPI_SWIGLU_SCALED>(p, d, ring, ctl, sums, side, x_pitch, nullptr, 0, p.act, p.I, it, n_block, ok);
         }
+        if (mark) mark[9] = global_ns();
         if (!ok || !grid_sync(p, ctl, n_barrier)) break;
+        if (mark) mark[10] = global_ns();
         // ---- E: x += s * act Wd^T ----
+        if (l + 1 < p.n_layers) fetch_norm(p, layers[l + 1].norm1, layers[l + 1].norm_f32, side, x_pitch);
         {
             const Product e = {L.wd, p.H, p.I, p.I, 0};
-            consume<NT, EPI_ACCUM>(p, e, ring, ctl, sums, nullptr, 0, p.act, p.I, p.h, p.H, it, ok);
+            consume<NT, EPI_ACCUM>(p, e, ring, ctl, sums, nullptr, 0, p.act, p.I, p.h, p.H, it, n_block, ok);
         }
+        if (mark) mark[11] = global_ns();
         if (!ok || !grid_sync(p, ctl, n_barrier)) break;
+        if (mark) mark[12] = global_ns();
     }
     if (!ok && threadIdx.x == 0) {
         ctl->abort_flag = 1;
@@ -740,7 +854,8 @@ decode_stack_kernel(StackParams p) {
 
 template <int D, int NT>
 int launch_stack(const StackParams& p, int grid, cudaStream_t stream) {
-    const size_t smem = (size_t)RING * STAGE_BYTES + SIDE_BYTES + (size_t)COMPUTE_WARPS * ROWS * (NT * 8 + 1) * 4 + sizeof(Control) + 128;
+    const size_t smem = (size_t)RING * STAGE_BYTES + SIDE_BYTES + (size_t)(NT == 1 ? 2 : 1) * COMPUTE_WARPS * ROWS * (NT * 8 + 1) * 4 + ((sizeof(Control) + 15) / 16) * 16 +
+                        (size_t)MAX_LAYERS * sizeof(LayerParams) + (size_t)MAX_TOKENS * 64 * sizeof(float2) + 128;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(decode_stack_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -789,6 +904,9 @@ LIA_EXPORT int lia_decode_stack_set_layer(void* host_layers, int index, const vo
     return LIA_OK;
 }
 
+// Most layers one launch takes.
+LIA_EXPORT int lia_decode_stack_max_layers() { return MAX_LAYERS; }
+
 // Whether the stack kernel takes these sizes (1) or the caller must use the per-part kernels (0).
 LIA_EXPORT int lia_decode_stack_accepts(int M, int H, int nq, int nkv, int d, int I, int rotary_dim, int n_splits) {
     if (M < 1 || M > MAX_TOKENS || (d != 64 && d != 128)) return 0;
@@ -805,12 +923,15 @@ LIA_EXPORT int lia_decode_stack_accepts(int M, int H, int nq, int nkv, int d, in
 // `layers`: device array of records written with lia_decode_stack_set_layer.  `barrier`: two 64-bit words,
 // zero before the first launch (and again after an error).  `counters`: M * nkv int32, zero.
 // `partial`: M * nq * n_splits * (d + 1) floats, 16-byte aligned.  `grid`: CTAs, at most one per SM.
+// `timeline` (optional, n_layers * 16 64-bit words): CTA 0 writes its clock in ns at the start of each layer,
+// after the parts of each phase and after each grid barrier (13 marks), for profiling.
 LIA_EXPORT int lia_decode_stack(const void* layers, int n_layers, int M, int H, int nq, int nkv, int d, int I,
                                 int rotary_dim, const float* inv_freq, float eps, float residual_scale, float attn_scale,
                                 float* h, float* qkv, void* attn, void* act, float* partial, int n_splits, int* counters,
                                 const int* positions, const int* slots, unsigned long long* barrier, int* error_flag,
-                                int grid, cudaStream_t stream) {
+                                long long* timeline, int grid, cudaStream_t stream) {
     if (n_layers <= 0 || M <= 0) return LIA_OK;
+    if (n_layers > MAX_LAYERS) return LIA_ERR_SIZE;
     if (!lia_decode_stack_accepts(M, H, nq, nkv, d, I, rotary_dim, n_splits) || grid <= 0) return LIA_ERR_SIZE;
     if (rotary_dim > 0 && !inv_freq) return LIA_ERR_SIZE;
     if (((uintptr_t)h & 15u) || ((uintptr_t)attn & 15u) || ((uintptr_t)act & 15u) || ((uintptr_t)partial & 15u)) return LIA_ERR_ALIGN;
@@ -819,7 +940,7 @@ LIA_EXPORT int lia_decode_stack(const void* layers, int n_layers, int M, int H, 
     p.rotary_dim = rotary_dim; p.n_splits = n_splits; p.eps = eps; p.residual_scale = residual_scale;
     p.scale_log2 = attn_scale * LOG2E; p.inv_freq = inv_freq; p.h = h; p.qkv = qkv;
     p.attn = (__nv_bfloat16*)attn; p.act = (__nv_bfloat16*)act; p.partial = partial; p.counters = counters;
-    p.positions = positions; p.slots = slots; p.barrier = barrier; p.error_flag = error_flag;
+    p.positions = positions; p.slots = slots; p.barrier = barrier; p.error_flag = error_flag; p.timeline = timeline;
     if (d == 128) return M <= 8 ? launch_stack<128, 1>(p, grid, stream) : launch_stack<128, 2>(p, grid, stream);
     return M <= 8 ? launch_stack<64, 1>(p, grid, stream) : launch_stack<64, 2>(p, grid, stream);
 }

@@ -136,9 +136,14 @@ gemm_skinny_kernel(Args a) {
     } else {
         // ---- eight warps: each takes every eighth group of 32 k ----
         const int g = lane >> 2, t = lane & 3;
-        float acc[NT][4];
+        // one accumulator per group of 32 k that the warp takes in a chunk: the tensor-core instructions of a
+        // chunk then do not wait for one another
+        constexpr int CHAINS = CHUNK_K / 32 / COMPUTE_WARPS;
+        float part[CHAINS][NT][4];
 #pragma unroll
-        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int i = 0; i < CHAINS; ++i)
+#pragma unroll
+            for (int n = 0; n < NT; ++n) part[i][n][0] = part[i][n][1] = part[i][n][2] = part[i][n][3] = 0.f;
         const bool row_lo = weight_row<MODE>(a, blockIdx.x, g) >= 0, row_hi = weight_row<MODE>(a, blockIdx.x, g + 8) >= 0;
         pdl_wait();                                   // X comes from the kernel ahead
         bool ok = true;
@@ -176,8 +181,8 @@ gemm_skinny_kernel(Args a) {
                     }
 #pragma unroll
                     for (int n = 0; n < NT; ++n) {
-                        mma_bf16(acc[n], lo.x, hi.x, lo.y, hi.y, xf[i][n].x, xf[i][n].y);
-                        mma_bf16(acc[n], lo.z, hi.z, lo.w, hi.w, xf[i][n].z, xf[i][n].w);
+                        mma_bf16(part[i][n], lo.x, hi.x, lo.y, hi.y, xf[i][n].x, xf[i][n].y);
+                        mma_bf16(part[i][n], lo.z, hi.z, lo.w, hi.w, xf[i][n].z, xf[i][n].w);
                     }
                 }
             }
@@ -185,6 +190,16 @@ gemm_skinny_kernel(Args a) {
             if (lane == 0 && c + a.stages < a.chunks) mbar_arrive(smem_u32(&empty_bar[st]));
         }
         if (!ok && lane == 0 && a.error_flag) atomicExch(a.error_flag, 3);
+        float acc[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float total = part[0][n][e];
+#pragma unroll
+                for (int i = 1; i < CHAINS; ++i) total += part[i][n][e];
+                acc[n][e] = total;
+            }
         // c0, c1: row g, tokens 2t, 2t+1; c2, c3: row g+8
 #pragma unroll
         for (int n = 0; n < NT; ++n) {

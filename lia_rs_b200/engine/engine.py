@@ -29,13 +29,14 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
-                 max_context: int = None, cuda_graphs: bool = True, decode_stack: bool = True, _random=None):
+                 max_context: int = None, cuda_graphs: bool = True, decode_stack: bool = None, _random=None):
         """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
         `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
         `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
         request (default: the model's max_position_embeddings); `decode_stack`: run decode steps of
         up to 16 tokens through the persistent kernel over all layers when the model's parts allow it
-        (csrc/decode_stack.cu; the environment variable LIA_DECODE_STACK=0 turns it off too);
+        (csrc/decode_stack.cu).  Off unless asked for (here, or with the environment variable
+        LIA_DECODE_STACK=1): on a B200 the part-by-part kernels under a CUDA graph are some 8% faster;
         `cuda_graphs`: capture decode steps
         (every entry a single token) in CUDA graphs, one per batch size, and replay them."""
         if dtype not in _DTYPES:
@@ -69,7 +70,9 @@ class Engine:
                                   self.device)
         self.runtime_step = StepRuntime(self.cache, self.spec.vocab_size, self.max_batch_tokens, self.device)
         self.stats = {"steps": 0, "tokens": 0, "kernels": 0, "graph_replays": 0}
-        self.model.use_decode_stack = bool(decode_stack) and os.environ.get("LIA_DECODE_STACK", "1") != "0"
+        if decode_stack is None:
+            decode_stack = os.environ.get("LIA_DECODE_STACK", "0") == "1"
+        self.model.use_decode_stack = bool(decode_stack)
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
         self._graphs = {}              # (tokens, wanted, context bucket) -> None (seen once) | (graph, logits, kernels, generation)
 

@@ -61,7 +61,7 @@ class _Signatures:
     lia_decode_stack_accepts = [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]
     lia_decode_stack = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float,
                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                        c_void_p, c_void_p, c_int, c_void_p]
+                        c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -320,7 +320,8 @@ def decode_stack_layers(records, device) -> torch.Tensor:
 
 
 def decode_stack(layers, n_layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, nq, nkv, d,
-                 intermediate, rotary_dim, inv_freq, eps, residual_scale, attn_scale, n_splits, grid, error_flag=None):
+                 intermediate, rotary_dim, inv_freq, eps, residual_scale, attn_scale, n_splits, grid, error_flag=None,
+                 timeline=None):
     """All `n_layers` pre-norm layers of a decode step in one persistent cooperative kernel; see
     csrc/decode_stack.cu.  `h` [tokens, hidden] 32-bit is the residual stream, updated in place."""
     _cuda(layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, inv_freq, error_flag)
@@ -334,4 +335,4 @@ def decode_stack(layers, n_layers, h, qkv, attn, act, partial, counters, positio
     _check(lib().lia_decode_stack(_p(layers), n_layers, tokens, hidden, nq, nkv, d, intermediate, rotary_dim,
                                   _p(inv_freq), eps, residual_scale, attn_scale, _p(h), _p(qkv), _p(attn), _p(act),
                                   _p(partial), n_splits, _p(counters), _p(positions), _p(slots), _p(barrier),
-                                  _p(error_flag), grid, _stream()), "decode_stack")
+                                  _p(error_flag), _p(timeline), grid, _stream()), "decode_stack")

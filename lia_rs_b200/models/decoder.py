@@ -109,6 +109,7 @@ class DecodeStack:
         self.records = None
         self.layers_device = None
         self.tables = None
+        self.timeline = None          # int64 [layers, 16] on the device: set it to have CTA 0 write its phase times
         self.usable = self._collect()
 
     def _collect(self) -> bool:
@@ -153,7 +154,7 @@ class DecodeStack:
 
     def plan(self, ctx, runtime_step):
         """The number of key ranges if this step can run through the kernel, else None."""
-        if not (self.usable and ctx.decode_only):
+        if not (self.usable and ctx.decode_only) or len(self.records) > 64:      # the kernel keeps 64 layer records
             return None
         mixer, ffn = self.records[0]["mixer"], self.records[0]["feed_forward"]
         n_splits = self.splits(ctx, runtime_step)
@@ -193,7 +194,7 @@ class DecodeStack:
         rt.ops.decode_stack(self._layer_array(ctx), len(self.records), h, qkv, attn, act, partial, counters,
                             ctx.positions, ctx.slots, step.stack_barrier(), nq, nkv, d, ffn["intermediate"],
                             mixer["rotary_dim"], mixer["inv_freq"], first["norm1"]["eps"], first["residual_scale"],
-                            mixer["attn_scale"], n_splits, step.sm_count, ctx.error_flag)
+                            mixer["attn_scale"], n_splits, step.sm_count, ctx.error_flag, self.timeline)
 
 
 class DecoderModel:

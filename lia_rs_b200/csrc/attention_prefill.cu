@@ -17,7 +17,17 @@ using namespace attn;
 
 namespace {
 constexpr int ROWS = 64;                 // query rows per CTA
-constexpr int PREFILL_STAGES = 2;
+constexpr int PREFILL_STAGES = 3;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^n for a whole number n <= 0 (or -infinity), exactly.
+__device__ __forceinline__ float exp2_whole(float n) {
+    return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
+}
 
 struct PrefillParams {
     const __nv_bfloat16* q;          // [tokens, nq, D]
@@ -27,7 +37,7 @@ struct PrefillParams {
     const int* slots;                // [tokens]
     const int* block_table;          // [slots, table_stride]
     __nv_bfloat16* out;              // [tokens, nq, D]
-    int n_segments, table_stride, nq, nkv, page_size, window, tokens_per_tile;
+    int n_segments, table_stride, nq, nkv, page_size, page_shift, window, tokens_per_tile;
     float scale_log2;
 };
 
@@ -36,7 +46,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(PrefillParams p) {
     using T = Tile<D>;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = p.nq / p.nkv;
     const int kvh = blockIdx.y;
 
@@ -53,8 +63,10 @@ attention_prefill_kernel(PrefillParams p) {
     if (seg >= p.n_segments) return;
     const int tok0 = tile * p.tokens_per_tile;
     const int tok_count = min(p.tokens_per_tile, seg_count - tok0);
+    pdl_launch_dependents();
     const int slot = p.slots[q_offset];
     if (slot < 0) return;
+    pdl_wait();                                   // q and this step's keys come from the kernel ahead
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     const int pos_first = seg_start + tok0, pos_last = pos_first + tok_count - 1;
     const int key_begin = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
@@ -71,7 +83,7 @@ attention_prefill_kernel(PrefillParams p) {
         const int tok = r / group, head = r % group;
         row_ok[i] = tok < tok_count;
         const int token_index = q_offset + tok0 + (row_ok[i] ? tok : 0);
-        row_pos[i] = row_ok[i] ? pos_first + tok : -1;
+        row_pos[i] = row_ok[i] ? pos_first + tok : 0x3fffffff;      // a row beyond the portion sees every key and is never written
         const size_t at = ((size_t)token_index * p.nq + kvh * group + head) * D;
         q_row[i] = p.q + at;
         o_row[i] = p.out + at;
@@ -88,23 +100,41 @@ attention_prefill_kernel(PrefillParams p) {
             qf[kk][3] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q_row[1] + col + 8) : 0u;
         }
     }
-    // the warp's rows see keys up to this position; tiles beyond it are skipped by the warp
-    int warp_last = max(row_pos[0], row_pos[1]);
+    // the warp's rows see keys up to warp_last (tiles beyond it are skipped by the warp); a tile whose keys all
+    // lie at or before warp_first, and inside every row's window, needs no mask
+    int warp_last = max(row_ok[0] ? row_pos[0] : -1, row_ok[1] ? row_pos[1] : -1), warp_first = min(row_pos[0], row_pos[1]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, o));
+    for (int o = 16; o > 0; o >>= 1) {
+        warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, o));
+        warp_first = min(warp_first, __shfl_xor_sync(0xffffffffu, warp_first, o));
+    }
 
+    // ---- loading a tile: CHUNKS lanes share a key row; lane j of them looks up the row of pass j ----
+    constexpr int CHUNKS = T::CHUNKS;
+    constexpr int ROWS_PER_PASS = WARPS * 32 / CHUNKS;
+    constexpr int PASSES = TILE_KEYS / ROWS_PER_PASS;
+    static_assert(ROWS_PER_PASS % 8 == 0 && PASSES <= CHUNKS, "the swizzle repeats every 8 rows; one lane per pass");
     const uint32_t smem_base = smem_u32(smem);
+    const int sub = lane / CHUNKS, piece = lane % CHUNKS;
+    const int row_base = warp * (32 / CHUNKS) + sub;
+    const uint32_t piece_offset = T::offset(row_base, piece);
     auto load_tile = [&](int stage, int key0) {
-        const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES, vs = ks + T::BYTES;
-        for (int id = tid; id < TILE_KEYS * T::CHUNKS; id += WARPS * 32) {
-            const int r = id / T::CHUNKS, c = id % T::CHUNKS;
-            const int key = key0 + r;
-            const bool valid = key < key_end;
-            size_t row = 0;
-            if (valid) row = (size_t)table[key / p.page_size] * p.page_size + key % p.page_size;
-            const size_t src = (row * p.nkv + kvh) * D + c * 8;
-            cp_async_16(ks + T::offset(r, c), p.k_pages + src, valid);
-            cp_async_16(vs + T::offset(r, c), p.v_pages + src, valid);
+        const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES + piece_offset, vs = ks + T::BYTES;
+        int my_row = -1;
+        if (piece < PASSES) {
+            const int key = key0 + row_base + piece * ROWS_PER_PASS;
+            if (key < key_end) {
+                const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+                my_row = table[page] * p.page_size + (key - page * p.page_size);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const int r = __shfl_sync(0xffffffffu, my_row, sub * CHUNKS + i);
+            const bool valid = r >= 0;
+            const size_t src = ((size_t)(valid ? r : 0) * p.nkv + kvh) * D + piece * 8;
+            cp_async_16(ks + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.k_pages + src, valid);
+            cp_async_16(vs + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.v_pages + src, valid);
         }
     };
 
@@ -149,30 +179,35 @@ attention_prefill_kernel(PrefillParams p) {
                 mma_bf16(s[np * 2 + 1], qf[kk], b2, b3);
             }
         }
-        // ---- scale and mask by each row's own position and window ----
+        // ---- mask by each row's own position and window, where the tile needs it ----
+        if (key0 + TILE_KEYS - 1 > warp_first || (p.window > 0 && key0 <= warp_last - p.window)) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+                    const int pos = row_pos[i >> 1];
+                    bool visible = key <= pos;
+                    if (p.window > 0) visible = visible && key > pos - p.window;
+                    if (!visible) s[nt][i] = -INFINITY;
+                }
+        }
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
-                const int pos = row_pos[i >> 1];
-                bool visible = key <= pos;
-                if (p.window > 0) visible = visible && key > pos - p.window;
-                const float v = visible ? s[nt][i] * p.scale_log2 : -INFINITY;
-                s[nt][i] = v;
-                tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
-            }
+        for (int nt = 0; nt < 8; ++nt) {
+            tile_max[0] = fmaxf(tile_max[0], fmaxf(s[nt][0], s[nt][1]));
+            tile_max[1] = fmaxf(tile_max[1], fmaxf(s[nt][2], s[nt][3]));
+        }
         float correction[2], safe_max[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
             // whole-number reference point: see attention_decode.cu
-            const float new_max = fmaxf(row_max[r], ceilf(tile_max[r]));
+            const float new_max = fmaxf(row_max[r], ceilf(tile_max[r] * p.scale_log2));
             // a row that has seen no key yet keeps maximum -inf; exponentials are taken against 0 then
             safe_max[r] = new_max == -INFINITY ? 0.f : new_max;
-            correction[r] = exp2f(row_max[r] - safe_max[r]);
+            correction[r] = exp2_whole(row_max[r] - safe_max[r]);
             row_max[r] = new_max;
             row_sum[r] *= correction[r];
         }
@@ -180,13 +215,15 @@ attention_prefill_kernel(PrefillParams p) {
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                s[nt][i] = exp2f(s[nt][i] - safe_max[i >> 1]);
+                s[nt][i] = ex2_approx(fmaf(s[nt][i], p.scale_log2, -safe_max[i >> 1]));
                 row_sum[i >> 1] += s[nt][i];
             }
+        if (__any_sync(0xffffffffu, correction[0] != 1.f || correction[1] != 1.f)) {
 #pragma unroll
-        for (int j = 0; j < D / 8; ++j) {
-            o[j][0] *= correction[0]; o[j][1] *= correction[0];
-            o[j][2] *= correction[1]; o[j][3] *= correction[1];
+            for (int j = 0; j < D / 8; ++j) {
+                o[j][0] *= correction[0]; o[j][1] *= correction[0];
+                o[j][2] *= correction[1]; o[j][3] *= correction[1];
+            }
         }
         // ---- O += P V: four k-steps of 16 keys ----
 #pragma unroll
@@ -234,8 +271,7 @@ int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
             return LIA_ERR_LAUNCH;
         configured = true;
     }
-    attention_prefill_kernel<D><<<dim3(n_tiles, p.nkv), WARPS * 32, smem, stream>>>(p);
-    return lia_check_launch();
+    return lia_launch(attention_prefill_kernel<D>, dim3(n_tiles, p.nkv), dim3(WARPS * 32), smem, stream, p);
 }
 }  // namespace
 
@@ -259,6 +295,9 @@ LIA_EXPORT int lia_attention_prefill(const void* q, const void* k_pages, const v
     p.segments = segments; p.slots = slots; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
     p.n_segments = n_segments; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E;
+    p.page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if (page_size == (1 << b)) p.page_shift = b;
     if (d == 128) return launch_prefill<128>(p, n_tiles, stream);
     if (d == 64) return launch_prefill<64>(p, n_tiles, stream);
     if (d == 32) return launch_prefill<32>(p, n_tiles, stream);

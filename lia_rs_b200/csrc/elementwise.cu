@@ -218,11 +218,14 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
         cache_row = ((size_t)(cache_ok ? page : 0) * page_size + pos % page_size) * nkv * d;
     }
     const int rot_heads = nq + nkv;
+    // sine and cosine of the token's angles, once for all heads
+    extern __shared__ float rotation[];                  // [half] cosines, then [half] sines
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &rotation[half + i], &rotation[i]);
+    __syncthreads();
     // rotated part: one work item per (head, i < half)
     for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
         const int head = w / half, i = w % half;
-        float s, c;
-        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float c = rotation[i], s = rotation[half + i];
         const float a = row[head * d + i], b = row[head * d + i + half];
         const float ra = a * c - b * s, rb = b * c + a * s;
         if (head < nq) {
@@ -263,7 +266,7 @@ LIA_EXPORT int lia_rope_kv_write(const float* qkv, const int* positions, const i
         return LIA_ERR_SIZE;
     const int threads = 256;
 #define LIA_ROPE(T)                                                                                          \
-    return lia_launch(rope_kv_kernel<T, T>, dim3(n_tokens), dim3(threads), 0, stream, qkv, positions, slots, \
+    return lia_launch(rope_kv_kernel<T, T>, dim3(n_tokens), dim3(threads), (size_t)rotary_dim * sizeof(float), stream, qkv, positions, slots, \
                       block_table, table_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, nq, nkv, d,  \
                       rotary_dim, inv_freq, page_size, num_pages, write_kv, error_flag)
     if (dtype == LIA_BF16) LIA_ROPE(__nv_bfloat16);

@@ -57,7 +57,8 @@ struct Shape {
     int splits;               // K ranges per tile
     int f_tiles, t_tiles;
     int acc_cols;             // TMEM columns of one accumulator buffer
-    int tmem_cols;            // TMEM columns allocated (both buffers, a power of two >= 32)
+    int tmem_cols;            // TMEM columns allocated (all buffers, a power of two >= 32)
+    int acc_buffers;          // 2: the epilogue drains one accumulator while the next unit fills the other; 1: they take turns
     int via_tma;              // 1: the epilogue leaves through shared memory and TMA
     int ldo;
     float alpha;
@@ -187,8 +188,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int it = 0, n_unit = 0;
         for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
             const Unit u = unit_at(s, index);
-            const int buf = n_unit & 1;
-            if (!mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)n_unit >> 1) & 1u) ^ 1u)) { ok = false; break; }
+            const int buf = s.acc_buffers == 2 ? (n_unit & 1) : 0;
+            const uint32_t use = s.acc_buffers == 2 ? (uint32_t)n_unit >> 1 : (uint32_t)n_unit;
+            if (!mbar_wait(smem_u32(&acc_empty[buf]), (use & 1u) ^ 1u)) { ok = false; break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(buf * s.acc_cols);
             for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
@@ -218,10 +220,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int n_unit = 0, chunk_count = 0;
         for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
             const Unit u = unit_at(s, index);
-            const int buf = n_unit & 1;
+            const int buf = s.acc_buffers == 2 ? (n_unit & 1) : 0;
+            const uint32_t use = s.acc_buffers == 2 ? (uint32_t)n_unit >> 1 : (uint32_t)n_unit;
             const int f = u.f0 + group * 32 + lane;
             const bool empty_range = u.kb_end <= u.kb_begin;           // cannot happen (splits <= kblocks)
-            if (!empty_range && !mbar_wait(smem_u32(&acc_full[buf]), ((uint32_t)n_unit >> 1) & 1u)) { ok = false; break; }
+            if (!empty_range && !mbar_wait(smem_u32(&acc_full[buf]), use & 1u)) { ok = false; break; }
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(group * 32) << 16) + (uint32_t)(buf * s.acc_cols);
 
@@ -379,17 +382,24 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
     Plan p;
     p.f_tiles = (N + TILE_F - 1) / TILE_F;
     const int cap = swiglu ? 128 : 256;          // two accumulators side by side, twice, must fit 512 columns
-    if (M <= cap / 2 || swiglu) {
+    if (swiglu && M > 128) {
+        // Many tokens: 256 per tile, gate and up side by side fill all 512 columns, so there is one buffer and
+        // the epilogue and the next tile take turns.  Per K block the tile then reads 64 KB of operands for
+        // twice the flops of the 128-wide tile's 48 KB: the product is bound by what shared memory takes in.
+        p.n_tile = 256;
+    } else if (M <= cap / 2 || swiglu) {
         p.n_tile = 16;
         while (p.n_tile < M && p.n_tile < cap) p.n_tile *= 2;
     } else {
-        // many tokens: 256 or 128 per tile, whichever leaves the SMs less idle in the last round
+        // many tokens: the tile width (a multiple of 32, the epilogue's step, up to 256) that leaves the SMs least idle: rounds of
+        // tiles times the time of one, which grows with the width plus a fixed cost; ties go to the wider
+        // tile (fewer bytes through shared memory per flop)
         long long best = -1;
         p.n_tile = 256;
-        for (int n = 256; n >= 128; n /= 2) {
+        for (int n = 256; n >= 96; n -= 32) {
             const long long tiles = (long long)p.f_tiles * ((M + n - 1) / n);
             const long long rounds = (tiles + sm_count - 1) / sm_count;
-            const long long cost = rounds * (n + 24);                   // + a tile's fixed cost
+            const long long cost = rounds * (n + 24);
             if (best < 0 || cost < best) { best = cost; p.n_tile = n; }
         }
     }
@@ -445,7 +455,8 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
     s.acc_cols = swiglu ? 2 * plan.n_tile : plan.n_tile;
-    s.tmem_cols = pow2_at_least(2 * s.acc_cols);
+    s.acc_buffers = 2 * s.acc_cols <= 512 ? 2 : 1;
+    s.tmem_cols = pow2_at_least(s.acc_buffers * s.acc_cols);
     s.ldo = ldo; s.alpha = alpha; s.error_flag = error_flag;
     s.counters = reinterpret_cast<int*>(scratch);
     s.partial = scratch ? scratch + COUNTER_WORDS : nullptr;

@@ -30,6 +30,14 @@ struct Params {
     int* counters;                   // [n_rows, gridDim.y], zero between launches; null: ranges are merged by a second kernel
     int n_tokens, table_stride, nq, nkv, page_size, page_shift, window, split_len, n_splits;
     float scale_log2;                // softmax scale * log2(e)
+    // position encoding and cache append in the same kernel (qkv non-null): q is taken from qkv, rotated here;
+    // the CTA of a token's last range also rotates its new key and appends key and value to their page
+    const float* qkv;                // [tokens, (nq + 2 nkv) D] 32-bit
+    const float* inv_freq;           // [rotary_dim / 2]
+    __nv_bfloat16* k_write;          // the pages again, writable
+    __nv_bfloat16* v_write;
+    int rotary_dim, write_kv, num_pages;
+    int* error_flag;
 };
 
 constexpr int MAX_FUSED_SPLITS = 128;     // ranges that the last CTA of a token can merge (its weights lie in shared memory)
@@ -110,19 +118,86 @@ attention_decode_kernel(Params p) {
     };
 
     const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+    // With the append in this kernel, the tile that holds the token's own key (the last of the last range) is
+    // asked for only after that key has been written; it is the last tile, so the order of the groups stands.
+    const bool appends = p.qkv != nullptr && key_end == pos + 1;
+    int deferred = -1;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < n_tiles) {
-            if (key_begin + (s + 1) * TILE_KEYS > pos) pdl_wait();       // the tile holds the key this step wrote
-            load_tile(s, key_begin + s * TILE_KEYS);
+            const bool holds_new = key_begin + (s + 1) * TILE_KEYS > pos;
+            if (holds_new && appends) {
+                deferred = s;
+            } else {
+                if (holds_new) pdl_wait();                               // the tile holds the key this step wrote
+                load_tile(s, key_begin + s * TILE_KEYS);
+            }
         }
-        cp_async_commit();
+        if (deferred < 0) cp_async_commit();
     }
     pdl_wait();
 
     // ---- Q fragments: rows = heads (row r -> head h0 + r), zero beyond `heads` ----
     uint32_t qf[D / 16][4];
-    {
+    if (p.qkv) {
+        __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * 2 * T::BYTES);       // [16][D]
+        const int width = (p.nq + 2 * p.nkv) * D;
+        const float* row = p.qkv + (size_t)t * width;
+        const int half = p.rotary_dim / 2;
+        float2* rotation = reinterpret_cast<float2*>(q_s + 16 * D);      // [half] (cos, sin) of the token's angles
+        for (int i = tid; i < half; i += WARPS * 32) {
+            float sn, cs;
+            sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+            rotation[i] = make_float2(cs, sn);
+        }
+        for (int w = tid; w < (16 - heads) * D; w += WARPS * 32) q_s[heads * D + w] = __float2bfloat16_rn(0.f);
+        __syncthreads();
+        for (int w = tid; w < heads * half; w += WARPS * 32) {
+            const int r = w / half, i = w % half;
+            const float cs = rotation[i].x, sn = rotation[i].y;
+            const float a = row[(h0 + r) * D + i], b = row[(h0 + r) * D + i + half];
+            q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
+            q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+        }
+        for (int w = tid; w < heads * (D - p.rotary_dim); w += WARPS * 32) {
+            const int r = w / (D - p.rotary_dim), i = p.rotary_dim + w % (D - p.rotary_dim);
+            q_s[r * D + i] = __float2bfloat16_rn(row[(h0 + r) * D + i]);
+        }
+        if (appends && p.write_kv && blockIdx.y % groups16 == 0) {
+            const int page_index = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+            const int page = table[page_index];
+            if (page < 0 || page >= p.num_pages) {
+                if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+            } else {
+                const size_t cache_row = (((size_t)page * p.page_size + (pos - page_index * p.page_size)) * p.nkv + kvh) * D;
+                const float* k = row + (p.nq + kvh) * D;
+                const float* v = row + (p.nq + p.nkv + kvh) * D;
+                for (int i = tid; i < half; i += WARPS * 32) {
+                    const float cs = rotation[i].x, sn = rotation[i].y;
+                    const float a = k[i], b = k[i + half];
+                    p.k_write[cache_row + i] = __float2bfloat16_rn(a * cs - b * sn);
+                    p.k_write[cache_row + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+                }
+                for (int i = p.rotary_dim + tid; i < D; i += WARPS * 32) p.k_write[cache_row + i] = __float2bfloat16_rn(k[i]);
+                for (int i = tid; i < D; i += WARPS * 32) p.v_write[cache_row + i] = __float2bfloat16_rn(v[i]);
+            }
+            __threadfence();                                              // the row is read back below, past L1
+        }
+        __syncthreads();
+        if (deferred >= 0) {
+            load_tile(deferred, key_begin + deferred * TILE_KEYS);
+            for (int s = deferred; s < STAGES - 1; ++s) cp_async_commit();
+        }
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int col = kk * 16 + c;
+            qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + r0 * D + col);
+            qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * D + col);
+            qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_s + r0 * D + col + 8);
+            qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * D + col + 8);
+        }
+    } else {
         const int r0 = lane >> 2, c = (lane & 3) * 2;
         const __nv_bfloat16* base = p.q + ((size_t)t * p.nq + h0) * D;
 #pragma unroll
@@ -356,7 +431,7 @@ __global__ void attention_merge_kernel(Params p) {
 
 template <int D>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
-    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES;
+    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4;       // the tiles, the rotated queries, the angles' cosines and sines
     const size_t merge = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
     const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
     const size_t smem = ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
@@ -381,6 +456,9 @@ LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, i
     return n_splits > 1 ? (long long)n_tokens * nq * n_splits * (d + 1) : 0;
 }
 
+// `qkv` non-null: q is ignored; the kernel takes the queries from the 32-bit q|k|v rows, applies the rotary
+// encoding (rotary_dim leading elements of each head; 0: none) and, when `write_kv`, the CTA of each token's last
+// range rotates the token's key and appends key and value to the page of its position before reading them.
 // Decode attention for the tokens listed in `rows` (indices into the step's batch), bfloat16 only,
 // head_dim 32, 64 or 128 (other sizes: LIA_ERR_SIZE; the caller falls back to the generic kernel).
 // `n_splits` ranges of `split_len` keys each must cover the longest visible span among the rows;
@@ -389,7 +467,8 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
                                     int n_rows, const int* positions, const int* slots, const int* block_table,
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
-                                    int split_len, int n_splits, cudaStream_t stream) {
+                                    int split_len, int n_splits, const float* qkv, const float* inv_freq, int rotary_dim,
+                                    int write_kv, int num_pages, int* error_flag, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
@@ -402,6 +481,11 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
     p.rows = rows; p.positions = positions; p.slots = slots; p.block_table = block_table;
     p.out = (__nv_bfloat16*)out; p.partial = partial;
     p.counters = n_splits <= MAX_FUSED_SPLITS ? counters : nullptr;
+    if (qkv && (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim > 0 && !inv_freq) || nq / nkv > 16))
+        return LIA_ERR_SIZE;             // with more than 16 heads per kv head two CTAs would share the appended key
+    p.qkv = qkv; p.inv_freq = inv_freq; p.rotary_dim = rotary_dim; p.write_kv = write_kv; p.num_pages = num_pages;
+    p.k_write = (__nv_bfloat16*)const_cast<void*>(k_pages); p.v_write = (__nv_bfloat16*)const_cast<void*>(v_pages);
+    p.error_flag = error_flag;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -72,6 +72,12 @@ class StepContext:
         """out = causal attention of q over the cache `kv`, for the tokens of this step."""
         self.runtime.attention(self, q, kv, out, nq, nkv, d, window, scale)
 
+    def attention_with_rotary(self, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq) -> bool:
+        """For a step of single decoded tokens: rotary encoding of q and k (rotary_dim 0: none), append of
+        k and v to `kv`, and attention, in one kernel.  Returns False, having done nothing, when the step
+        or the sizes are not the ones that kernel takes; the caller then encodes and attends separately."""
+        return self.runtime.attention_with_rotary(self, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq)
+
 
 class StepRuntime:
     def __init__(self, cache, vocab_size: int, max_batch_tokens: int, device):
@@ -232,6 +238,20 @@ class StepRuntime:
             else:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
                                       nq, nkv, d, window, scale, rows=ctx.prefill_rows)
+
+    def attention_with_rotary(self, ctx, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq) -> bool:
+        if not (ctx.decode_only and out.dtype == torch.bfloat16 and kv.k_pages.dtype == torch.bfloat16
+                and d in ops.DECODE_HEAD_DIMS and nq // nkv <= 16):
+            return False
+        n_splits = self.decode_splits(ctx.n_tokens, nq, nkv, ctx.context_bucket)
+        partial = counters = None
+        if n_splits > 1:
+            partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
+            counters = self.counters(ctx.n_tokens * nkv)
+        ops.attention_decode(None, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table,
+                             out, partial, nq, nkv, d, window, scale, 0, n_splits, counters, qkv=qkv,
+                             inv_freq=inv_freq, rotary_dim=rotary_dim, write_kv=kv.writes, error_flag=ctx.error_flag)
+        return True
 
     def decode_splits(self, rows, nq, nkv, context_bucket):
         """Into how many ranges the decode attention cuts each token's keys: as many as fill the two

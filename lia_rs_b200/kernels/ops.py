@@ -48,7 +48,7 @@ class _Signatures:
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_void_p]
+                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
     lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -247,14 +247,22 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
-                     scale, split_len, n_splits, counters=None):
+                     scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
+                     error_flag=None):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
     least rows * kv_heads * ceil(group / 16) words, zero before the first call; every call leaves them
     zero) lets the CTA that finishes a token last combine its ranges; without them (or with more than
-    128 ranges) a second kernel does."""
-    _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters)
+    128 ranges) a second kernel does.  With `qkv` (32-bit q|k|v rows of the step, at most 16 query heads per
+    kv head) `q` may be None: the kernel takes the queries from `qkv`, applies the rotary encoding
+    (`inv_freq`, `rotary_dim`; 0: none) and, if `write_kv`, appends each token's key and value to the cache
+    itself, so no separate position-encoding kernel runs."""
+    _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters, qkv, inv_freq, error_flag)
+    if qkv is not None:
+        if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
+            raise KernelError("attention_decode: qkv must be 32-bit q|k|v rows")
+        q = out if q is None else q             # unused by the kernel then; only its element type is checked
     if counters is not None and (counters.dtype != torch.int32
                                  or counters.numel() < rows.shape[0] * nkv * ((nq // nkv + 15) // 16)):
         raise KernelError("attention_decode: counters must be int32, one per row and head group")
@@ -263,7 +271,8 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
     _check(lib().lia_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(rows), rows.shape[0], _p(positions),
                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
                                       0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
-                                      k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _stream()),
+                                      k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
+                                      int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], _p(error_flag), _stream()),
            "attention_decode")
 
 

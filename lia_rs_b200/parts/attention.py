@@ -65,8 +65,11 @@ class GQAttention(Mixer):
         nq, nkv, d = self.nq, self.nkv, self.d
         qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * d), torch.float32)
         linear(rt, STORE, x, self.w_qkv, qkv)
-        q = ctx.buffer("attn.q", (n, nq * d), rt.compute_dtype)
-        self.position.encode_and_store(ctx, qkv, q, kv, nq, nkv, d)
         o = ctx.buffer("attn.o", (n, nq * d), rt.compute_dtype)
-        ctx.attention(q, kv, o, nq, nkv, d, self.window, self.scale)
+        rotary = self.position.stack_record()           # a rotary (or no) encoding can ride in the decode attention kernel
+        if rotary is None or not ctx.attention_with_rotary(qkv, kv, o, nq, nkv, d, self.window, self.scale,
+                                                           rotary["rotary_dim"], rotary["inv_freq"]):
+            q = ctx.buffer("attn.q", (n, nq * d), rt.compute_dtype)
+            self.position.encode_and_store(ctx, qkv, q, kv, nq, nkv, d)
+            ctx.attention(q, kv, o, nq, nkv, d, self.window, self.scale)
         linear(rt, ACCUM, o, self.w_o, residual, scale)

@@ -475,3 +475,63 @@ def test_attention_prefill_portions(d, nq, nkv, page_size, window):
     assert float((got[:150] - want_b).abs().max()) <= limit
     assert float((got[150:] - want_a).abs().max()) <= limit
     assert float((got[-1, 0] - va[far, 0].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("d,nq,nkv,page_size,window,rotary_dim,n_splits", [
+    (128, 16, 2, 16, None, 128, 5), (64, 12, 3, 8, None, 64, 1), (32, 3, 1, 16, 50, 16, 3), (128, 4, 4, 32, 300, 0, 2),
+    (64, 32, 2, 4, None, 32, 7)])
+def test_attention_decode_with_rotary_and_append(d, nq, nkv, page_size, window, rotary_dim, n_splits):
+    """The decode attention kernel that also encodes positions and appends the token's key and value,
+    against the two separate kernels: the same pages afterwards, the same output (each token at another
+    position, one at position 0, one at a page's first slot, one at its last)."""
+    o = ops()
+    torch.manual_seed(d + nq + rotary_dim)
+    positions = [0, 1, page_size - 1, page_size, 63, 64, 65, 200, 333]
+    n = len(positions)
+    T = 340
+    k_old = (torch.randn(n, T, nkv, d, device=DEV) * 0.5).to(torch.bfloat16)
+    v_old = torch.randn(n, T, nkv, d, device=DEV).to(torch.bfloat16)
+    blocks = (T + page_size - 1) // page_size
+    num_pages = n * blocks + 3
+    order = np.random.default_rng(3).permutation(num_pages)
+    kp = torch.zeros(num_pages, page_size, nkv, d, device=DEV, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    bt = torch.full((n, blocks + 1), -1, dtype=torch.int32)
+    for r in range(n):
+        pages_k, table = paged(k_old[r], page_size, num_pages, order[r * blocks:(r + 1) * blocks])
+        pages_v, _ = paged(v_old[r], page_size, num_pages, order[r * blocks:(r + 1) * blocks])
+        used = table.long()
+        kp[used] = pages_k[used]
+        vp[used] = pages_v[used]
+        bt[r, :blocks] = table
+    bt = bt.to(DEV)
+    qkv = torch.randn(n, (nq + 2 * nkv) * d, device=DEV)
+    pos = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    rows = torch.arange(n, dtype=torch.int32, device=DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rotary_dim, 2, dtype=torch.float64) / max(rotary_dim, 1)))).float().to(DEV) if rotary_dim else None
+    scale = 1 / math.sqrt(d)
+
+    def scratch():
+        partial = torch.empty(n * nq * n_splits * (d + 1), device=DEV) if n_splits > 1 else None
+        counters = torch.zeros(n * nkv, dtype=torch.int32, device=DEV) if n_splits > 1 else None
+        return partial, counters
+
+    # separately
+    k1, v1 = kp.clone(), vp.clone()
+    q1 = torch.empty(n, nq * d, device=DEV, dtype=torch.bfloat16)
+    o.rope_kv_write(qkv, pos, slots, bt, q1, k1, v1, nq, nkv, d, rotary_dim, inv)
+    out1 = torch.empty(n, nq * d, device=DEV, dtype=torch.bfloat16)
+    partial, counters = scratch()
+    o.attention_decode(q1, k1, v1, rows, pos, slots, bt, out1, partial, nq, nkv, d, window, scale, 0, n_splits, counters)
+    # in one kernel
+    k2, v2 = kp.clone(), vp.clone()
+    out2 = torch.empty(n, nq * d, device=DEV, dtype=torch.bfloat16)
+    partial, counters = scratch()
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.attention_decode(None, k2, v2, rows, pos, slots, bt, out2, partial, nq, nkv, d, window, scale, 0, n_splits, counters,
+                       qkv=qkv, inv_freq=inv, rotary_dim=rotary_dim, write_kv=True, error_flag=flag)
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(out1, out2)

@@ -60,13 +60,42 @@ TINY = {
 # random weights every key gets nearly the same probability and a wrong or missing key would hide.
 
 
+# Few layers at the widths of the real family sizes (2B-, 0.5B- and 8B-class: hidden, heads, groups, head size,
+# intermediate and MiniCPM's scalars as published; a vocabulary cut to a few thousand, no power of two, so
+# that the plain implementation on the CPU stays a matter of seconds).  They put the kernels at the sizes the
+# benchmark runs: rows of 4 to 32 KB, 16 query heads per kv head, K of 16384.
+REAL_WIDTHS = {
+    "width-2B": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048,
+                    intermediate_size=6144, num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=128, vocab_size=7001, max_position_embeddings=4096, rms_norm_eps=1e-5,
+                    rope_theta=10000.0, tie_word_embeddings=True, scale_emb=12, scale_depth=1.4,
+                    dim_model_base=256, initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=0, page_size=16, sharpen=2.0),
+    "width-0.5B": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=1024,
+                    intermediate_size=4096, num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=64, vocab_size=5003, max_position_embeddings=4096, rms_norm_eps=1e-5,
+                    rope_theta=10000.0, tie_word_embeddings=True, scale_emb=12, scale_depth=1.4,
+                    dim_model_base=256, initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=4, page_size=16, sharpen=2.0),
+    "width-8B": dict(
+        config=dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=4096,
+                    intermediate_size=16384, num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=2,
+                    head_dim=128, vocab_size=3001, max_position_embeddings=4096, rms_norm_eps=1e-5,
+                    rope_theta=10000.0, tie_word_embeddings=False, scale_emb=12, scale_depth=1.4,
+                    dim_model_base=256, initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"),
+        seed=5, page_size=16, sharpen=2.0),
+}
+
+
 def make_model(folder: str, name: str) -> dict:
     """Write the folder through the package's random-weights mode, then sharpen q/k and rewrite.
     Returns {dir, config (dict), weights (dict by checkpoint name, as stored), page_size}."""
     from safetensors.torch import load_file, save_file
 
     from lia_rs_b200 import LlamaConfig, write_random_model
-    entry = TINY[name]
+    entry = TINY[name] if name in TINY else REAL_WIDTHS[name]
     write_random_model(LlamaConfig.from_dict(entry["config"]), folder, seed=entry["seed"])
     path = os.path.join(folder, "model.safetensors")
     weights = load_file(path)            # the safetensors library, independent of the package's reader

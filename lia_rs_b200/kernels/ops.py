@@ -54,6 +54,9 @@ class _Signatures:
     lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_int, c_void_p, c_void_p]
     lia_gemm_cluster_splits = [c_int, c_int, c_int, c_int, c_int]
+    lia_gemm_pair = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                     c_int, c_void_p, c_void_p]
+    lia_gemm_pair_accepts = [c_int, c_int, c_int, c_int, c_int]
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
     lia_decode_stack_set_layer = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -204,6 +207,29 @@ def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None):
     _, sms = _device_scratch(a.device)
     _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                   out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
+
+
+def gemm_pair_accepts(mode, a, w, out) -> bool:
+    """Whether the two-CTA tcgen05 kernel takes this product: what the tcgen05 kernel takes, many tokens,
+    and an output that TMA can address (16-byte aligned base and rows)."""
+    if not gemm_tc_accepts(mode, a, w, out) or out.stride(1) != 1:
+        return False
+    if out.data_ptr() % 16 or (out.stride(0) * out.element_size()) % 16:
+        return False
+    _, sms = _device_scratch(a.device)
+    return bool(lib().lia_gemm_pair_accepts(mode, a.shape[0], out.shape[1], a.shape[1], sms))
+
+
+def gemm_pair(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on pairs of SMs (tcgen05 with cta_group::2); see
+    csrc/gemm_pair.cu."""
+    M, K = a.shape
+    N = out.shape[1]
+    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _, sms = _device_scratch(a.device)
+    _check(lib().lia_gemm_pair(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                               out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_pair")
 
 
 SKINNY_MAX_TOKENS = 32

@@ -1,0 +1,410 @@
+// Causal attention of prompt portions over the paged bfloat16 cache on the 5th-generation tensor cores.
+//
+// A CTA owns 128 query rows = (128 / g) consecutive tokens x the g query heads of one kv head, and walks
+// the keys its rows can see, 128 at a time:
+//     S = Q K^T     tcgen05.mma, M 128 (rows), N 128 (keys), K head_dim, accumulator in TMEM
+//     softmax       one thread per row reads its 128 scores with tcgen05.ld (no shuffles: a row lives in one
+//                   TMEM lane), running maximum (a whole number of base-2 logarithms, so rescaling is exact and
+//                   rare) and sum in 32-bit, probabilities to shared memory as bf16
+//     O += P V      tcgen05.mma, M 128, N head_dim, K 128 keys, V taken as it lies in its pages ([key][dim],
+//                   an MN-major operand), accumulator in TMEM for the whole walk
+// Roles: warps 0..3 softmax (thread = row), warp 4 allocates TMEM and one of its lanes issues the MMAs, warps
+// 5..8 bring Q once and then K and V tiles from their pages with cp.async into 128-byte-swizzled shared
+// memory (two stages).  The roles meet only through mbarriers, every wait on one is bounded.  The first product
+// of tile j + 1 is issued before the softmax of tile j is awaited (two score buffers in TMEM), and the softmax of
+// tile j + 1 runs while the second product of tile j does: the tensor cores and the exponentials overlap.
+//
+// Rows are (token, head) pairs: row r is token r / g, head r % g of the CTA's tokens, so the keys of a kv
+// head are read once for all its query heads.  Head sizes 64 and 128, g a divisor of 128; the caller uses
+// the mma.sync kernel (attention_prefill.cu) for everything else.
+#include "tcgen05.cuh"
+
+using namespace tc5;
+
+namespace {
+constexpr int ROWS = 128;                // query rows per CTA: the MMA's M
+constexpr int KT = 128;                  // keys per tile: N of the first product, K of the second
+constexpr int SOFTMAX_WARPS = 4, LOAD_WARPS = 4;
+constexpr int THREADS = (SOFTMAX_WARPS + 1 + LOAD_WARPS) * 32;
+constexpr int LOADERS = LOAD_WARPS * 32;
+constexpr int STAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Params {
+    const __nv_bfloat16* q;          // [tokens, nq, D]
+    const __nv_bfloat16* k_pages;    // [pages, page_size, nkv, D]
+    const __nv_bfloat16* v_pages;
+    const int* segments;             // [n_segments][3]: first token's batch index, its position, count
+    const int* slots;                // [tokens]
+    const int* block_table;          // [slots, table_stride]
+    __nv_bfloat16* out;              // [tokens, nq, D]
+    int n_segments, table_stride, nq, nkv, page_size, page_shift, window, tokens_per_tile;
+    float scale_log2;
+    int* error_flag;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float exp2_whole(float n) {       // 2^n for a whole number n <= 0 (or -infinity), exactly
+    return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// 16 consecutive columns of this warp's 32 TMEM lanes, written from registers.
+__device__ __forceinline__ void tmem_store16(uint32_t addr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+// 64 consecutive columns of this warp's 32 TMEM lanes into registers; the caller waits (tmem_load_wait) before use.
+__device__ __forceinline__ void tmem_load64_nowait(uint32_t addr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// A tile of `rows` rows x D elements as the tensor cores want a K-major operand (and, read with the other
+// descriptor, an MN-major one): blocks of 64 elements (128 bytes) per row, 128-byte swizzle, 8 rows per 1024
+// bytes, the blocks of one row `rows` * 128 bytes apart.  Byte offset of the 16-byte piece `piece` of row `row`.
+template <int TILE_ROWS>
+__device__ __forceinline__ uint32_t tile_offset(int row, int piece) {
+    return (uint32_t)((piece >> 3) * (TILE_ROWS * 128) + (row >> 3) * 1024 + (row & 7) * 128 + (((piece & 7) ^ (row & 7)) << 4));
+}
+// K-major operand: see smem_desc in tcgen05.cuh.  MN-major operand with 128-byte swizzle: leading offset = the
+// distance between two 64-element blocks of the MN dimension, stride offset = the distance between two groups
+// of 8 rows of K.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((leading_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((stride_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor as instr_desc(), with B taken MN-major.
+__device__ __forceinline__ uint32_t instr_desc_b_mn(int m, int n) { return instr_desc(m, n) | (1u << 16); }
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], p_ready, pv_done;
+    __shared__ uint32_t tmem_base_slot;
+    constexpr int PIECES = D / 8;                      // 16-byte pieces per row
+    constexpr uint32_t Q_BYTES = ROWS * D * 2, KV_BYTES = KT * D * 2, P_BYTES = ROWS * KT * 2;
+    constexpr int TMEM_COLS = 512;                     // two score buffers of 128 columns, then the output's head_dim columns
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = smem_base, p_s = q_s + Q_BYTES, kv_s = p_s + P_BYTES;       // kv_s: [stage][K, V]
+    uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    // ---- which portion, which tokens, which kv head (later tiles first: they have the most keys) ----
+    const int group = p.nq / p.nkv;
+    const int kvh = blockIdx.y;
+    int tile = gridDim.x - 1 - blockIdx.x, seg = 0, q_offset = 0, seg_start = 0, seg_count = 0;
+    for (; seg < p.n_segments; ++seg) {
+        q_offset = p.segments[seg * 3];
+        seg_start = p.segments[seg * 3 + 1];
+        seg_count = p.segments[seg * 3 + 2];
+        const int tiles = (seg_count + p.tokens_per_tile - 1) / p.tokens_per_tile;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    const bool active = seg < p.n_segments && p.slots[q_offset] >= 0;
+    const int tok0 = tile * p.tokens_per_tile;
+    const int tok_count = active ? min(p.tokens_per_tile, seg_count - tok0) : 0;
+    const int pos_first = seg_start + tok0, pos_last = pos_first + tok_count - 1;
+    const int key_begin = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    const int key_end = pos_last + 1;
+    const int n_tiles = active ? (key_end - key_begin + KT - 1) / KT : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&q_full), LOADERS);
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(smem_u32(&k_full[i]), LOADERS);
+            mbar_init(smem_u32(&v_full[i]), LOADERS);
+            mbar_init(smem_u32(&k_empty[i]), 1);
+            mbar_init(smem_u32(&v_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&s_full[0]), 1);
+        mbar_init(smem_u32(&s_full[1]), 1);
+        mbar_init(smem_u32(&p_ready), SOFTMAX_WARPS * 32);
+        mbar_init(smem_u32(&pv_done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == SOFTMAX_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 2 * KT;       // score buffer b at tmem_s + b * KT
+    pdl_launch_dependents();
+    pdl_wait();                                   // q and this step's keys come from the kernel ahead
+
+    if (warp > SOFTMAX_WARPS && n_tiles > 0) {
+        // ---- loaders: Q once, then the K and V tiles, each thread whole 16-byte pieces ----
+        const int lt = threadIdx.x - (SOFTMAX_WARPS + 1) * 32;            // 0..127
+        const int* table = p.block_table + (size_t)p.slots[q_offset] * p.table_stride;
+        for (int id = lt; id < ROWS * PIECES; id += LOADERS) {
+            const int r = id / PIECES, piece = id % PIECES;
+            const int tok = r / group, head = r % group;
+            const bool valid = tok < tok_count;
+            const size_t src = ((size_t)(q_offset + tok0 + (valid ? tok : 0)) * p.nq + kvh * group + head) * D + piece * 8;
+            cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        fence_async_smem();
+        mbar_arrive(smem_u32(&q_full));
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j % STAGES;
+            // the keys' stage is free as soon as the first product of two tiles ago has read it, the values' stage
+            // only after the second
+            if (j >= STAGES && !mbar_wait(smem_u32(&k_empty[st]), ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { ok = false; break; }
+            const uint32_t ks = kv_s + (uint32_t)st * 2 * KV_BYTES, vs = ks + KV_BYTES;
+            const int key0 = key_begin + j * KT;
+            // PIECES lanes share a key row (their 16-byte pieces make one coalesced request); lane j of them looks
+            // up the row of pass j
+            {
+                constexpr int ROWS_PER_PASS = LOADERS / PIECES, PASSES = KT / ROWS_PER_PASS;
+                static_assert(PASSES <= PIECES, "one lane per pass");
+                const int sub = lt / PIECES, piece = lt % PIECES, lane_group = (lane / PIECES) * PIECES;
+                int my_row = -1, rows[PASSES];
+                if (piece < PASSES) {
+                    const int key = key0 + sub + piece * ROWS_PER_PASS;
+                    if (key < key_end) {
+                        const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+                        my_row = table[page] * p.page_size + (key - page * p.page_size);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < PASSES; ++i) {
+                    const int row = __shfl_sync(0xffffffffu, my_row, lane_group + i);
+                    const bool valid = row >= 0;
+                    const size_t src = ((size_t)(valid ? row : 0) * p.nkv + kvh) * D + piece * 8;
+                    const uint32_t at = tile_offset<KT>(sub + i * ROWS_PER_PASS, piece);
+                    cp_async_16(ks + at, p.k_pages + src, valid);
+                    rows[i] = row;
+                }
+                cp_async_commit();
+                if (j >= STAGES && !mbar_wait(smem_u32(&v_empty[st]), ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { ok = false; break; }
+#pragma unroll
+                for (int i = 0; i < PASSES; ++i) {
+                    const bool valid = rows[i] >= 0;
+                    const size_t src = ((size_t)(valid ? rows[i] : 0) * p.nkv + kvh) * D + piece * 8;
+                    cp_async_16(vs + tile_offset<KT>(sub + i * ROWS_PER_PASS, piece), p.v_pages + src, valid);
+                }
+                cp_async_commit();
+            }
+            asm volatile("cp.async.wait_group 1;" ::: "memory");        // the keys have landed
+            fence_async_smem();
+            mbar_arrive(smem_u32(&k_full[st]));
+            cp_async_wait_all();
+            fence_async_smem();
+            mbar_arrive(smem_u32(&v_full[st]));
+        }
+        if (!ok && p.error_flag) atomicExch(p.error_flag, 3);
+    } else if (warp == SOFTMAX_WARPS && lane == 0 && n_tiles > 0) {
+        // ---- MMA issuer ----
+        const uint32_t idesc_s = instr_desc(ROWS, KT), idesc_o = instr_desc_b_mn(ROWS, D);
+        bool ok = mbar_wait(smem_u32(&q_full), 0u);
+        // S_j = Q K_j^T into score buffer j & 1: issued one tile ahead, so that it runs while the softmax of the
+        // tile before is at work (that buffer's last reader arrived on p_ready two tiles ago)
+        auto first_product = [&](int j) {
+            const int st = j % STAGES;
+            const uint32_t ks = kv_s + (uint32_t)st * 2 * KV_BYTES;
+            if (!mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / STAGES) & 1u)) { ok = false; return; }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t a = q_s + (uint32_t)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
+                const uint32_t b = ks + (uint32_t)((kk >> 2) * (KT * 128) + (kk & 3) * 32);
+                tc_mma(tmem_s + (uint32_t)((j & 1) * KT), smem_desc(a), smem_desc(b), idesc_s, kk > 0 ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&s_full[j & 1]));
+            tc_commit(smem_u32(&k_empty[st]));
+        };
+        if (ok) first_product(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j % STAGES;
+            const uint32_t vs = kv_s + (uint32_t)st * 2 * KV_BYTES + KV_BYTES;
+            if (j + 1 < n_tiles) first_product(j + 1);
+            if (!ok) break;
+            // O += P V once the values and the probabilities lie in shared memory (and O has been rescaled if it had to be)
+            if (!mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / STAGES) & 1u)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&p_ready), (uint32_t)j & 1u)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int ks16 = 0; ks16 < KT / 16; ++ks16) {
+                const uint32_t a = p_s + (uint32_t)((ks16 >> 2) * (ROWS * 128) + (ks16 & 3) * 32);
+                const uint32_t b = vs + (uint32_t)(ks16 * 2048);              // 16 keys = two groups of 8 rows
+                tc_mma(tmem_o, smem_desc(a), smem_desc_mn(b, KT * 128, 1024), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&v_empty[st]));
+            tc_commit(smem_u32(&pv_done));
+        }
+        if (!ok && p.error_flag) atomicExch(p.error_flag, 3);
+    } else if (warp < SOFTMAX_WARPS && n_tiles > 0) {
+        // ---- softmax: thread = row (TMEM lane) ----
+        const int r = threadIdx.x;                                          // 0..127
+        const int tok = r / group, head = r % group;
+        const bool row_ok = tok < tok_count;
+        const int pos = row_ok ? pos_first + tok : 0x3fffffff;              // a row beyond the portion sees every key and is never written
+        const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
+        float row_max = -INFINITY, row_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int key0 = key_begin + j * KT;
+            if (!mbar_wait(smem_u32(&s_full[j & 1]), ((uint32_t)j >> 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const bool masked = key0 + KT - 1 > pos_first || (p.window > 0 && key0 <= pos_last - p.window);
+            // the row's 128 scores, in two loads that are both in flight before the wait
+            uint32_t raw[KT];
+            tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT) + lane_base, raw);
+            tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT) + lane_base + 64u, raw + 64);
+            tmem_load_wait();
+            float tile_max = -INFINITY;
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < KT; ++c) {
+                    const int key = key0 + c;
+                    bool visible = key <= pos;
+                    if (p.window > 0) visible = visible && key > pos - p.window;
+                    if (!visible) raw[c] = 0xff800000u;                         // -infinity
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < KT; ++c) tile_max = fmaxf(tile_max, __uint_as_float(raw[c]));
+            // whole-number reference point: see attention_decode.cu
+            const float new_max = fmaxf(row_max, ceilf(tile_max * p.scale_log2));
+            const float safe_max = new_max == -INFINITY ? 0.f : new_max;        // a row that has seen no key yet
+            const float correction = exp2_whole(row_max - safe_max);
+            row_max = new_max;
+            row_sum *= correction;
+            // probabilities, as bf16 pairs (the scores' registers are reused)
+#pragma unroll
+            for (int c = 0; c < KT; c += 2) {
+                const float e0 = ex2_approx(fmaf(__uint_as_float(raw[c]), p.scale_log2, -safe_max));
+                const float e1 = ex2_approx(fmaf(__uint_as_float(raw[c + 1]), p.scale_log2, -safe_max));
+                row_sum += e0 + e1;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
+                raw[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            // the second product of the tile before must be done: it reads P, and O is about to be rescaled
+            if (j > 0 && !mbar_wait(smem_u32(&pv_done), (uint32_t)(j - 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            if (__any_sync(0xffffffffu, correction != 1.f) && j > 0) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 16) {
+                    float o[16];
+                    tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) o[c] *= correction;
+                    tmem_store16(tmem_o + lane_base + (uint32_t)c0, o);
+                }
+                tmem_store_wait();
+            }
+#pragma unroll
+            for (int piece = 0; piece < KT / 8; ++piece)
+                *reinterpret_cast<uint4*>(smem + Q_BYTES + tile_offset<ROWS>(r, piece)) =
+                    make_uint4(raw[piece * 4], raw[piece * 4 + 1], raw[piece * 4 + 2], raw[piece * 4 + 3]);
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&p_ready));
+        }
+        // ---- the row's output ----
+        if (ok && !mbar_wait(smem_u32(&pv_done), (uint32_t)(n_tiles - 1) & 1u)) ok = false;
+        tc_fence_after();
+        if (ok) {
+            const float inv = 1.0f / row_sum;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_offset + tok0 + (row_ok ? tok : 0)) * p.nq + kvh * group + head) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 16) {
+                float o[16];
+                tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);           // every lane takes part in the load
+                if (row_ok) {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int c = 0; c < 16; c += 2) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
+                        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        } else if (lane == 0 && p.error_flag) {
+            atomicExch(p.error_flag, 3);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == SOFTMAX_WARPS) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+template <int D>
+int launch(const Params& p, int n_tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)ROWS * D * 2 + (size_t)ROWS * KT * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return LIA_ERR_LAUNCH;
+        configured = true;
+    }
+    return lia_launch(attention_prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(THREADS), smem, stream, p);
+}
+}  // namespace
+
+// Tokens of a portion that one CTA takes for `group` query heads per kv head and this head size (0: the tcgen05
+// kernel does not take the combination; use lia_attention_prefill).
+LIA_EXPORT int lia_attention_prefill_tc_tokens_per_tile(int group, int d) {
+    if (d != 64 && d != 128) return 0;
+    return group >= 1 && group <= ROWS && ROWS % group == 0 ? ROWS / group : 0;
+}
+
+// Arguments as lia_attention_prefill; `n_tiles` = sum over portions of ceil(count / tokens_per_tile) with the
+// tokens per tile of this kernel.
+LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
+                                        int n_segments, int n_tiles, const int* slots, const int* block_table,
+                                        int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
+                                        float scale, int* error_flag, cudaStream_t stream) {
+    if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
+    const int per_tile = lia_attention_prefill_tc_tokens_per_tile(nq / nkv, d);
+    if (per_tile == 0) return LIA_ERR_SIZE;
+    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)k_pages & 15u) || ((uintptr_t)v_pages & 15u)) return LIA_ERR_ALIGN;
+    Params p;
+    p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.segments = segments; p.slots = slots; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
+    p.n_segments = n_segments; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
+    p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
+    p.page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if (page_size == (1 << b)) p.page_shift = b;
+    if (d == 128) return launch<128>(p, n_tiles, stream);
+    return launch<64>(p, n_tiles, stream);
+}

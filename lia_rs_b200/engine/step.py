@@ -230,11 +230,16 @@ class StepRuntime:
             ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
                                  kv.block_table, out, partial, nq, nkv, d, window, scale, 0, n_splits, counters)
         if ctx.n_prefill_segments:
-            per_tile = ops.attention_prefill_tokens_per_tile(nq // nkv)
+            # prompt portions: the tcgen05 kernel where it takes the head size and group, else the mma.sync kernel,
+            # else (groups above 64) the kernel for every size
+            per_tile_tc = ops.attention_prefill_tc_tokens_per_tile(nq // nkv, d)
+            per_tile = per_tile_tc or ops.attention_prefill_tokens_per_tile(nq // nkv)
             if per_tile:
                 tiles = sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1)
-                ops.attention_prefill(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments,
-                                      tiles, ctx.slots, kv.block_table, out, nq, nkv, d, window, scale)
+                kernel = ops.attention_prefill_tc if per_tile_tc else ops.attention_prefill
+                extra = (ctx.error_flag,) if per_tile_tc else ()
+                kernel(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles, ctx.slots,
+                       kv.block_table, out, nq, nkv, d, window, scale, *extra)
             else:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
                                       nq, nkv, d, window, scale, rows=ctx.prefill_rows)

@@ -67,6 +67,9 @@ class _Signatures:
                         c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+    lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
 
 
@@ -317,6 +320,25 @@ def attention_prefill(q, k_pages, v_pages, segments, n_segments, n_tiles, slots,
     _check(lib().lia_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
                                        _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
                                        k_pages.shape[1], int(window or 0), scale, _stream()), "attention_prefill")
+
+
+def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
+    """Tokens of a portion that one CTA of the tcgen05 prefill kernel takes (0: it does not take this group
+    size or head size)."""
+    return int(lib().lia_attention_prefill_tc_tokens_per_tile(group, d))
+
+
+def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
+                         window, scale, error_flag=None):
+    """Prompt-portion attention on the tcgen05 tensor cores (bfloat16, head size 64 or 128, heads per kv head a
+    divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`."""
+    _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("attention_prefill_tc is a bfloat16 kernel")
+    _check(lib().lia_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
+                                          _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
+                                          k_pages.shape[1], int(window or 0), scale, _p(error_flag), _stream()),
+           "attention_prefill_tc")
 
 
 def select_tokens(logits, out, temperature=None, seeds=None, positions=None):

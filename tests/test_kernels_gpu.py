@@ -461,9 +461,11 @@ def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len, f
     assert float((got[-1, 0] - v[far, 0].double()).abs().max()) < 0.05
 
 
+@pytest.mark.parametrize("kernel", ["mma.sync", "tcgen05"])
 @pytest.mark.parametrize("d,nq,nkv,page_size,window", [(128, 16, 2, 16, None), (64, 16, 2, 4, None), (32, 3, 1, 16, 40),
-                                                       (64, 10, 2, 8, 150), (128, 4, 4, 32, None), (32, 64, 1, 16, None)])
-def test_attention_prefill_portions(d, nq, nkv, page_size, window):
+                                                       (64, 10, 2, 8, 150), (128, 4, 4, 32, None), (32, 64, 1, 16, None),
+                                                       (128, 32, 2, 16, 300), (64, 8, 2, 12, 100), (128, 2, 1, 16, 37)])
+def test_attention_prefill_portions(d, nq, nkv, page_size, window, kernel):
     """Tensor-core prefill attention: portions that start and end anywhere (at 0, inside a page, one that
     continues an earlier portion), groups that do not divide 64, a far key that dominates, the window's
     edge, scrambled pages, two requests in one launch."""
@@ -500,11 +502,21 @@ def test_attention_prefill_portions(d, nq, nkv, page_size, window):
     n = q.shape[0]
     slots = torch.tensor([0] * 150 + [1] * (T - 437), dtype=torch.int32, device=DEV)
     segments = torch.tensor([[0, 0, 150], [150, 437, T - 437]], dtype=torch.int32, device=DEV)
-    per_tile = ops().attention_prefill_tokens_per_tile(nq // nkv)
+    tc = kernel == "tcgen05"
+    per_tile = ops().attention_prefill_tc_tokens_per_tile(nq // nkv, d) if tc else ops().attention_prefill_tokens_per_tile(nq // nkv)
+    if tc and per_tile == 0:
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and group sizes that divide 128")
     tiles = (150 + per_tile - 1) // per_tile + (T - 437 + per_tile - 1) // per_tile
     out = torch.zeros(n, nq * d, device=DEV, dtype=torch.bfloat16)
-    ops().attention_prefill(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), out, nq, nkv, d,
-                            window, scale)
+    if tc:
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().attention_prefill_tc(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), out, nq, nkv, d,
+                                   window, scale, flag)
+        torch.cuda.synchronize()
+        assert flag.item() == 0
+    else:
+        ops().attention_prefill(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), out, nq, nkv, d,
+                                window, scale)
     want_b = reference_attention(qb, kb, vb, list(range(150)), window, scale)
     want_a = reference_attention(qa, ka, va, list(range(437, T)), window, scale)
     got = out.view(n, nq, d).double()

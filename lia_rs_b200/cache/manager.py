@@ -60,7 +60,24 @@ class CacheGroup:
         self.dirty[slot] = (min(lo, block), max(hi, block + 1))
 
     def pages_needed(self, slot, start, end):
-        """(blocks to allocate, blocks to give back) for positions [start, end)."""
+        """(blocks to allocate, blocks to give back, first block kept) for positions [start, end).
+        The blocks of a slot's table from `first_block` on are all present (blocks are only ever given
+        back from the front, and allocated without gaps), so only the table's ends are looked at: a
+        decode step costs the same whatever the context length."""
+        ps = self.page_size
+        table = self.tables[slot]
+        n, first = len(table), self.first_block[slot]
+        keep_from = 0
+        if self.window is not None:
+            keep_from = max(0, start - self.window + 1) // ps
+        give_back = [b for b in range(first, min(keep_from, n)) if table[b] >= 0]
+        last = (end - 1) // ps
+        allocate = [b for b in range(keep_from, min(first, last + 1))]        # given back earlier, wanted again
+        allocate += [b for b in range(max(keep_from, n), last + 1)]           # beyond the table's end
+        return allocate, give_back, keep_from
+
+    def pages_needed_by_scan(self, slot, start, end):
+        """The same by looking at every block (what `check` compares `pages_needed` with)."""
         ps = self.page_size
         table = self.tables[slot]
         keep_from = 0
@@ -209,6 +226,14 @@ class CacheManager:
             if len(set(held)) != len(held):
                 raise PageError(f"group {group.index}: a page is held twice")
             group.pool.check(held)
+            for slot in self._live:                          # the table's shape that pages_needed relies on
+                table, first = group.tables[slot], group.first_block[slot]
+                if any(p >= 0 for p in table[:first]) or any(p < 0 for p in table[first:]):
+                    raise PageError(f"group {group.index}, slot {slot}: the block table has a gap")
+                probe = (self.length[slot], self.length[slot] + 1)
+                if self.length[slot] < self.max_context and \
+                        group.pages_needed(slot, *probe) != group.pages_needed_by_scan(slot, *probe):
+                    raise PageError(f"group {group.index}, slot {slot}: pages_needed disagrees with a scan of the table")
         if len(set(self._free_slots)) != len(self._free_slots) or set(self._free_slots) & self._live:
             raise PageError("a slot is both free and live, or free twice")
         if len(self._free_slots) + len(self._live) != self.max_slots:

@@ -300,12 +300,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int c0 = 0; c0 < s.n_tile; c0 += STAGING_TOKENS) {
                     if (u.t0 + c0 >= s.M) break;
                     float acc[32], up[32];
-                    tmem_load16(lane_addr + (uint32_t)c0, acc);
-                    tmem_load16(lane_addr + (uint32_t)(c0 + 16), acc + 16);
-                    if (MODE == GEMM_SWIGLU) {
-                        tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
-                        tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0 + 16), up + 16);
-                    }
+                    tmem_load32_nowait(lane_addr + (uint32_t)c0, acc);
+                    if (MODE == GEMM_SWIGLU) tmem_load32_nowait(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                    tmem_load_wait();
                     const int sbuf = chunk_count & 1;
                     ++chunk_count;
                     // the store that last read this staging buffer must be done reading it
@@ -316,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         float v;
-                        if (MODE == GEMM_SWIGLU) v = up[c] * (acc[c] / (1.0f + __expf(-acc[c])));
+                        if (MODE == GEMM_SWIGLU) v = up[c] * __fdividef(acc[c], 1.0f + __expf(-acc[c]));
                         else v = s.alpha * acc[c];
                         stage[c * TILE_F + group * 32 + lane] = from_float<TO>(v);
                     }

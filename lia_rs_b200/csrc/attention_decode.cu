@@ -97,12 +97,15 @@ attention_decode_kernel(Params p) {
     const int row_base = warp * (32 / CHUNKS) + sub;                 // this thread's row in pass 0
     const uint32_t piece_offset = T::offset(row_base, piece);        // later passes: + ROWS_PER_PASS rows, same swizzle
     static_assert(ROWS_PER_PASS % 8 == 0 && PASSES <= CHUNKS, "the swizzle repeats every 8 rows; one lane per pass");
-    auto load_tile = [&](int stage, int key0) {
+    // `left_out`: a key whose row of the tile no copy touches (this CTA writes it into the tile itself)
+    auto load_tile = [&](int stage, int key0, int left_out) {
         const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES + piece_offset, vs = ks + T::BYTES;
         int my_row = -1;
         if (piece < PASSES) {
             const int key = key0 + row_base + piece * ROWS_PER_PASS;
-            if (key < key_end) {
+            if (key == left_out) {
+                my_row = -2;
+            } else if (key < key_end) {
                 const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
                 my_row = table[page] * p.page_size + (key - page * p.page_size);
             }
@@ -110,6 +113,7 @@ attention_decode_kernel(Params p) {
 #pragma unroll
         for (int i = 0; i < PASSES; ++i) {
             const int row = __shfl_sync(0xffffffffu, my_row, sub * CHUNKS + i);
+            if (row == -2) continue;
             const bool valid = row >= 0;
             const size_t src = ((size_t)(valid ? row : 0) * p.nkv + kvh) * D + piece * 8;
             cp_async_16(ks + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.k_pages + src, valid);
@@ -118,24 +122,28 @@ attention_decode_kernel(Params p) {
     };
 
     const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
-    // With the append in this kernel, the tile that holds the token's own key (the last of the last range) is
-    // asked for only after that key has been written; it is the last tile, so the order of the groups stands.
+    // With the append in this kernel, the range that ends at the token's own position holds a key that does not
+    // exist yet.  Where its tile (the range's last) is among the first STAGES, the copies leave that row
+    // out and this CTA writes the rotated key and the value into the tile itself, beside the cache (`direct`);
+    // otherwise the tile is asked for only after the append (and a fence).  A layer that reads another layer's
+    // cache (write_kv 0) waits for the step's earlier kernels before it asks for that tile (`deferred`).
     const bool appends = p.qkv != nullptr && key_end == pos + 1;
+    const bool writes = appends && p.write_kv && blockIdx.y % groups16 == 0;
+    const bool direct = writes && n_tiles <= STAGES;
     int deferred = -1;
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 0; s < STAGES; ++s) {       // the first STAGES tiles are asked for at once: tile i is copy group i
         if (s < n_tiles) {
             const bool holds_new = key_begin + (s + 1) * TILE_KEYS > pos;
-            if (holds_new && appends) {
+            if (holds_new && appends && !direct) {
                 deferred = s;
             } else {
-                if (holds_new) pdl_wait();                               // the tile holds the key this step wrote
-                load_tile(s, key_begin + s * TILE_KEYS);
+                if (holds_new && !appends) pdl_wait();                   // the tile holds the key this step wrote
+                load_tile(s, key_begin + s * TILE_KEYS, direct ? pos : -1);
             }
         }
         if (deferred < 0) cp_async_commit();
     }
-    pdl_wait();
 
     // ---- Q fragments: rows = heads (row r -> head h0 + r), zero beyond `heads` ----
     uint32_t qf[D / 16][4];
@@ -145,48 +153,85 @@ attention_decode_kernel(Params p) {
         const float* row = p.qkv + (size_t)t * width;
         const int half = p.rotary_dim / 2;
         float2* rotation = reinterpret_cast<float2*>(q_s + 16 * D);      // [half] (cos, sin) of the token's angles
+        float* raw = reinterpret_cast<float*>(rotation + D / 2);        // [16 + 2][D] the step's 32-bit q, k and v rows
+        // the angles and the padding depend on the position alone: before the wait
         for (int i = tid; i < half; i += WARPS * 32) {
             float sn, cs;
             sincosf((float)pos * p.inv_freq[i], &sn, &cs);
             rotation[i] = make_float2(cs, sn);
         }
         for (int w = tid; w < (16 - heads) * D; w += WARPS * 32) q_s[heads * D + w] = __float2bfloat16_rn(0.f);
+        const int page_index = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+        const int page = writes ? table[page_index] : 0;
+        pdl_wait();
+        // The step's rows come in with ONE trip to memory: every thread has all its 16-byte loads in flight
+        // before it stores the first.  (Heads of 16 k elements: rows and widths are multiples of 16 bytes.)
+        {
+            constexpr int PER_THREAD = (18 * D / 4 + WARPS * 32 - 1) / (WARPS * 32);
+            const int q4 = heads * (D / 4), all4 = q4 + (writes ? 2 * (D / 4) : 0);
+            const float4* q_src = reinterpret_cast<const float4*>(row + (size_t)h0 * D);
+            const float4* k_src = reinterpret_cast<const float4*>(row + (size_t)(p.nq + kvh) * D);
+            const float4* v_src = reinterpret_cast<const float4*>(row + (size_t)(p.nq + p.nkv + kvh) * D);
+            float4 got[PER_THREAD] = {};
+#pragma unroll
+            for (int j = 0; j < PER_THREAD; ++j) {
+                const int w = tid + j * WARPS * 32;
+                if (w < q4) got[j] = __ldcg(q_src + w);
+                else if (w < q4 + D / 4 && w < all4) got[j] = __ldcg(k_src + (w - q4));
+                else if (w < all4) got[j] = __ldcg(v_src + (w - q4 - D / 4));
+            }
+#pragma unroll
+            for (int j = 0; j < PER_THREAD; ++j) {
+                const int w = tid + j * WARPS * 32;
+                if (w < q4) reinterpret_cast<float4*>(raw)[w] = got[j];
+                else if (w < all4) reinterpret_cast<float4*>(raw + 16 * D)[w - q4] = got[j];
+            }
+        }
         __syncthreads();
+#pragma unroll 4
         for (int w = tid; w < heads * half; w += WARPS * 32) {
             const int r = w / half, i = w % half;
             const float cs = rotation[i].x, sn = rotation[i].y;
-            const float a = row[(h0 + r) * D + i], b = row[(h0 + r) * D + i + half];
+            const float a = raw[r * D + i], b = raw[r * D + i + half];
             q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
             q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
         }
         for (int w = tid; w < heads * (D - p.rotary_dim); w += WARPS * 32) {
             const int r = w / (D - p.rotary_dim), i = p.rotary_dim + w % (D - p.rotary_dim);
-            q_s[r * D + i] = __float2bfloat16_rn(row[(h0 + r) * D + i]);
+            q_s[r * D + i] = __float2bfloat16_rn(raw[r * D + i]);
         }
-        if (appends && p.write_kv && blockIdx.y % groups16 == 0) {
-            const int page_index = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-            const int page = table[page_index];
+        if (writes) {
             if (page < 0 || page >= p.num_pages) {
                 if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+                // (a `direct` tile then keeps whatever the row held: the step's results are discarded anyway)
             } else {
                 const size_t cache_row = (((size_t)page * p.page_size + (pos - page_index * p.page_size)) * p.nkv + kvh) * D;
-                const float* k = row + (p.nq + kvh) * D;
-                const float* v = row + (p.nq + p.nkv + kvh) * D;
+                const float* k = raw + 16 * D;
+                const float* v = raw + 17 * D;
+                // the row of the tile that the copies left out, if this CTA fills it itself
+                const int tile_row = pos - key_begin - (n_tiles - 1) * TILE_KEYS;
+                uint8_t* k_tile = smem + (size_t)(n_tiles - 1) * 2 * T::BYTES;
+                uint8_t* v_tile = k_tile + T::BYTES;
+                auto put = [&](__nv_bfloat16* cache, uint8_t* tile, int i, float value) {
+                    const __nv_bfloat16 x = __float2bfloat16_rn(value);
+                    cache[cache_row + i] = x;
+                    if (direct) *reinterpret_cast<__nv_bfloat16*>(tile + T::offset(tile_row, i >> 3) + (i & 7) * 2) = x;
+                };
                 for (int i = tid; i < half; i += WARPS * 32) {
                     const float cs = rotation[i].x, sn = rotation[i].y;
                     const float a = k[i], b = k[i + half];
-                    p.k_write[cache_row + i] = __float2bfloat16_rn(a * cs - b * sn);
-                    p.k_write[cache_row + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+                    put(p.k_write, k_tile, i, a * cs - b * sn);
+                    put(p.k_write, k_tile, i + half, b * cs + a * sn);
                 }
-                for (int i = p.rotary_dim + tid; i < D; i += WARPS * 32) p.k_write[cache_row + i] = __float2bfloat16_rn(k[i]);
-                for (int i = tid; i < D; i += WARPS * 32) p.v_write[cache_row + i] = __float2bfloat16_rn(v[i]);
+                for (int i = p.rotary_dim + tid; i < D; i += WARPS * 32) put(p.k_write, k_tile, i, k[i]);
+                for (int i = tid; i < D; i += WARPS * 32) put(p.v_write, v_tile, i, v[i]);
             }
-            __threadfence();                                              // the row is read back below, past L1
+            if (!direct) __threadfence();                                 // the row is read back below, past L1
         }
         __syncthreads();
         if (deferred >= 0) {
-            load_tile(deferred, key_begin + deferred * TILE_KEYS);
-            for (int s = deferred; s < STAGES - 1; ++s) cp_async_commit();
+            load_tile(deferred, key_begin + deferred * TILE_KEYS, -1);
+            for (int s = deferred; s < STAGES; ++s) cp_async_commit();
         }
         const int r0 = lane >> 2, c = (lane & 3) * 2;
 #pragma unroll
@@ -198,6 +243,7 @@ attention_decode_kernel(Params p) {
             qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * D + col + 8);
         }
     } else {
+        pdl_wait();
         const int r0 = lane >> 2, c = (lane & 3) * 2;
         const __nv_bfloat16* base = p.q + ((size_t)t * p.nq + h0) * D;
 #pragma unroll
@@ -219,26 +265,41 @@ attention_decode_kernel(Params p) {
     const int k_row = warp * 16 + (lm >> 1) * 8 + (lane & 7), v_row = warp * 16 + (lm & 1) * 8 + (lane & 7);
 
     for (int tile = 0; tile < n_tiles; ++tile) {
-        cp_async_wait<STAGES - 2>();
+        // groups asked for so far: STAGES, and one per earlier iteration but the first; tile i is group i
+        if (tile == 0) cp_async_wait<STAGES - 1>(); else cp_async_wait<STAGES - 2>();
         __syncthreads();
-        {   // refill the stage that was consumed in the previous iteration
-            const int next = tile + STAGES - 1;
-            if (next < n_tiles) load_tile(next % STAGES, key_begin + next * TILE_KEYS);
+        if (tile > 0) {   // refill the stage that was consumed in the previous iteration
+            const int next = tile - 1 + STAGES;
+            if (next < n_tiles) load_tile(next % STAGES, key_begin + next * TILE_KEYS, -1);
             cp_async_commit();
         }
         const int stage = tile % STAGES;
         const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES, vs = ks + T::BYTES;
         const int key0 = key_begin + tile * TILE_KEYS + warp * 16;       // this warp's 16 keys
         if (key0 < key_end) {
-            // ---- S = Q K^T for 16 keys: two n-tiles of 8 ----
+            // ---- S = Q K^T for 16 keys: two n-tiles of 8.  All fragments are asked for before the first
+            //      product (one warp per scheduler: nothing else hides the shared-memory latency), and
+            //      the sums run in four chains that meet at the end ----
+            uint32_t kf[D / 16][4];
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                ldmatrix_x4(ks + T::offset(k_row, kk * 2 + (lm & 1)), kf[kk][0], kf[kk][1], kf[kk][2], kf[kk][3]);
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(ks + T::offset(k_row, kk * 2 + (lm & 1)), b0, b1, b2, b3);
-                mma_bf16(s[0], qf[kk], b0, b1);
-                mma_bf16(s[1], qf[kk], b2, b3);
+                mma_bf16(kk & 1 ? s_odd[0] : s[0], qf[kk], kf[kk][0], kf[kk][1]);
+                mma_bf16(kk & 1 ? s_odd[1] : s[1], qf[kk], kf[kk][2], kf[kk][3]);
             }
+            // the values' fragments travel while the probabilities are made
+            uint32_t vf[D / 16][4];
+#pragma unroll
+            for (int j = 0; j < D / 8; j += 2)
+                ldmatrix_x4_trans(vs + T::offset(v_row, j + (lm >> 1)), vf[j / 2][0], vf[j / 2][1], vf[j / 2][2], vf[j / 2][3]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[nt][i] += s_odd[nt][i];
             // ---- mask (only the range's last keys need it), running maximum and sum ----
             if (key0 + 16 > key_end) {
 #pragma unroll
@@ -287,10 +348,8 @@ attention_decode_kernel(Params p) {
             }
 #pragma unroll
             for (int j = 0; j < D / 8; j += 2) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vs + T::offset(v_row, j + (lm >> 1)), b0, b1, b2, b3);
-                mma_bf16(o[j], pf, b0, b1);
-                mma_bf16(o[j + 1], pf, b2, b3);
+                mma_bf16(o[j], pf, vf[j / 2][0], vf[j / 2][1]);
+                mma_bf16(o[j + 1], pf, vf[j / 2][2], vf[j / 2][3]);
             }
         }
     }
@@ -303,16 +362,18 @@ attention_decode_kernel(Params p) {
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
     }
-    float* merge_o = reinterpret_cast<float*>(smem);                  // [WARPS][16][D]
-    float* merge_m = merge_o + WARPS * 16 * D;                        // [WARPS][16]
+    constexpr int MERGE_STRIDE = D + 8;                               // rows 8 words apart: the 8-byte stores of a warp meet no bank twice
+    float* merge_o = reinterpret_cast<float*>(smem);                  // [WARPS][16][MERGE_STRIDE]
+    float* merge_m = merge_o + WARPS * 16 * MERGE_STRIDE;             // [WARPS][16]
     float* merge_l = merge_m + WARPS * 16;
+    float* merge_f = merge_l + WARPS * 16;                            // [WARPS][16] each warp's share of a row
     {
         const int r0 = lane >> 2, c = (lane & 3) * 2;
 #pragma unroll
         for (int j = 0; j < D / 8; ++j) {
-            float* dst = merge_o + ((size_t)warp * 16 + r0) * D + j * 8 + c;
-            dst[0] = o[j][0]; dst[1] = o[j][1];
-            dst[8 * D] = o[j][2]; dst[8 * D + 1] = o[j][3];
+            float* dst = merge_o + ((size_t)warp * 16 + r0) * MERGE_STRIDE + j * 8 + c;
+            *reinterpret_cast<float2*>(dst) = make_float2(o[j][0], o[j][1]);
+            *reinterpret_cast<float2*>(dst + 8 * MERGE_STRIDE) = make_float2(o[j][2], o[j][3]);
         }
         if ((lane & 3) == 0) {
             merge_m[warp * 16 + r0] = row_max[0]; merge_m[warp * 16 + r0 + 8] = row_max[1];
@@ -320,27 +381,49 @@ attention_decode_kernel(Params p) {
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < heads * D; idx += WARPS * 32) {
-        const int r = idx / D, dcol = idx % D;
+    if (tid < heads) {                                                // one thread per row: the warps' shares
+        const int r = tid;
         float top = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) top = fmaxf(top, merge_m[w * 16 + r]);
-        float total = 0.f, value = 0.f;
+        float f[WARPS], total = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float mw = merge_m[w * 16 + r];
-            const float f = exp2_whole(mw - top);                     // both are whole numbers (or -infinity)
-            total += f * merge_l[w * 16 + r];
-            value += f * merge_o[((size_t)w * 16 + r) * D + dcol];
+            f[w] = exp2_whole(merge_m[w * 16 + r] - top);             // both are whole numbers (or -infinity)
+            total += f[w] * merge_l[w * 16 + r];
         }
-        const float result = value / total;
-        const int h = h0 + r;
-        if (p.n_splits == 1) {
-            p.out[((size_t)t * p.nq + h) * D + dcol] = __float2bfloat16_rn(result);
-        } else {
-            const size_t at = ((size_t)t * p.nq + h) * p.n_splits + blockIdx.z;
-            p.partial[at * D + dcol] = result;
-            if (dcol == 0) p.partial[(size_t)p.n_tokens * p.nq * p.n_splits * D + at] = top + log2f(total);
+        const float inv = 1.0f / total;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) merge_f[w * 16 + r] = f[w] * inv;
+        if (p.n_splits > 1)
+            p.partial[(size_t)p.n_tokens * p.nq * p.n_splits * D + ((size_t)t * p.nq + h0 + r) * p.n_splits + blockIdx.z] =
+                top + log2f(total);
+    }
+    __syncthreads();
+    {
+        constexpr int PER_THREAD = (16 * (D / 4) + WARPS * 32 - 1) / (WARPS * 32);
+#pragma unroll
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int idx = tid + j * WARPS * 32;
+            if (idx >= heads * (D / 4)) break;
+            const int r = idx / (D / 4), c4 = idx % (D / 4);
+            float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float share = merge_f[w * 16 + r];
+                const float4 part = *reinterpret_cast<const float4*>(merge_o + ((size_t)w * 16 + r) * MERGE_STRIDE + c4 * 4);
+                value.x += share * part.x; value.y += share * part.y; value.z += share * part.z; value.w += share * part.w;
+            }
+            const int h = h0 + r;
+            if (p.n_splits == 1) {
+                uint2 packed;
+                packed.x = pack_bf16(value.x, value.y);
+                packed.y = pack_bf16(value.z, value.w);
+                *reinterpret_cast<uint2*>(p.out + ((size_t)t * p.nq + h) * D + c4 * 4) = packed;
+            } else {
+                const size_t at = ((size_t)t * p.nq + h) * p.n_splits + blockIdx.z;
+                *reinterpret_cast<float4*>(p.partial + at * D + c4 * 4) = value;
+            }
         }
     }
     if (p.n_splits == 1 || !p.counters) return;
@@ -359,9 +442,46 @@ attention_decode_kernel(Params p) {
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
+    const float* lse = p.partial + (size_t)p.n_tokens * p.nq * p.n_splits * D;
+    if (used <= 16) {
+        // Few ranges: a thread owns eight elements of a head and has every load it needs (the ranges'
+        // log-sum-exps and their eight elements) in flight at once, so the token's tail is one trip to L2.
+        for (int idx = tid; idx < heads * (D / 8); idx += WARPS * 32) {
+            const int r = idx / (D / 8), c8 = idx % (D / 8);
+            const float* lrow = lse + ((size_t)t * p.nq + h0 + r) * p.n_splits;
+            const float4* base = reinterpret_cast<const float4*>(p.partial + ((size_t)t * p.nq + h0 + r) * p.n_splits * D) + c8 * 2;
+            float l[16];
+            float4 v[16][2];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const bool there = j < used;
+                l[j] = there ? __ldcg(lrow + j) : -INFINITY;
+                v[j][0] = there ? __ldcg(base + (size_t)j * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[j][1] = there ? __ldcg(base + (size_t)j * (D / 4) + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float top = l[0];
+#pragma unroll
+            for (int j = 1; j < 16; ++j) top = fmaxf(top, l[j]);
+            float total = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {                        // ascending ranges: the order depends on nothing else
+                const float w = exp2f(l[j] - top);
+                total += w;
+                acc[0] += w * v[j][0].x; acc[1] += w * v[j][0].y; acc[2] += w * v[j][0].z; acc[3] += w * v[j][0].w;
+                acc[4] += w * v[j][1].x; acc[5] += w * v[j][1].y; acc[6] += w * v[j][1].z; acc[7] += w * v[j][1].w;
+            }
+            const float inv = 1.0f / total;
+            uint4 packed;
+            packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+            packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+            packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+            packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+            *reinterpret_cast<uint4*>(p.out + ((size_t)t * p.nq + h0 + r) * D + c8 * 8) = packed;
+        }
+        return;
+    }
     float* weight = reinterpret_cast<float*>(smem);                   // [16][used], then [16] totals
     float* totals = weight + 16 * used;
-    const float* lse = p.partial + (size_t)p.n_tokens * p.nq * p.n_splits * D;
     for (int r = warp; r < heads; r += WARPS) {
         const float* base = lse + ((size_t)t * p.nq + h0 + r) * p.n_splits;
         float top = -INFINITY;
@@ -431,8 +551,8 @@ __global__ void attention_merge_kernel(Params p) {
 
 template <int D>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
-    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4;       // the tiles, the rotated queries, the angles' cosines and sines
-    const size_t merge = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4 + 18 * D * 4;   // the tiles, the rotated queries, the angles' cosines and sines, the step's 32-bit rows
+    const size_t merge = (size_t)WARPS * 16 * (D + 8 + 3) * sizeof(float);
     const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
     const size_t smem = ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
     static bool configured = false;

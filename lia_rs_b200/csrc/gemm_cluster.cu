@@ -27,7 +27,7 @@ using namespace tc5;
 #define GEMM_SWIGLU 2
 
 namespace {
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;            // warp 0: TMA, warps 1 and 6: MMA, warps 2-5: accumulator to shared memory
 constexpr int MAX_STAGES = 12;
 constexpr int MAX_CLUSTER = 8;
 constexpr int SMEM_LIMIT = 200 * 1024;
@@ -38,6 +38,7 @@ struct Shape {
     int box_rows;             // rows of W per TMA box (divides 128, a multiple of 8)
     int stages, batch, kblocks, splits, f_tiles, t_tiles;   // batch: K blocks whose W boxes are issued together
     int tmem_cols;
+    int chains;               // accumulators that take the K steps in turn (1, 2 or 4)
     int ldo, vector_ok;       // vector_ok: rows of out may be stored 4 elements at a time
     float alpha;
     int* error_flag;
@@ -97,7 +98,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_init(smem_u32(&full_bar[i]), 1);
             mbar_init(smem_u32(&empty_bar[i]), 1);
         }
-        mbar_init(smem_u32(&acc_full), 1);
+        mbar_init(smem_u32(&acc_full), s.chains >= 2 ? 2 : 1);       // one arrival per MMA issuer
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -158,28 +159,39 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = max(0, issued - s.stages); i < issued; ++i)      // copies in flight must land before the CTA may end
                 mbar_wait(smem_u32(&full_bar[i % s.stages]), (uint32_t)(i / s.stages) & 1u);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
+    } else if ((warp == 1 || warp == 6) && lane == 0) {
+        // ---- MMA issuers.  Issuing one tcgen05.mma costs a thread some 130 cycles, four times what a tile this
+        //      narrow computes for, so two threads issue: they take the K blocks in turn, each into accumulators of
+        //      its own (an MMA that adds to the accumulator of the one before it would wait for it, too).  The
+        //      epilogue adds the accumulators up in a fixed order. ----
+        const int issuers = s.chains >= 2 ? 2 : 1;
+        const int me = warp == 1 ? 0 : 1;
+        const int own = s.chains / issuers;                   // accumulators of this issuer
         const uint32_t idesc = instr_desc(TILE_F, s.n_tile);
         bool ok = true;
-        for (int it = 0; it < nkb; ++it) {
-            const int st = it % s.stages;
-            if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
-            const uint32_t b_addr = a_addr + A_TILES * a_bytes;
+        int mine = 0;                                         // K blocks this issuer has taken
+        if (me < issuers) {
+            for (int it = me; it < nkb; it += issuers, ++mine) {
+                const int st = it % s.stages;
+                if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
+                const uint32_t b_addr = a_addr + A_TILES * a_bytes;
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / 16; ++k) {
-                const uint64_t db = smem_desc(b_addr + k * 32);
-                const uint32_t accumulate = (it > 0 || k > 0) ? 1u : 0u;
-                tc_mma(tmem_base, smem_desc(a_addr + k * 32), db, idesc, accumulate);
-                if (A_TILES == 2) tc_mma(tmem_base + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                for (int k = 0; k < BLOCK_K / 16; ++k) {
+                    const uint64_t db = smem_desc(b_addr + k * 32);
+                    const int chain = me * own + (k & (own - 1));
+                    const uint32_t accumulate = (mine > 0 || k >= own) ? 1u : 0u;
+                    const uint32_t acc_addr = tmem_base + (uint32_t)(chain * A_TILES * s.n_tile);
+                    tc_mma(acc_addr, smem_desc(a_addr + k * 32), db, idesc, accumulate);
+                    if (A_TILES == 2) tc_mma(acc_addr + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                }
+                tc_commit(smem_u32(&empty_bar[st]));
             }
-            tc_commit(smem_u32(&empty_bar[st]));
+            if (ok) tc_commit(smem_u32(&acc_full));
+            else if (s.error_flag) atomicExch(s.error_flag, 3);
         }
-        if (ok) tc_commit(smem_u32(&acc_full));
-        else if (s.error_flag) atomicExch(s.error_flag, 3);
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp <= 5) {
         // ---- accumulator to the exchange buffer: warp w holds TMEM lanes 32*(w%4) .. +31 = features ----
         const int group = warp & 3;
         const bool ok = nkb <= 0 || mbar_wait(smem_u32(&acc_full), 0u);     // all MMAs done: the ring is free to reuse
@@ -192,6 +204,18 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (ok && nkb > 0) {
                 tmem_load16(lane_addr + (uint32_t)c0, acc);
                 if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                const int live = (s.chains >= 2 && nkb < 2) ? s.chains / 2 : s.chains;   // the second issuer's stay untouched with one K block
+                for (int chain = 1; chain < live; ++chain) {              // in chain order: the same sum in every run
+                    float more[16];
+                    tmem_load16(lane_addr + (uint32_t)(chain * A_TILES * s.n_tile + c0), more);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) acc[c] += more[c];
+                    if (MODE == GEMM_SWIGLU) {
+                        tmem_load16(lane_addr + (uint32_t)(chain * A_TILES * s.n_tile + s.n_tile + c0), more);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) up[c] += more[c];
+                    }
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) acc[c] = up[c] = 0.f;
@@ -388,7 +412,9 @@ LIA_EXPORT int lia_gemm_cluster(int mode, const void* X, int ldx, const void* W,
     s.M = M; s.N = N; s.K = K;
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-    s.tmem_cols = pow2_columns((swiglu ? 2 : 1) * plan.n_tile);
+    s.chains = 4;
+    while (s.chains > 1 && s.chains * (swiglu ? 2 : 1) * plan.n_tile > 512) s.chains /= 2;
+    s.tmem_cols = pow2_columns(s.chains * (swiglu ? 2 : 1) * plan.n_tile);
     s.ldo = ldo; s.alpha = alpha; s.error_flag = error_flag;
     const int esize = out_dtype == LIA_F32 ? 4 : 2;
     s.vector_ok = (((uintptr_t)out % (4 * esize)) == 0 && ldo % 4 == 0) ? 1 : 0;

@@ -26,6 +26,19 @@ from .step import StepEntry, StepError, StepRuntime
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
+class PendingTokens:
+    """Tokens that have been selected on the device and are on their way to the host."""
+
+    def __init__(self, engine, device_tokens, host_tokens, event):
+        self.engine, self.device_tokens, self.host_tokens, self.event = engine, device_tokens, host_tokens, event
+
+    def tokens(self) -> list:
+        self.event.synchronize()
+        tokens = self.host_tokens.tolist()
+        self.engine._raise_device_errors()
+        return tokens
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
@@ -107,14 +120,17 @@ class Engine:
         self.cache.release(slot)
 
     # ---- the step ----
-    def step(self, entries) -> torch.Tensor:
+    def step(self, entries, feed: "PendingTokens" = None) -> torch.Tensor:
         """Run one batch.  Returns 32-bit logits [wanted, vocab] on the device, in the order of the
-        entries and of each entry's `want`.  The pages for every position must have been reserved."""
+        entries and of each entry's `want`.  The pages for every position must have been reserved.
+        With `feed` (tokens selected for the step before, perhaps not read by the host yet) every entry
+        is one token, and entry i's token is row i of `feed`, taken on the device: the ids in the
+        entries only stand in."""
         entries = list(entries)
         if not entries:
             return self.runtime_step.logits(0, self.spec.vocab_size)
         with torch.cuda.device(self.device):
-            ctx = self.runtime_step.begin(entries)
+            ctx = self.runtime_step.begin(entries, feed=None if feed is None else feed.device_tokens)
             if self.cuda_graphs and ctx.decode_only:
                 logits = self._replay(ctx)
             else:
@@ -158,6 +174,12 @@ class Engine:
     def select_tokens(self, logits: torch.Tensor, samplings, positions) -> list:
         """One token per row of `logits` on the device (greedy, or Gumbel-max keyed by seed and
         position); returns host integers.  This is the step's device-to-host read."""
+        return self.select_tokens_start(logits, samplings, positions).tokens()
+
+    def select_tokens_start(self, logits: torch.Tensor, samplings, positions) -> "PendingTokens":
+        """The same, without waiting: the tokens are selected on the device and copied to pinned host
+        memory behind the step; `PendingTokens.tokens()` waits for that copy.  Meanwhile the next step may
+        be launched with the tokens fed on the device (`step(..., feed=)`)."""
         rows = logits.shape[0]
         out = self._workspace("select.out", (1, max(rows, self.max_seqs)), torch.int32)[0, :rows]
         if all(s.greedy for s in samplings):
@@ -168,9 +190,17 @@ class Engine:
             where = torch.tensor(list(positions), dtype=torch.int64)
             ops.select_tokens(logits, out, temperature.to(self.device), seeds.to(self.device),
                               where.to(self.device))
-        tokens = out.tolist()
-        self._raise_device_errors()
-        return tokens
+        if not hasattr(self, "_select_host"):
+            self._select_host = [torch.empty(self.max_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._select_events = [torch.cuda.Event() for _ in range(2)]
+            self._select_turn = 0
+        self._select_turn ^= 1                      # two buffers: a copy may be in flight while the one before is read
+        host, event = self._select_host[self._select_turn], self._select_events[self._select_turn]
+        if rows > host.numel():
+            host = self._select_host[self._select_turn] = torch.empty(rows, dtype=torch.int32, pin_memory=True)
+        host[:rows].copy_(out, non_blocking=True)
+        event.record()
+        return PendingTokens(self, out, host[:rows], event)
 
     def logits_to_host(self, logits: torch.Tensor):
         rows = logits.float().cpu().numpy()

@@ -22,6 +22,15 @@ src/server/paged/{request,schedule,preempt}.rs):
   "active KV scheduler made no progress" (schedule.rs:123-125).
 * A request is done at an end-of-sequence token or after `max_tokens` tokens; the last token is not
   fed back (request.rs:128-147).  Its pages and slot are freed at once (schedule.rs:126-137).
+
+Steady decoding is pipelined (`pipeline=True`, with an engine that offers `select_tokens_start`): while every
+live request just decodes, nothing waits to be admitted, nobody reaches `max_tokens` and the pages suffice,
+`step()` launches the next decode step with the tokens fed on the device and only then reads the tokens of
+the step before from the host copy, so the host's bookkeeping runs under the GPU's work.  What the requests
+receive does not change.  A request that the token just read ends (end of sequence) has one more token
+computed that nobody looks at; its pages are freed when that is known.  Every other situation (a prompt
+portion, an admission, a request at its last token, pages running out) first reads what is pending and then
+takes the plain path above.
 """
 from __future__ import annotations
 
@@ -62,7 +71,7 @@ class Request:
 
 class Scheduler:
     def __init__(self, engine, max_batch_tokens: int = 512, even_split: bool = False, eos_token_ids=(),
-                 context: Optional[int] = None):
+                 context: Optional[int] = None, pipeline: bool = True):
         self.engine = engine
         self.cache = engine.cache
         self.budget = int(max_batch_tokens)
@@ -74,7 +83,10 @@ class Scheduler:
         self.queue, self.paused = deque(), deque()
         self.active = [None] * self.cache.max_slots      # by slot
         self.finished = []
-        self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0, "admitted": 0}
+        self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0, "admitted": 0,
+                      "pipelined_steps": 0}
+        self.pipeline = bool(pipeline) and hasattr(engine, "select_tokens_start")
+        self._pending = None                             # (tokens on their way to the host, the requests they belong to)
 
     # ---- requests ----
     def add(self, rid, prompt, sampling: Sampling = None, max_tokens: int = 8192) -> Request:
@@ -202,8 +214,16 @@ class Scheduler:
         return plan
 
     def step(self) -> list:
-        """Admit, make room, run one batch, sample, finish.  Returns the requests that finished in
-        this step."""
+        """Admit, make room, run one batch, sample, finish.  Returns the requests that finished (with
+        `pipeline`, those whose last token this call read: it may belong to the step before)."""
+        done = []
+        if self._pending is not None:
+            if self._can_continue():
+                following = self._launch_fed()           # the GPU goes on ...
+                done = self._collect()                   # ... while the host reads the step before
+                self._pending = following
+                return done
+            done = self._collect()
         self.admit()
         self.pause_for_capacity()
         plan = self.plan()
@@ -211,7 +231,7 @@ class Scheduler:
         if not plan:
             if any(not r.done for r in live):
                 raise SchedulerError("active KV scheduler made no progress")
-            return []
+            return done
         entries, outputs = [], []
         for request, count in plan:
             start = request.computed
@@ -227,12 +247,19 @@ class Scheduler:
         logits = self.engine.step(entries)
         for request, count in plan:
             request.computed += count
+        self.stats["steps"] += 1
         if outputs:
+            if self.pipeline and all(r.sampling.on_device for r in outputs):
+                self._pending = (self._select_start(logits, outputs), outputs)
+                return done
             tokens = self._select(logits, outputs)
             now = time.perf_counter()
             for request, token in zip(outputs, tokens):
                 self._accept(request, int(token), now)
-        self.stats["steps"] += 1
+        return done + self._retire()
+
+    def _retire(self) -> list:
+        """Free what the finished requests hold."""
         done = []
         for request in self.live():
             if request.done:
@@ -243,6 +270,55 @@ class Scheduler:
                 done.append(request)
         self.finished.extend(done)
         return done
+
+    # ---- pipelined decoding ----
+    def _select_start(self, logits, requests):
+        return self.engine.select_tokens_start(logits, [r.sampling for r in requests], [r.computed - 1 for r in requests])
+
+    def _collect(self) -> list:
+        """Read the pending tokens, give them to their requests, retire the finished."""
+        pending, requests = self._pending
+        self._pending = None
+        tokens = pending.tokens()
+        now = time.perf_counter()
+        for request, token in zip(requests, tokens):
+            if request.done:                             # ended a step ago: this token was computed for nobody
+                continue
+            request.sampler.accept(int(token))
+            self._accept(request, int(token), now)
+        return self._retire()
+
+    def _can_continue(self) -> bool:
+        """Whether the step after the pending one is known before its tokens are: every live request decodes
+        on, whatever token it gets (short of an end of sequence)."""
+        _, requests = self._pending
+        live = self.live()
+        if self.queue or self.paused or len(live) != len(requests) or len(live) > self.budget:
+            return False
+        needed = 0
+        for request, other in zip(live, requests):
+            if request is not other or request.done or len(request.tokens) != request.computed:
+                return False
+            if len(request.generated) + 1 >= request.max_tokens:        # the pending token is its last
+                return False
+            needed += self.cache.pages_for(request.slot, request.computed, request.computed + 1) > 0
+        return needed <= self.cache.available_pages()
+
+    def _launch_fed(self):
+        """The next decode step of the pending step's requests, their tokens taken on the device."""
+        pending, requests = self._pending
+        entries = []
+        for request in requests:
+            if not self.cache.ensure(request.slot, request.computed, request.computed + 1):
+                raise SchedulerError("a page that was counted free could not be had")
+            entries.append(StepEntry(request.slot, [0], request.computed, [0]))
+        logits = self.engine.step(entries, feed=pending)
+        for request in requests:
+            request.computed += 1
+        self.stats["steps"] += 1
+        self.stats["pipelined_steps"] += 1
+        self.stats["decode_tokens"] += len(requests)
+        return (self._select_start(logits, requests), requests)
 
     def _select(self, logits, requests) -> list:
         """One token per output row: on the device where the rule allows it, else on the host."""

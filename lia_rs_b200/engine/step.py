@@ -144,9 +144,10 @@ class StepRuntime:
         return buf[:rows]
 
     # ---- a step's metadata ----
-    def begin(self, entries) -> StepContext:
+    def begin(self, entries, feed=None) -> StepContext:
         """Check the batch, stage its metadata and the changed block-table rows on the device,
-        and return the context for the model."""
+        and return the context for the model.  `feed` (int32, on the device): the token of entry i is
+        feed[i] (every entry then brings one token, whose id in the entry only stands in)."""
         tokens, positions, slots, out_rows, segments = [], [], [], [], []
         seen = set()
         for entry in entries:
@@ -188,6 +189,10 @@ class StepRuntime:
         total = 4 * n + n_out + len(prefill_segments)
         host[:total] = packed
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
+        if feed is not None:
+            if any(count != 1 for _, _, count, _ in segments) or feed.numel() < n or feed.dtype != torch.int32:
+                raise StepError("tokens can be fed on the device only to a step of single tokens, one per entry")
+            self._meta_device[:n].copy_(feed[:n], non_blocking=True)
         self.cache.flush()
         self._copy_event.record()
         dev = self._meta_device

@@ -162,3 +162,80 @@ def test_host_sampling_is_used_when_the_rule_needs_it():
     g = s.add("g", [1, 2, 3], Sampling(temperature=0.7, seed=3, presence_penalty=1.5), max_tokens=5)
     s.run()
     assert len(r.generated) == 5 and len(g.generated) == 5
+
+
+class PipelinedStandIn(StandInEngine):
+    """The stand-in with the engine's non-waiting selection: tokens become readable only through
+    `tokens()`, and a fed step takes them where the device would, from the last selection."""
+
+    class Pending:
+        def __init__(self, tokens):
+            self.device_tokens, self.read = tokens, False
+
+        def tokens(self):
+            self.read = True
+            return list(self.device_tokens)
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.fed_steps = 0
+
+    def select_tokens_start(self, logits, samplings, positions):
+        return self.Pending(self.select_tokens(logits, samplings, positions))
+
+    def step(self, entries, feed=None):
+        if feed is not None:
+            assert not feed.read, "a fed step after its tokens were read gains nothing: it should not happen"
+            assert all(len(e.tokens) == 1 for e in entries) and len(entries) <= len(feed.device_tokens)
+            entries = [type(e)(e.slot, [feed.device_tokens[i]], e.start, e.want) for i, e in enumerate(entries)]
+            self.fed_steps += 1
+        return super().step(entries)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_pipelined_decoding_gives_every_request_the_same_tokens(seed):
+    """Random workloads (prompt lengths, limits, end-of-sequence tokens that do occur, few pages so that
+    requests are paused, more requests than slots) through the plain and the pipelined scheduler: the same
+    tokens for every request, no page lost, and the pipelined one does feed steps on the device."""
+    rng = np.random.default_rng(seed)
+    jobs = [([int(t) for t in rng.integers(1, VOCAB, size=int(rng.integers(1, 30)))], int(rng.integers(1, 40)))
+            for _ in range(int(rng.integers(3, 9)))]
+    eos = [int(t) for t in rng.integers(0, VOCAB, size=2)] if seed % 3 else []
+    pages = int(rng.integers(24, 60))
+    results = []
+    for engine_type, pipeline in ((StandInEngine, False), (PipelinedStandIn, True)):
+        engine = engine_type(num_pages=pages, page_size=4, max_slots=3, context=128)
+        s = Scheduler(engine, max_batch_tokens=int(8 + seed), eos_token_ids=eos, context=128, pipeline=pipeline)
+        assert s.pipeline == pipeline
+        requests = [s.add(i, prompt, max_tokens=limit) for i, (prompt, limit) in enumerate(jobs)]
+        finished = s.run()
+        assert len(finished) == len(jobs) and all(r.done for r in requests)
+        assert engine.cache.available_pages() == pages and engine.cache.free_slots() == 3
+        engine.cache.check()
+        results.append([(list(r.generated), r.stopped) for r in requests])
+        if pipeline:
+            assert s.stats["pipelined_steps"] == engine.fed_steps
+            if any(limit > 4 for _, limit in jobs) and not eos:
+                assert engine.fed_steps > 0
+    assert results[0] == results[1]
+    for (prompt, limit), (generated, stopped) in zip(jobs, results[0]):
+        want = expected(prompt, limit)
+        if not stopped:
+            assert generated == want
+        else:
+            assert generated == want[:len(generated)] and generated[-1] in eos
+
+
+def test_a_request_ended_by_its_token_has_one_step_computed_for_nobody():
+    engine = PipelinedStandIn(num_pages=32)
+    prompt = [3, 4]
+    stop = expected(prompt, 3)[2]
+    assume_distinct = stop not in expected(prompt, 2)
+    s = Scheduler(engine, eos_token_ids=[stop], context=64)
+    a = s.add("a", prompt, max_tokens=20)
+    b = s.add("b", [5, 6, 7], max_tokens=6)
+    s.run()
+    if assume_distinct:
+        assert a.generated == expected(prompt, 3) and a.stopped
+    assert b.generated == expected([5, 6, 7], 6)
+    assert engine.cache.available_pages() == 32

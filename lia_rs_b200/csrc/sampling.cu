@@ -11,7 +11,14 @@
 #include "common.cuh"
 
 namespace {
-constexpr int THREADS = 1024;
+constexpr int PART_THREADS = 256;
+constexpr int MAX_ROWS = 65535;          // rows of one call (the grid's second dimension)
+
+// Ranges a row is cut into: about 2,048 tokens each, at most 64.
+inline int select_parts(int vocab) {
+    const int parts = (vocab + 2047) / 2048;
+    return parts < 1 ? 1 : (parts > 64 ? 64 : parts);
+}
 
 __device__ __forceinline__ uint32_t rotl32(uint32_t x, int r) { return (x << r) | (x >> (32 - r)); }
 
@@ -81,48 +88,98 @@ __device__ Best block_best(Best mine, Best* scratch) {
     return total;
 }
 
-// One block per row.  temperature[r] <= 0 selects greedy for that row.
-__global__ void __launch_bounds__(THREADS)
-select_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
-              const unsigned long long* __restrict__ seeds, const long long* __restrict__ positions,
-              int* __restrict__ out, int rows) {
+// A row is cut into `parts` ranges of `chunk` tokens, a CTA each, so that a handful of rows still keeps many SMs
+// busy; the CTA that finishes a row last (a counter that it leaves at zero again) picks among the ranges' bests.
+// `better` is a total order (value, then id), so the pick does not depend on which CTA that is.
+// PICK false: the row's largest logit: the greedy choice, written to out, and the reference point of the
+// Gumbel scores, written to tops.  PICK true (rows with temperature > 0 only): the best Gumbel score.
+template <bool PICK>
+__global__ void __launch_bounds__(PART_THREADS)
+select_part_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
+                   const unsigned long long* __restrict__ seeds, const long long* __restrict__ positions,
+                   int* __restrict__ out, int parts, int chunk, int* __restrict__ counters, float* __restrict__ tops,
+                   float* __restrict__ part_value, int* __restrict__ part_index) {
     __shared__ Best scratch[32];
-    const int r = blockIdx.x;
-    if (r >= rows) return;
-    const float* row = logits + (size_t)r * ld;
+    __shared__ int last;
+    pdl_launch_dependents();
+    const int r = blockIdx.y, part = blockIdx.x;
     const float T = temperature ? temperature[r] : 0.f;
+    if (PICK && !(T > 0.f)) return;
+    pdl_wait();                                        // the logits come from the kernel ahead
+    const float* row = logits + (size_t)r * ld;
+    const int begin = part * chunk, end = min(vocab, begin + chunk);
     Best mine{0.f, -1};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float x = row[i];
-        if (x != x) continue;   // a NaN never wins
-        mine = better<true>(mine, Best{x, i});
+    if (!PICK) {
+#pragma unroll 4
+        for (int i = begin + threadIdx.x; i < end; i += PART_THREADS) {
+            const float x = row[i];
+            if (x == x) mine = better<true>(mine, Best{x, i});       // a NaN never wins
+        }
+    } else {
+        const float top = tops[r];
+        const unsigned long long seed = seeds[r];
+        const unsigned long long position = (unsigned long long)positions[r];
+#pragma unroll 4
+        for (int i = begin + threadIdx.x; i < end; i += PART_THREADS) {
+            const float x = row[i];
+            if (x != x || x == -INFINITY) continue;
+            const float score = (x - top) / T + gumbel_noise(murmur_hash(seed, position, (uint32_t)i));
+            mine = better<false>(mine, Best{score, i});
+        }
     }
-    Best top = block_best<true>(mine, scratch);
-    if (!(T > 0.f)) {
-        if (threadIdx.x == 0) out[r] = top.index;
-        return;
+    const Best best = block_best<!PICK>(mine, scratch);
+    if (threadIdx.x == 0) {
+        part_value[(size_t)r * parts + part] = best.value;
+        part_index[(size_t)r * parts + part] = best.index;
+        __threadfence();
+        const int seen = atomicAdd(&counters[r], 1);
+        last = seen == parts - 1;
+        if (last) counters[r] = 0;
     }
-    const unsigned long long seed = seeds[r];
-    const unsigned long long position = (unsigned long long)positions[r];
-    mine = Best{0.f, -1};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float x = row[i];
-        if (x != x || x == -INFINITY) continue;
-        const float score = (x - top.value) / T + gumbel_noise(murmur_hash(seed, position, (uint32_t)i));
-        mine = better<false>(mine, Best{score, i});
+    __syncthreads();
+    if (!last || threadIdx.x >= 32) return;
+    __threadfence();
+    Best pick{0.f, -1};
+    for (int i = threadIdx.x; i < parts; i += 32)
+        pick = better<!PICK>(pick, Best{__ldcg(part_value + (size_t)r * parts + i), __ldcg(part_index + (size_t)r * parts + i)});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, pick.value, o), __shfl_xor_sync(0xffffffffu, pick.index, o)};
+        pick = better<!PICK>(pick, other);
     }
-    Best pick = block_best<false>(mine, scratch);
-    if (threadIdx.x == 0) out[r] = pick.index;
+    if (threadIdx.x == 0) {
+        out[r] = pick.index;
+        if (!PICK) tops[r] = pick.value;
+    }
 }
 }  // namespace
 
+// Floats of scratch that `rows` rows of `vocab` logits need (zero before the first call).  Its first MAX_ROWS words
+// are the rows' counters, whatever the number of rows, and every call leaves them zero; the rest is rewritten by
+// every call.
+LIA_EXPORT long long lia_select_tokens_scratch_floats(int rows, int vocab) {
+    const int parts = select_parts(vocab);
+    return (long long)MAX_ROWS + (long long)rows * (1 + 2 * parts);
+}
+
 // logits [rows, ld >= vocab] 32-bit; temperature [rows] (may be null: all greedy);
-// seeds [rows] u64, positions [rows] i64 (used only where temperature > 0); out [rows] i32.
+// seeds [rows] u64, positions [rows] i64 (used only where temperature > 0); out [rows] i32;
+// scratch: lia_select_tokens_scratch_floats(rows, vocab) 32-bit words.
 LIA_EXPORT int lia_select_tokens(const float* logits, int ld, int vocab, const float* temperature,
                                  const unsigned long long* seeds, const long long* positions, int* out,
-                                 int rows, cudaStream_t stream) {
+                                 int rows, float* scratch, long long scratch_floats, cudaStream_t stream) {
     if (rows <= 0) return LIA_OK;
-    if (vocab <= 0 || ld < vocab) return LIA_ERR_SIZE;
-    select_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, temperature, seeds, positions, out, rows);
-    return lia_check_launch();
+    if (vocab <= 0 || ld < vocab || rows > MAX_ROWS) return LIA_ERR_SIZE;
+    if (!scratch || scratch_floats < lia_select_tokens_scratch_floats(rows, vocab)) return LIA_ERR_SIZE;
+    const int parts = select_parts(vocab);
+    const int chunk = (vocab + parts - 1) / parts;
+    int* counters = reinterpret_cast<int*>(scratch);
+    float* tops = scratch + MAX_ROWS;
+    float* part_value = tops + rows;
+    int* part_index = reinterpret_cast<int*>(part_value + (size_t)rows * parts);
+    int rc = lia_launch(select_part_kernel<false>, dim3(parts, rows), dim3(PART_THREADS), 0, stream, logits, ld, vocab,
+                        temperature, seeds, positions, out, parts, chunk, counters, tops, part_value, part_index);
+    if (rc != LIA_OK || !temperature) return rc;
+    return lia_launch(select_part_kernel<true>, dim3(parts, rows), dim3(PART_THREADS), 0, stream, logits, ld, vocab,
+                      temperature, seeds, positions, out, parts, chunk, counters, tops, part_value, part_index);
 }

@@ -70,7 +70,9 @@ class _Signatures:
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
     lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
-    lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                         ctypes.c_longlong, c_void_p]
+    lia_select_tokens_scratch_floats = [c_int, c_int]
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -341,6 +343,9 @@ def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slo
            "attention_prefill_tc")
 
 
+_select_scratch = {}
+
+
 def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
     _cuda(logits, out, temperature, seeds, positions)
     rows, vocab = logits.shape
@@ -348,8 +353,16 @@ def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
         raise KernelError("select_tokens takes 32-bit logits and writes int32 tokens")
     if temperature is not None and (seeds is None or positions is None):
         raise KernelError("select_tokens: temperature needs seeds and positions")
+    key = torch.device(logits.device).index or 0
+    fn = lib().lia_select_tokens_scratch_floats
+    fn.restype = ctypes.c_longlong
+    need = int(fn(rows, vocab))
+    scratch = _select_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        # zeroed: its head holds the rows' counters, which every call leaves at zero
+        scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
     _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
-                                   _p(positions), _p(out), rows, _stream()), "select_tokens")
+                                   _p(positions), _p(out), rows, _p(scratch), scratch.numel(), _stream()), "select_tokens")
 
 
 def decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits) -> bool:

@@ -51,7 +51,8 @@ constexpr int COUNTER_WORDS = 4096;            // tile counters at the head of t
 struct Shape {
     int M, N, K;              // tokens, output features (per half for SWIGLU), reduction length
     int n_total;              // rows of W: N, or 2N for SWIGLU
-    int n_tile;               // tokens per tile: 16..256, a multiple of 16
+    int n_tile;               // tokens per tile: 16..512, a multiple of 16 (of 32 beyond 256: two MMAs, two X boxes)
+    int x_box;                // tokens per TMA box of X: n_tile, or half of it beyond 256
     int stages;
     int kblocks;              // ceil(K / 64)
     int splits;               // K ranges per tile
@@ -172,6 +173,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
                 }
                 tma_load_2d(dst + A_TILES * a_bytes, &map_x, kb * BLOCK_K, u.t0, full);
+                if (s.x_box < s.n_tile)
+                    tma_load_2d(dst + A_TILES * a_bytes + (uint32_t)s.x_box * 128u, &map_x, kb * BLOCK_K, u.t0 + s.x_box, full);
                 issued = it + 1;
             }
         }
@@ -183,7 +186,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
-        const uint32_t idesc = instr_desc(TILE_F, s.n_tile);
+        // a tile of more than 256 tokens takes two MMAs per K step: 256 tokens, then the rest
+        const int n_first = s.n_tile > 256 ? 256 : s.n_tile, n_rest = s.n_tile - n_first;
+        const uint32_t idesc = instr_desc(TILE_F, n_first), idesc_rest = instr_desc(TILE_F, n_rest > 0 ? n_rest : 16);
         bool ok = true;
         int it = 0, n_unit = 0;
         for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
@@ -199,12 +204,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t b_addr = a_addr + A_TILES * a_bytes;
+                // (the issuing thread sets the pace of a 256-wide tile: the wide tile's second MMA has a loop of its own,
+                // so that the common loop carries nothing for it)
+                if (n_rest == 0) {
 #pragma unroll
-                for (int k = 0; k < BLOCK_K / 16; ++k) {
-                    const uint64_t db = smem_desc(b_addr + k * 32);
-                    const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
-                    tc_mma(acc, smem_desc(a_addr + k * 32), db, idesc, accumulate);
-                    if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                    for (int k = 0; k < BLOCK_K / 16; ++k) {
+                        const uint64_t db = smem_desc(b_addr + k * 32);
+                        const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
+                        tc_mma(acc, smem_desc(a_addr + k * 32), db, idesc, accumulate);
+                        if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / 16; ++k) {
+                        const uint64_t da = smem_desc(a_addr + k * 32);
+                        const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
+                        tc_mma(acc, da, smem_desc(b_addr + k * 32), idesc, accumulate);
+                        tc_mma(acc + (uint32_t)n_first, da, smem_desc(b_addr + (uint32_t)n_first * 128u + k * 32), idesc_rest, accumulate);
+                    }
                 }
                 tc_commit(smem_u32(&empty_bar[st]));      // the stage is free when these MMAs have read it
             }
@@ -392,10 +409,12 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
         // least idle: rounds of tiles times the time of one.  Measured on a B200: a tile takes 5.5 us plus 0.43 us
         // per K block of a 256-wide tile, so in units of "tokens of width" the fixed part is 3244 / K blocks;
         // ties go to the wider tile (fewer bytes through shared memory per flop)
+        // Up to 512 tokens wide (all of TMEM, so one buffer: the epilogue and the next tile take turns), where that
+        // saves a round: 2,048 tokens x 2,560 features are 140 tiles of 320 tokens, one round, against 260 of 160.
         const double fixed = 3244.0 / (double)kblocks;
         double best = -1;
         p.n_tile = 256;
-        for (int n = 256; n >= 128; n -= 32) {
+        for (int n = 512; n >= 128; n -= 32) {
             const long long tiles = (long long)p.f_tiles * ((M + n - 1) / n);
             const long long rounds = (tiles + sm_count - 1) / sm_count;
             const double cost = (double)rounds * ((double)n + fixed);
@@ -453,6 +472,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     s.M = M; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    s.x_box = plan.n_tile > 256 ? plan.n_tile / 2 : plan.n_tile;
     s.acc_cols = swiglu ? 2 * plan.n_tile : plan.n_tile;
     s.acc_buffers = 2 * s.acc_cols <= 512 ? 2 : 1;
     s.tmem_cols = pow2_at_least(s.acc_buffers * s.acc_cols);
@@ -469,7 +489,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     CUtensorMap mw, mx, mo;
     int rc;
     if ((rc = make_map(&mw, W, s.n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
-    if ((rc = make_map(&mx, X, M, K, ldx, plan.n_tile)) != LIA_OK) return rc;
+    if ((rc = make_map(&mx, X, M, K, ldx, s.x_box)) != LIA_OK) return rc;
     if (s.via_tma) {
         if ((rc = make_out_map(&mo, out, out_dtype, M, N, ldo, STAGING_TOKENS)) != LIA_OK) return rc;
     } else {

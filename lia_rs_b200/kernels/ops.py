@@ -180,6 +180,14 @@ def gemm_tc_accepts(mode, a, w, out) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def gemm_tc_tiles_fill_the_sms(a, out) -> bool:
+    """Whether the product's output tiles (128 features each, all tokens of up to 256 in one) are at least
+    three quarters as many as the device has SMs: the tcgen05 kernel then streams the weights with every SM at
+    work without cutting K, whatever the number of tokens."""
+    _, sms = _device_scratch(a.device)
+    return 4 * ((out.shape[1] + 127) // 128) >= 3 * sms
+
+
 def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores; see csrc/gemm_tc.cu.  Products
     with few tiles split K and use this device's scratch, so calls on one device must not overlap."""

@@ -1,15 +1,16 @@
 // Decode attention over the paged bfloat16 cache, split over the keys.
 //
-// One CTA serves one decoded token's query heads of ONE kv head (up to 16 of them: they are the 16
-// rows of the MMA's M, so the keys of a group are read once for all its query heads) over ONE range of
-// keys.  Its four warps take 16 keys each of every 64-key tile: S = Q K^T by mma.sync (bf16 in, 32-bit
-// out), running maximum and sum per row in 32-bit (base-2 exponentials with the scale folded in),
-// P in bf16 back into the tensor cores against V.  Keys and values come from their pages through a
+// One CTA serves one decoded token's query heads of ONE kv head (up to 16 of them, so the keys of a group are
+// read once for all its query heads) over ONE range of keys.  Its four warps take 16 keys each of every 64-key
+// tile.  The KEYS are the 16 rows of the MMA's M and the heads its N (8, or twice 8): S^T = K Q^T by mma.sync
+// (bf16 in, 32-bit out), so a group of 8 heads wastes nothing of the instruction; running maximum and sum per
+// head in 32-bit (base-2 exponentials with the scale folded in); P^T in bf16, turned into an operand with
+// movmatrix, back into the tensor cores: O^T = V^T P^T.  Keys and values come from their pages through a
 // three-stage cp.async ring in shared memory; ldmatrix (transposed for V) builds the fragments.  The
 // four warps' partial results are merged in shared memory; the CTA then writes either the final
-// output (one range) or a normalised partial output with its log-sum-exp to scratch, which
-// `attention_merge_kernel` combines.  Ranges are `split_len` keys long, counted from the first visible
-// key, so how a token's keys are cut depends on its own position, the window and split_len only.
+// output (one range) or a normalised partial output with its log-sum-exp to scratch, which the last CTA of the
+// token to finish (or `attention_merge_kernel`) combines.  Ranges are `split_len` keys long, counted from the
+// first visible key, so how a token's keys are cut depends on its own position, the window and split_len only.
 //
 // The work of this kernel is streaming the cache: 2 * kv_heads * head_dim * 2 bytes per key and token.
 #include "attention_tc.cuh"
@@ -61,7 +62,14 @@ __device__ __forceinline__ float exp2_whole(float n) {
     return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
 }
 
-template <int D>
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t pair) {       // movmatrix: the 8 x 8 matrix of 16-bit elements a warp holds, transposed
+    uint32_t out;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(out) : "r"(pair));
+    return out;
+}
+
+// NH: groups of 8 query heads per kv head that the CTA serves (1 or 2)
+template <int D, int NH>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(Params p) {
     using T = Tile<D>;
@@ -146,7 +154,7 @@ attention_decode_kernel(Params p) {
     }
 
     // ---- Q fragments: rows = heads (row r -> head h0 + r), zero beyond `heads` ----
-    uint32_t qf[D / 16][4];
+    uint32_t qb[D / 16][NH][2];          // Q^T as the MMA's second operand: lane (g, t) holds head g (+ 8), d = 2t, 2t + 1 (+ 8)
     if (p.qkv) {
         __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * 2 * T::BYTES);       // [16][D]
         const int width = (p.nq + 2 * p.nkv) * D;
@@ -235,34 +243,42 @@ attention_decode_kernel(Params p) {
         }
         const int r0 = lane >> 2, c = (lane & 3) * 2;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int col = kk * 16 + c;
-            qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + r0 * D + col);
-            qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * D + col);
-            qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_s + r0 * D + col + 8);
-            qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * D + col + 8);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const __nv_bfloat16* src = q_s + (h * 8 + r0) * D + kk * 16 + c;
+                qb[kk][h][0] = *reinterpret_cast<const uint32_t*>(src);
+                qb[kk][h][1] = *reinterpret_cast<const uint32_t*>(src + 8);
+            }
     } else {
         pdl_wait();
         const int r0 = lane >> 2, c = (lane & 3) * 2;
         const __nv_bfloat16* base = p.q + ((size_t)t * p.nq + h0) * D;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int col = kk * 16 + c;
-            qf[kk][0] = r0 < heads ? *reinterpret_cast<const uint32_t*>(base + (size_t)r0 * D + col) : 0u;
-            qf[kk][1] = r0 + 8 < heads ? *reinterpret_cast<const uint32_t*>(base + (size_t)(r0 + 8) * D + col) : 0u;
-            qf[kk][2] = r0 < heads ? *reinterpret_cast<const uint32_t*>(base + (size_t)r0 * D + col + 8) : 0u;
-            qf[kk][3] = r0 + 8 < heads ? *reinterpret_cast<const uint32_t*>(base + (size_t)(r0 + 8) * D + col + 8) : 0u;
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const bool there = h * 8 + r0 < heads;
+                const __nv_bfloat16* src = base + (size_t)(h * 8 + r0) * D + kk * 16 + c;
+                qb[kk][h][0] = there ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+                qb[kk][h][1] = there ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+            }
     }
 
-    float o[D / 8][4];
+    // O^T: d = 16 mt + g (+ 8) down the rows, head 8 h + 2 t (+ 1) across; lane (g, t) holds [mt][h][0..3]
+    float o[D / 16][NH][4];
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
-    // shared-memory offsets of this lane's ldmatrix rows inside a tile (the tile's base is added per stage)
+    for (int mt = 0; mt < D / 16; ++mt)
+#pragma unroll
+        for (int h = 0; h < NH; ++h) o[mt][h][0] = o[mt][h][1] = o[mt][h][2] = o[mt][h][3] = 0.f;
+    // per head 8 h + 2 t + j: the running maximum (the same in the 8 lanes that share t) and THIS lane's part of the sum
+    float head_max[NH][2], head_sum[NH][2];
+#pragma unroll
+    for (int h = 0; h < NH; ++h) { head_max[h][0] = head_max[h][1] = -INFINITY; head_sum[h][0] = head_sum[h][1] = 0.f; }
+    // shared-memory offsets of this lane's ldmatrix rows inside a tile (the tile's base is added per stage):
+    // keys as the first operand want the matrices in the order (keys 0-7, k low), (keys 8-15, k low), (.., k high)
     const int lm = lane >> 3;
-    const int k_row = warp * 16 + (lm >> 1) * 8 + (lane & 7), v_row = warp * 16 + (lm & 1) * 8 + (lane & 7);
+    const int k_row = warp * 16 + (lm & 1) * 8 + (lane & 7), v_row = warp * 16 + (lm >> 1) * 8 + (lane & 7);
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         // groups asked for so far: STAGES, and one per earlier iteration but the first; tile i is group i
@@ -277,80 +293,69 @@ attention_decode_kernel(Params p) {
         const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES, vs = ks + T::BYTES;
         const int key0 = key_begin + tile * TILE_KEYS + warp * 16;       // this warp's 16 keys
         if (key0 < key_end) {
-            // ---- S = Q K^T for 16 keys: two n-tiles of 8.  All fragments are asked for before the first
-            //      product (one warp per scheduler: nothing else hides the shared-memory latency), and
-            //      the sums run in four chains that meet at the end ----
+            // ---- S^T = K Q^T for 16 keys.  All fragments are asked for before the first product (one warp per
+            //      scheduler: nothing else hides the shared-memory latency); the sums run in two chains per
+            //      group of heads that meet at the end ----
             uint32_t kf[D / 16][4];
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk)
-                ldmatrix_x4(ks + T::offset(k_row, kk * 2 + (lm & 1)), kf[kk][0], kf[kk][1], kf[kk][2], kf[kk][3]);
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                ldmatrix_x4(ks + T::offset(k_row, kk * 2 + (lm >> 1)), kf[kk][0], kf[kk][1], kf[kk][2], kf[kk][3]);
+            float st[NH][4], st_odd[NH][4];
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                mma_bf16(kk & 1 ? s_odd[0] : s[0], qf[kk], kf[kk][0], kf[kk][1]);
-                mma_bf16(kk & 1 ? s_odd[1] : s[1], qf[kk], kf[kk][2], kf[kk][3]);
-            }
-            // the values' fragments travel while the probabilities are made
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) st[h][i] = st_odd[h][i] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+                for (int h = 0; h < NH; ++h) mma_bf16(kk & 1 ? st_odd[h] : st[h], kf[kk], qb[kk][h][0], qb[kk][h][1]);
+            // the values' fragments travel while the probabilities are made: V^T as the first operand
             uint32_t vf[D / 16][4];
 #pragma unroll
-            for (int j = 0; j < D / 8; j += 2)
-                ldmatrix_x4_trans(vs + T::offset(v_row, j + (lm >> 1)), vf[j / 2][0], vf[j / 2][1], vf[j / 2][2], vf[j / 2][3]);
+            for (int mt = 0; mt < D / 16; ++mt)
+                ldmatrix_x4_trans(vs + T::offset(v_row, mt * 2 + (lm & 1)), vf[mt][0], vf[mt][1], vf[mt][2], vf[mt][3]);
+            // st[h][0], [1]: key g, heads 2t, 2t + 1; [2], [3]: key g + 8
+            const bool low_hidden = key0 + (lane >> 2) >= key_end, high_hidden = key0 + (lane >> 2) + 8 >= key_end;
+            uint32_t pb[NH][2];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int h = 0; h < NH; ++h) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s[nt][i] += s_odd[nt][i];
-            // ---- mask (only the range's last keys need it), running maximum and sum ----
-            if (key0 + 16 > key_end) {
+                for (int i = 0; i < 4; ++i) st[h][i] += st_odd[h][i];
+                if (low_hidden) st[h][0] = st[h][1] = -INFINITY;       // (only the range's last keys can be)
+                if (high_hidden) st[h][2] = st[h][3] = -INFINITY;
+                float correction[2], e[4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int j = 0; j < 2; ++j) {
+                    float top = fmaxf(st[h][j], st[h][j + 2]);
+                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
+                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 8));
+                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 16));
+                    // The reference point of the exponentials is a whole number (in base-2 logarithms), so the
+                    // 16-bit probabilities have the same mantissas whatever tile, warp or range a key falls
+                    // in, and rescaling by `correction` (a power of two) is exact.
+                    const float new_max = fmaxf(head_max[h][j], ceilf(top * p.scale_log2));   // finite: key0 < key_end
+                    correction[j] = exp2_whole(head_max[h][j] - new_max);
+                    head_max[h][j] = new_max;
+                    e[j] = ex2_approx(fmaf(st[h][j], p.scale_log2, -new_max));
+                    e[j + 2] = ex2_approx(fmaf(st[h][j + 2], p.scale_log2, -new_max));
+                    head_sum[h][j] = head_sum[h][j] * correction[j] + (e[j] + e[j + 2]);
+                }
+                // P^T as the second operand: what lane (g, t) holds of P (key g, heads 2t, 2t+1) it must hold of P^T
+                pb[h][0] = transpose_8x8(pack_bf16(e[0], e[1]));
+                pb[h][1] = transpose_8x8(pack_bf16(e[2], e[3]));
+                // ---- O^T = O^T * correction + V^T P^T (the maximum is a whole number and seldom moves) ----
+                if (__any_sync(0xffffffffu, correction[0] != 1.f || correction[1] != 1.f)) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (key0 + nt * 8 + (lane & 3) * 2 + (i & 1) >= key_end) s[nt][i] = -INFINITY;
-            }
-            float tile_max[2];
-            tile_max[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-            tile_max[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-            float correction[2];
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-                tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-                // The reference point of the exponentials is a whole number (in base-2 logarithms), so the
-                // 16-bit probabilities have the same mantissas whatever tile, warp or range a key falls
-                // in, and rescaling by `correction` (a power of two) is exact.
-                const float new_max = fmaxf(row_max[r], ceilf(tile_max[r] * p.scale_log2));   // finite: key0 < key_end
-                correction[r] = exp2_whole(row_max[r] - new_max);
-                row_max[r] = new_max;
-                row_sum[r] *= correction[r];
-            }
-            uint32_t pf[4];
-            {
-                float e[2][4];
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        e[nt][i] = ex2_approx(fmaf(s[nt][i], p.scale_log2, -row_max[i >> 1]));
-                        row_sum[i >> 1] += e[nt][i];
+                    for (int mt = 0; mt < D / 16; ++mt) {
+                        o[mt][h][0] *= correction[0]; o[mt][h][1] *= correction[1];
+                        o[mt][h][2] *= correction[0]; o[mt][h][3] *= correction[1];
                     }
-                pf[0] = pack_bf16(e[0][0], e[0][1]);
-                pf[1] = pack_bf16(e[0][2], e[0][3]);
-                pf[2] = pack_bf16(e[1][0], e[1][1]);
-                pf[3] = pack_bf16(e[1][2], e[1][3]);
-            }
-            // ---- O = O * correction + P V (the maximum is a whole number and seldom moves) ----
-            if (__any_sync(0xffffffffu, correction[0] != 1.f || correction[1] != 1.f)) {
-#pragma unroll
-                for (int j = 0; j < D / 8; ++j) {
-                    o[j][0] *= correction[0]; o[j][1] *= correction[0]; o[j][2] *= correction[1]; o[j][3] *= correction[1];
                 }
             }
 #pragma unroll
-            for (int j = 0; j < D / 8; j += 2) {
-                mma_bf16(o[j], pf, vf[j / 2][0], vf[j / 2][1]);
-                mma_bf16(o[j + 1], pf, vf[j / 2][2], vf[j / 2][3]);
-            }
+            for (int mt = 0; mt < D / 16; ++mt)
+#pragma unroll
+                for (int h = 0; h < NH; ++h) mma_bf16(o[mt][h], vf[mt], pb[h][0], pb[h][1]);
         }
     }
     cp_async_wait<0>();
@@ -358,26 +363,38 @@ attention_decode_kernel(Params p) {
 
     // ---- merge the four warps (each saw a quarter of the keys) ----
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
-        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
-    }
-    constexpr int MERGE_STRIDE = D + 8;                               // rows 8 words apart: the 8-byte stores of a warp meet no bank twice
+    for (int h = 0; h < NH; ++h)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {                                 // the eight lanes that share t hold parts of a head's sum
+            head_sum[h][j] += __shfl_xor_sync(0xffffffffu, head_sum[h][j], 4);
+            head_sum[h][j] += __shfl_xor_sync(0xffffffffu, head_sum[h][j], 8);
+            head_sum[h][j] += __shfl_xor_sync(0xffffffffu, head_sum[h][j], 16);
+        }
+    constexpr int MERGE_STRIDE = D + 4;                               // heads 4 words apart: a warp's 32 stores meet 32 banks
     float* merge_o = reinterpret_cast<float*>(smem);                  // [WARPS][16][MERGE_STRIDE]
     float* merge_m = merge_o + WARPS * 16 * MERGE_STRIDE;             // [WARPS][16]
     float* merge_l = merge_m + WARPS * 16;
     float* merge_f = merge_l + WARPS * 16;                            // [WARPS][16] each warp's share of a row
     {
-        const int r0 = lane >> 2, c = (lane & 3) * 2;
+        const int g = lane >> 2, t2 = (lane & 3) * 2;
 #pragma unroll
-        for (int j = 0; j < D / 8; ++j) {
-            float* dst = merge_o + ((size_t)warp * 16 + r0) * MERGE_STRIDE + j * 8 + c;
-            *reinterpret_cast<float2*>(dst) = make_float2(o[j][0], o[j][1]);
-            *reinterpret_cast<float2*>(dst + 8 * MERGE_STRIDE) = make_float2(o[j][2], o[j][3]);
-        }
-        if ((lane & 3) == 0) {
-            merge_m[warp * 16 + r0] = row_max[0]; merge_m[warp * 16 + r0 + 8] = row_max[1];
-            merge_l[warp * 16 + r0] = row_sum[0]; merge_l[warp * 16 + r0 + 8] = row_sum[1];
+        for (int mt = 0; mt < D / 16; ++mt)
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                float* dst = merge_o + ((size_t)warp * 16 + h * 8 + t2) * MERGE_STRIDE + mt * 16 + g;
+                dst[0] = o[mt][h][0];
+                dst[MERGE_STRIDE] = o[mt][h][1];
+                dst[8] = o[mt][h][2];
+                dst[MERGE_STRIDE + 8] = o[mt][h][3];
+            }
+        if (g == 0) {
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    merge_m[warp * 16 + h * 8 + t2 + j] = head_max[h][j];
+                    merge_l[warp * 16 + h * 8 + t2 + j] = head_sum[h][j];
+                }
         }
     }
     __syncthreads();
@@ -549,21 +566,21 @@ __global__ void attention_merge_kernel(Params p) {
     }
 }
 
-template <int D>
+template <int D, int NH>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
     const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4 + 18 * D * 4;   // the tiles, the rotated queries, the angles' cosines and sines, the step's 32-bit rows
-    const size_t merge = (size_t)WARPS * 16 * (D + 8 + 3) * sizeof(float);
+    const size_t merge = (size_t)WARPS * 16 * (D + 4 + 3) * sizeof(float);
     const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
     const size_t smem = ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return LIA_ERR_LAUNCH;
         configured = true;
     }
     const int group = p.nq / p.nkv;
     dim3 grid(n_rows, p.nkv * ((group + 15) / 16), p.n_splits);
-    int rc = lia_launch(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream, p);
+    int rc = lia_launch(attention_decode_kernel<D, NH>, grid, dim3(WARPS * 32), smem, stream, p);
     if (rc != LIA_OK) return rc;
     if (p.n_splits > 1 && !p.counters)
         rc = lia_launch(attention_merge_kernel<D>, dim3(n_rows, p.nq), dim3(D < 128 ? D : 128), 0, stream, p);
@@ -611,8 +628,9 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
         if (page_size == (1 << b)) p.page_shift = b;
     p.n_tokens = n_tokens; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
     p.split_len = split_len; p.n_splits = n_splits; p.scale_log2 = scale * LOG2E;
-    if (d == 128) return launch_decode<128>(p, n_rows, stream);
-    if (d == 64) return launch_decode<64>(p, n_rows, stream);
-    if (d == 32) return launch_decode<32>(p, n_rows, stream);
+    const bool wide = nq / nkv > 8;             // more than 8 query heads per kv head: two groups of 8 per CTA
+    if (d == 128) return wide ? launch_decode<128, 2>(p, n_rows, stream) : launch_decode<128, 1>(p, n_rows, stream);
+    if (d == 64) return wide ? launch_decode<64, 2>(p, n_rows, stream) : launch_decode<64, 1>(p, n_rows, stream);
+    if (d == 32) return wide ? launch_decode<32, 2>(p, n_rows, stream) : launch_decode<32, 1>(p, n_rows, stream);
     return LIA_ERR_SIZE;
 }

@@ -196,13 +196,26 @@ attention_decode_kernel(Params p) {
             }
         }
         __syncthreads();
-#pragma unroll 4
-        for (int w = tid; w < heads * half; w += WARPS * 32) {
-            const int r = w / half, i = w % half;
+        if (p.rotary_dim == D) {
+            // the whole head rotates (the usual case): a thread keeps its column, so its angle, and walks the heads
+            constexpr int HALF = D / 2, STEP = WARPS * 32 / HALF > 0 ? WARPS * 32 / HALF : 1;
+            const int i = tid % HALF;
             const float cs = rotation[i].x, sn = rotation[i].y;
-            const float a = raw[r * D + i], b = raw[r * D + i + half];
-            q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
-            q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+#pragma unroll 4
+            for (int r = tid / HALF; r < heads; r += STEP) {
+                const float a = raw[r * D + i], b = raw[r * D + i + HALF];
+                q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
+                q_s[r * D + i + HALF] = __float2bfloat16_rn(b * cs + a * sn);
+            }
+        } else {
+#pragma unroll 4
+            for (int w = tid; w < heads * half; w += WARPS * 32) {
+                const int r = w / half, i = w % half;
+                const float cs = rotation[i].x, sn = rotation[i].y;
+                const float a = raw[r * D + i], b = raw[r * D + i + half];
+                q_s[r * D + i] = __float2bfloat16_rn(a * cs - b * sn);
+                q_s[r * D + i + half] = __float2bfloat16_rn(b * cs + a * sn);
+            }
         }
         for (int w = tid; w < heads * (D - p.rotary_dim); w += WARPS * 32) {
             const int r = w / (D - p.rotary_dim), i = p.rotary_dim + w % (D - p.rotary_dim);
@@ -449,16 +462,18 @@ attention_decode_kernel(Params p) {
     //      order, so the result does not depend on which CTA that is ----
     const int used = min(p.n_splits, (pos + 1 - first + split_len - 1) / split_len);
     int* counter = p.counters + blockIdx.x * gridDim.y + blockIdx.y;
-    __threadfence();
+    // The CTA's partial results are published by ONE release: the barrier orders every thread's stores before
+    // thread 0's atomic, whose release carries them along (and its acquire, with the barrier after it, orders the
+    // last CTA's loads behind the other CTAs' releases): one trip instead of a fence in each thread and an atomic.
     __syncthreads();
     if (tid == 0) {
-        const int seen = atomicAdd(counter, 1);
+        int seen;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(seen) : "l"(counter) : "memory");
         last_flag = seen == used - 1;
         if (seen == used - 1) *counter = 0;
     }
     __syncthreads();
     if (!last_flag) return;
-    __threadfence();
     const float* lse = p.partial + (size_t)p.n_tokens * p.nq * p.n_splits * D;
     if (used <= 16) {
         // Few ranges: a thread owns eight elements of a head and has every load it needs (the ranges'

@@ -222,6 +222,36 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
     extern __shared__ float rotation[];                  // [half] cosines, then [half] sines
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &rotation[half + i], &rotation[i]);
     __syncthreads();
+    if (rotary_dim == d && d % 8 == 0) {
+        // The usual case, four elements at a time: 16-byte loads of the 32-bit row, 8-byte (or 16-byte) stores.
+        // (Rows of qkv, q_out and the pages are multiples of 4 elements long from 16-byte-aligned bases.)
+        const int quads = half / 4;
+        for (int w = threadIdx.x; w < rot_heads * quads; w += blockDim.x) {
+            const int head = w / quads, i = (w % quads) * 4;
+            const float4 a = *reinterpret_cast<const float4*>(row + head * d + i);
+            const float4 b = *reinterpret_cast<const float4*>(row + head * d + i + half);
+            const float4 c = *reinterpret_cast<const float4*>(rotation + i), sn = *reinterpret_cast<const float4*>(rotation + half + i);
+            const float lo[4] = {a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w};
+            const float hi[4] = {b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y, b.z * c.z + a.z * sn.z, b.w * c.w + a.w * sn.w};
+            if (head < nq) {
+                TQ* dst = q_out + (size_t)t * nq * d + head * d + i;
+                store4<TQ>(dst, lo[0], lo[1], lo[2], lo[3]);
+                store4<TQ>(dst + half, hi[0], hi[1], hi[2], hi[3]);
+            } else if (cache_ok) {
+                TC* dst = k_pages + cache_row + (head - nq) * d + i;
+                store4<TC>(dst, lo[0], lo[1], lo[2], lo[3]);
+                store4<TC>(dst + half, hi[0], hi[1], hi[2], hi[3]);
+            }
+        }
+        if (cache_ok) {
+            const float* v = row + (nq + nkv) * d;
+            for (int w = threadIdx.x * 4; w < nkv * d; w += blockDim.x * 4) {
+                const float4 x = *reinterpret_cast<const float4*>(v + w);
+                store4<TC>(v_pages + cache_row + w, x.x, x.y, x.z, x.w);
+            }
+        }
+        return;
+    }
     // rotated part: one work item per (head, i < half)
     for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
         const int head = w / half, i = w % half;

@@ -30,7 +30,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the 2B-class configuration
+# the 2B-class configuration the headline numbers are quoted on
 CONFIG_2B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048, intermediate_size=6144,
                  num_hidden_layers=40, num_attention_heads=16, num_key_value_heads=2, head_dim=128,
                  vocab_size=73448, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,

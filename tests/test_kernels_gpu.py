@@ -220,7 +220,7 @@ def test_select_tokens_greedy_ties_and_gumbel_matches_the_host_rule():
 
 
 @pytest.mark.parametrize("M", [1, 8, 40, 64, 100, 300, 1000])
-@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96)])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (15000, 520)])
 def test_gemm_tc_all_epilogues_against_64_bit(M, N, K):
     """The tcgen05 product at sizes that are no multiple of its tiles, with and without split K."""
     o = ops()

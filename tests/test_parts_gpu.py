@@ -171,3 +171,32 @@ def test_order_of_layers_is_data(tmp_path, dtype):
     got += [replay.step([("a", [t], [0])]) for t in tokens[11:]]
     import numpy as np
     helpers.assert_close(np.concatenate(got), want, dtype, "looped order")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16384, 512), (8, 16384, 512), (24, 16384, 264), (8, 2048, 512), (16, 2048, 1024),
+                                   (24, 2048, 512), (40, 1024, 2048), (300, 1024, 512), (8, 1000, 100), (5, 333, 72)])
+def test_linear_gives_the_product_whichever_kernel_it_chooses(M, N, K):
+    """`linear` sends a bfloat16 product to one of four kernels by its shape (many output tiles: the tcgen05
+    kernel at any number of tokens; few tokens: the streaming kernel; more: the cluster kernel; what TMA cannot
+    address: the streaming kernel or the 32-bit pipes): every choice gives the product, with every epilogue."""
+    from lia_rs_b200.parts import Runtime
+    from lia_rs_b200.parts.linear import ACCUM, STORE, SWIGLU, linear
+    rt = Runtime(DEV, torch.bfloat16)
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    exact = a.double() @ w.double().T
+    scale = max(1.0, float(exact.abs().max()))
+    out = torch.empty(M, N, device=DEV)
+    linear(rt, STORE, a, w[:N], out, 0.5)
+    assert float((out.double() - 0.5 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(max(K, 64) / 64)
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    linear(rt, ACCUM, a, w[:N], acc, 1.5)
+    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(max(K, 64) / 64)
+    act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    linear(rt, SWIGLU, a, w, act)
+    gate, up = exact[:, :N], exact[:, N:]
+    want = up * gate / (1 + torch.exp(-gate))
+    assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()

@@ -206,6 +206,112 @@ def time_prefill(engine, warmup=2, repeats=3):
     return best
 
 
+# The family's other sizes and the workloads they are quoted on (--workload): not the contract's line, one line each.
+CONFIG_8B = dict(CONFIG_2B, hidden_size=4096, num_attention_heads=32, intermediate_size=16384, num_hidden_layers=32,
+                 tie_word_embeddings=False)
+CONFIG_05B = dict(CONFIG_2B, hidden_size=1024, num_attention_heads=16, head_dim=64, intermediate_size=4096,
+                  num_hidden_layers=24)
+
+
+def fill_in_portions(engine, batch, prompt_tokens, portion, rng_seed):
+    """As `fill`, with prompts longer than a step takes: `portion` tokens a step."""
+    import numpy as np
+    from lia_rs_b200.engine import StepEntry
+    rng = np.random.default_rng(rng_seed)
+    slots = []
+    for _ in range(batch):
+        slot = engine.admit()
+        assert engine.reserve(slot, 0, prompt_tokens)
+        for start in range(0, prompt_tokens, portion):
+            count = min(portion, prompt_tokens - start)
+            tokens = [int(t) for t in rng.integers(0, engine.spec.vocab_size, size=count)]
+            engine.step([StepEntry(slot, tokens, start, [])])
+        slots.append(slot)
+    engine.synchronize()
+    return slots
+
+
+def other_workload(name, steps, warmup) -> int:
+    import numpy as np
+    import torch
+    from lia_rs_b200 import LlamaConfig
+    from lia_rs_b200.engine import Engine, StepEntry
+    from lia_rs_b200.engine.scheduler import Scheduler
+    peak = peaks()
+    if name in ("8b-decode", "8b-prefill"):
+        cfg, batch, prompt = CONFIG_8B, 64, 8192
+        layers = cfg["num_hidden_layers"]
+        if name == "8b-decode":
+            pool = batch * (prompt + 256)
+            engine = Engine.random(LlamaConfig.from_dict(cfg), seed=5, dtype="bfloat16", page_size=PAGE, max_tokens=pool,
+                                   max_seqs=batch, max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
+            slots = fill_in_portions(engine, batch, prompt, PROMPT, 7)
+            ms, launches = time_decode(engine, slots, prompt, steps, warmup)
+            weight_bytes, cache_bytes_per_token = model_bytes(cfg, layers)       # (untied: of the table only a few rows are read)
+            step_bytes = weight_bytes + batch * (prompt + warmup + steps // 2) * cache_bytes_per_token
+            achieved = step_bytes / (ms * 1e-3) / 1e9
+            print(json.dumps({"workload": name, "metric": "decode tokens/s (8B-class, batch 64, 8,192-token prompts, bf16)",
+                              "value": round(batch * 1000.0 / ms, 1), "ms_per_step": round(ms, 3), "steps": steps,
+                              "gpu_launches": int(launches),
+                              "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm"], "unit": "GB/s",
+                                           "frac": round(achieved / peak["hbm"], 4)}}))
+            return 0
+        context = cfg["max_position_embeddings"]
+        engine = Engine.random(LlamaConfig.from_dict(cfg), seed=5, dtype="bfloat16", page_size=PAGE, max_tokens=context,
+                               max_seqs=1, max_batch_tokens=PROMPT, max_context=context)
+        rng = np.random.default_rng(3)
+        times = []
+        for repeat in range(2):
+            slot = engine.admit()
+            assert engine.reserve(slot, 0, context)
+            times = []
+            for start in range(0, context, PROMPT):
+                tokens = [int(t) for t in rng.integers(0, cfg["vocab_size"], size=PROMPT)]
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                begin.record()
+                engine.step([StepEntry(slot, tokens, start, [PROMPT - 1] if start + PROMPT == context else [])])
+                end.record()
+                torch.cuda.synchronize()
+                times.append(begin.elapsed_time(end))
+            engine.synchronize()
+            engine.release(slot)
+        linear = prefill_flops(cfg, layers, PROMPT) - layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * PROMPT * (PROMPT + 1) / 2
+        print(json.dumps({"workload": name, "metric": "prefill in 2,048-token portions up to 32,768 tokens (8B-class, bf16)",
+                          "value": round(context * 1000.0 / sum(times), 1), "unit": "tokens/s",
+                          "ms_first_portion": round(times[0], 2), "ms_last_portion": round(times[-1], 2),
+                          "frac_first_portion": round(prefill_flops(cfg, layers, PROMPT) / (times[0] * 1e-3) / (peak["tflops"] * 1e12), 4),
+                          "linear_tflop_per_portion": round(linear / 1e12, 2)}))
+        return 0
+    if name == "0.5b-mixed":
+        cfg, requests, decode_tokens = CONFIG_05B, 64, 256
+        rng = np.random.default_rng(4)
+        prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], size=int(rng.integers(16, 4097)))] for _ in range(requests)]
+        pool = 160 * 1024
+        engine = Engine.random(LlamaConfig.from_dict(cfg), seed=4, dtype="bfloat16", page_size=PAGE, max_tokens=pool,
+                               max_seqs=requests, max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
+        result = {}
+        for repeat in range(2):                      # the first pass compiles nothing but allocates and captures
+            scheduler = Scheduler(engine, max_batch_tokens=PROMPT)
+            for i, prompt in enumerate(prompts):
+                scheduler.add(i, prompt, max_tokens=decode_tokens)
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            scheduler.run()
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - started
+            generated = sum(len(r.generated) for r in scheduler.finished)
+            result = {"workload": name,
+                      "metric": "generated tokens/s through the scheduler (0.5B-class, 64 requests, prompts U[16, 4096], 256 tokens each, bf16)",
+                      "value": round(generated / seconds, 1), "unit": "tokens/s", "seconds": round(seconds, 3),
+                      "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated,
+                      "steps": scheduler.stats["steps"], "pipelined_steps": scheduler.stats["pipelined_steps"],
+                      "preemptions": scheduler.stats["preemptions"], "kv_pool_tokens": pool}
+        print(json.dumps(result))
+        return 0
+    print(f"bench.py: unknown workload {name!r}")
+    return 2
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -216,6 +322,8 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
+    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed"],
+                        help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode steps kernel by kernel instead of replaying CUDA graphs (for profilers)")
     args = parser.parse_args()
@@ -229,6 +337,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload:
+        return other_workload(args.workload, args.steps, args.warmup)
 
     import torch
     from lia_rs_b200 import LlamaConfig

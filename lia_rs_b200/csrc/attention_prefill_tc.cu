@@ -293,8 +293,12 @@ attention_prefill_tc_kernel(Params p) {
                     if (!visible) raw[c] = 0xff800000u;                         // -infinity
                 }
             }
+            {   // four chains: a single one would be 128 instructions that wait for one another
+                float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < KT; ++c) tile_max = fmaxf(tile_max, __uint_as_float(raw[c]));
+                for (int c = 0; c < KT; ++c) part[c & 3] = fmaxf(part[c & 3], __uint_as_float(raw[c]));
+                tile_max = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+            }
             // whole-number reference point: see attention_decode.cu
             const float new_max = fmaxf(row_max, ceilf(tile_max * p.scale_log2));
             const float safe_max = new_max == -INFINITY ? 0.f : new_max;        // a row that has seen no key yet
@@ -302,14 +306,16 @@ attention_prefill_tc_kernel(Params p) {
             row_max = new_max;
             row_sum *= correction;
             // probabilities, as bf16 pairs (the scores' registers are reused)
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};                     // four chains again, met in a fixed order
 #pragma unroll
             for (int c = 0; c < KT; c += 2) {
                 const float e0 = ex2_approx(fmaf(__uint_as_float(raw[c]), p.scale_log2, -safe_max));
                 const float e1 = ex2_approx(fmaf(__uint_as_float(raw[c + 1]), p.scale_log2, -safe_max));
-                row_sum += e0 + e1;
+                sums[(c >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
                 raw[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
+            row_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             // the second product of the tile before must be done: it reads P, and O is about to be rescaled
             if (j > 0 && !mbar_wait(smem_u32(&pv_done), (uint32_t)(j - 1) & 1u)) { ok = false; break; }
             tc_fence_after();

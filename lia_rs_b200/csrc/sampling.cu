@@ -152,6 +152,79 @@ select_part_kernel(const float* __restrict__ logits, int ld, int vocab, const fl
         if (!PICK) tops[r] = pick.value;
     }
 }
+
+// The best `k` logits of every row with their token ids, best first: larger logit, among equal logits the
+// larger id (the order in which the host's sampling rule takes its top_k candidates); minus infinity is no
+// candidate, a row with fewer than k others ends in ids of -1.  `nonfinite` counts NaN and infinities of either
+// sign over all rows (the host refuses such logits).  A row is cut into ranges as above: every CTA keeps its
+// range in shared memory and takes its best k out of it one by one; the last CTA of a row to finish does the
+// same with the ranges' candidates.
+__global__ void __launch_bounds__(PART_THREADS)
+candidates_kernel(const float* __restrict__ logits, int ld, int vocab, int k, float* __restrict__ out_value,
+                  int* __restrict__ out_index, int* __restrict__ nonfinite, int parts, int chunk,
+                  int* __restrict__ counters, float* __restrict__ part_value, int* __restrict__ part_index) {
+    extern __shared__ float held[];                     // the range's logits; later the row's parts * k candidates
+    __shared__ Best scratch[32];
+    __shared__ int last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y, part = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const int begin = part * chunk, count = max(0, min(vocab, begin + chunk) - begin);
+    int odd = 0;
+    for (int i = threadIdx.x; i < count; i += PART_THREADS) {
+        const float x = row[begin + i];
+        odd += !(fabsf(x) <= 3.402823466e38f);          // NaN or an infinity
+        held[i] = x == x ? x : -INFINITY;
+    }
+    if (odd) atomicAdd(nonfinite, odd);
+    __syncthreads();
+    for (int n = 0; n < k; ++n) {
+        Best mine{0.f, -1};
+        for (int i = threadIdx.x; i < count; i += PART_THREADS)
+            if (held[i] != -INFINITY) mine = better<true>(mine, Best{held[i], begin + i});
+        const Best best = block_best<true>(mine, scratch);
+        if (threadIdx.x == 0) {
+            part_value[((size_t)r * parts + part) * k + n] = best.index >= 0 ? best.value : -INFINITY;
+            part_index[((size_t)r * parts + part) * k + n] = best.index;
+            if (best.index >= 0) held[best.index - begin] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int seen = atomicAdd(&counters[r], 1);
+        last = seen == parts - 1;
+        if (last) counters[r] = 0;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const int all = parts * k;                            // at most 64 * 32 candidates: they fit where the range lay (see the launch)
+    int* held_index = reinterpret_cast<int*>(held + all);
+    for (int i = threadIdx.x; i < all; i += PART_THREADS) {
+        held[i] = __ldcg(part_value + (size_t)r * all + i);
+        held_index[i] = __ldcg(part_index + (size_t)r * all + i);
+    }
+    __syncthreads();
+    for (int n = 0; n < k; ++n) {
+        Best mine{0.f, -1};
+        int where = -1;
+        for (int i = threadIdx.x; i < all; i += PART_THREADS) {
+            if (held_index[i] < 0) continue;
+            const Best here{held[i], held_index[i]};
+            const Best top = better<true>(mine, here);
+            if (top.index == here.index) { mine = here; where = i; }
+        }
+        const Best best = block_best<true>(mine, scratch);
+        if (best.index >= 0 && mine.index == best.index && where >= 0) held_index[where] = -1;    // token ids are unique: one thread owns it
+        if (threadIdx.x == 0) {
+            out_value[(size_t)r * k + n] = best.index >= 0 ? best.value : -INFINITY;
+            out_index[(size_t)r * k + n] = best.index;
+        }
+        __syncthreads();
+    }
+}
 }  // namespace
 
 // Floats of scratch that `rows` rows of `vocab` logits need (zero before the first call).  Its first MAX_ROWS words
@@ -182,4 +255,38 @@ LIA_EXPORT int lia_select_tokens(const float* logits, int ld, int vocab, const f
     if (rc != LIA_OK || !temperature) return rc;
     return lia_launch(select_part_kernel<true>, dim3(parts, rows), dim3(PART_THREADS), 0, stream, logits, ld, vocab,
                       temperature, seeds, positions, out, parts, chunk, counters, tops, part_value, part_index);
+}
+
+// Most candidates a row can be asked for.
+LIA_EXPORT int lia_select_candidates_max() { return 32; }
+
+// Floats of scratch for lia_select_candidates (zero before the first call; the counters at its head stay zero).
+LIA_EXPORT long long lia_select_candidates_scratch_floats(int rows, int vocab, int k) {
+    return (long long)MAX_ROWS + 2LL * rows * select_parts(vocab) * k;
+}
+
+// logits [rows, ld >= vocab] 32-bit; out_value, out_index [rows, k], 1 <= k <= 32; nonfinite: one int32 that the
+// kernel adds to.
+LIA_EXPORT int lia_select_candidates(const float* logits, int ld, int vocab, int rows, int k, float* out_value,
+                                     int* out_index, int* nonfinite, float* scratch, long long scratch_floats,
+                                     cudaStream_t stream) {
+    if (rows <= 0) return LIA_OK;
+    if (vocab <= 0 || ld < vocab || rows > MAX_ROWS || k < 1 || k > 32 || !nonfinite) return LIA_ERR_SIZE;
+    if (!scratch || scratch_floats < lia_select_candidates_scratch_floats(rows, vocab, k)) return LIA_ERR_SIZE;
+    const int parts = select_parts(vocab);
+    const int chunk = (vocab + parts - 1) / parts;
+    const size_t range = (size_t)chunk * sizeof(float), merged = (size_t)parts * k * 2 * sizeof(float);
+    const size_t smem = range > merged ? range : merged;
+    if (smem > 200 * 1024) return LIA_ERR_SIZE;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return LIA_ERR_LAUNCH;
+        configured = smem;
+    }
+    int* counters = reinterpret_cast<int*>(scratch);
+    float* part_value = scratch + MAX_ROWS;
+    int* part_index = reinterpret_cast<int*>(part_value + (size_t)rows * parts * k);
+    return lia_launch(candidates_kernel, dim3(parts, rows), dim3(PART_THREADS), smem, stream, logits, ld, vocab, k, out_value,
+                      out_index, nonfinite, parts, chunk, counters, part_value, part_index);
 }

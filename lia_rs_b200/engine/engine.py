@@ -202,6 +202,22 @@ class Engine:
         event.record()
         return PendingTokens(self, out, host[:rows], event)
 
+    def select_candidates(self, logits: torch.Tensor, k: int):
+        """The best `k` logits of every row and their token ids on the host (float32 [rows, k], int32 [rows, k],
+        best first, ids of -1 where a row has fewer): all that a sampling rule which keeps at most k tokens needs
+        of a row, instead of the row.  Raises if a logit is not finite, as the host's rule would."""
+        rows = logits.shape[0]
+        values = self._workspace("select.candidate_values", (max(rows, self.max_seqs), k), torch.float32)[:rows]
+        ids = self._workspace("select.candidate_ids", (max(rows, self.max_seqs), k), torch.int32)[:rows]
+        odd = self._workspace("select.nonfinite", (1, 1), torch.int32)
+        odd.zero_()
+        ops.select_candidates(logits, k, values, ids, odd[0])
+        host_values, host_ids, count = values.cpu().numpy(), ids.cpu().numpy(), int(odd.item())
+        self._raise_device_errors()
+        if count:
+            raise ValueError("nonfinite output logits")
+        return host_values, host_ids
+
     def logits_to_host(self, logits: torch.Tensor):
         rows = logits.float().cpu().numpy()
         self._raise_device_errors()

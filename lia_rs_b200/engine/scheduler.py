@@ -84,7 +84,7 @@ class Scheduler:
         self.active = [None] * self.cache.max_slots      # by slot
         self.finished = []
         self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0, "admitted": 0,
-                      "pipelined_steps": 0}
+                      "pipelined_steps": 0, "candidate_steps": 0}
         self.pipeline = bool(pipeline) and hasattr(engine, "select_tokens_start")
         self._pending = None                             # (tokens on their way to the host, the requests they belong to)
 
@@ -328,6 +328,15 @@ class Scheduler:
             for request, token in zip(requests, tokens):
                 request.sampler.accept(int(token))
             return tokens
+        # rules that keep at most top_k tokens (and greedy ones) need only the row's best candidates, which the
+        # device extracts: a few hundred bytes to the host instead of the rows (the reference's top-20 extraction,
+        # src/gpu/kernels/llama_nucleus.rs:17-124)
+        if hasattr(self.engine, "select_candidates") and all(
+                r.sampling.presence_penalty == 0.0 and (r.sampling.greedy or r.sampling.top_k >= 1) for r in requests):
+            k = max([r.sampling.top_k for r in requests if not r.sampling.greedy] + [1])
+            values, ids = self.engine.select_candidates(logits, k)
+            self.stats["candidate_steps"] += 1
+            return [r.sampler.sample_candidates(ids[i], values[i], positions[i]) for i, r in enumerate(requests)]
         rows = self.engine.logits_to_host(logits)
         return [r.sampler.sample(rows[i], positions[i]) for i, r in enumerate(requests)]
 

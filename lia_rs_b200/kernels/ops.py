@@ -73,6 +73,9 @@ class _Signatures:
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p]
     lia_select_tokens_scratch_floats = [c_int, c_int]
+    lia_select_candidates = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                             ctypes.c_longlong, c_void_p]
+    lia_select_candidates_scratch_floats = [c_int, c_int, c_int]
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -371,6 +374,30 @@ def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
         scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
     _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
                                    _p(positions), _p(out), rows, _p(scratch), scratch.numel(), _stream()), "select_tokens")
+
+
+CANDIDATES_MAX = 32
+
+
+def select_candidates(logits, k: int, out_values, out_ids, nonfinite):
+    """The best k logits of every row and their token ids, best first (larger logit, then larger id; minus
+    infinity is no candidate, missing ones have id -1): what the host's sampling rule needs of a row when it
+    keeps at most k tokens.  `nonfinite` (int32[1]) is increased by the number of NaN and infinite logits."""
+    _cuda(logits, out_values, out_ids, nonfinite)
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or out_values.dtype != torch.float32 or out_ids.dtype != torch.int32:
+        raise KernelError("select_candidates takes 32-bit logits and writes float32 values and int32 ids")
+    if tuple(out_values.shape) != (rows, k) or tuple(out_ids.shape) != (rows, k) or nonfinite.dtype != torch.int32:
+        raise KernelError("select_candidates: outputs must be [rows, k]")
+    key = torch.device(logits.device).index or 0
+    fn = lib().lia_select_candidates_scratch_floats
+    fn.restype = ctypes.c_longlong
+    need = int(fn(rows, vocab, k))
+    scratch = _select_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
+    _check(lib().lia_select_candidates(_p(logits), logits.stride(0), vocab, rows, k, _p(out_values), _p(out_ids),
+                                       _p(nonfinite), _p(scratch), scratch.numel(), _stream()), "select_candidates")
 
 
 def decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits) -> bool:

@@ -189,6 +189,29 @@ def distribution(logits: np.ndarray, temperature: float, top_k: int, top_p: floa
     return list(zip((int(i) for i in ids[:keep]), (float(w) for w in weights)))
 
 
+def distribution_of_candidates(ids, values, temperature: float, top_k: int, top_p: float) -> list:
+    """`distribution` for a row of which only the best candidates are known: `ids` and `values` hold at least
+    top_k of them (or all that are not minus infinity), best first in the order `distribution` sorts by (larger
+    logit, then larger id; an id of -1 ends the list).  The same arithmetic on the same numbers."""
+    ids = np.asarray(ids)
+    values = np.asarray(values, dtype=np.float32)
+    present = int((ids >= 0).sum())
+    if present == 0:
+        raise ValueError("empty sampling distribution")
+    if not 1 <= top_k <= ids.size:
+        raise ValueError("the candidates cover a rule that keeps at most as many tokens as there are candidates")
+    keep_k = min(top_k, present)
+    ids, values = ids[:keep_k], values[:keep_k].astype(np.float64)
+    weights = np.exp((values - values[0]) / temperature)
+    total = float(weights.sum())
+    mass = np.cumsum(weights)
+    reach = np.nonzero(mass >= top_p * total)[0]
+    keep = int(reach[0]) + 1 if reach.size else ids.size
+    weights = weights[:keep]
+    weights = weights / float(weights.sum())
+    return list(zip((int(i) for i in ids[:keep]), (float(w) for w in weights)))
+
+
 class RequestSampler:
     """The sampling state of one request."""
 
@@ -204,6 +227,20 @@ class RequestSampler:
         out[sorted(self.generated)] -= np.float32(self.params.presence_penalty)
         return out
 
+    def sample_candidates(self, ids, values, position: int) -> int:
+        """`sample` for a row of which the device extracted the best candidates (see
+        `distribution_of_candidates`): for rules without a presence penalty that are greedy or keep at most
+        len(ids) tokens.  The same token as `sample` on the whole row."""
+        p = self.params
+        if p.presence_penalty != 0.0:
+            raise ValueError("a presence penalty needs the whole row")
+        if p.greedy:
+            token = int(ids[0])
+        else:
+            token = self._draw(distribution_of_candidates(ids, values, p.temperature, p.top_k, p.top_p), position)
+        self.accept(token)
+        return token
+
     def sample(self, logits: np.ndarray, position: int) -> int:
         """Choose from one row of 32-bit logits on the host.  `position` is that of the token
         whose logits these are (it keys the Gumbel noise: src/server/paged/request.rs:114)."""
@@ -216,21 +253,25 @@ class RequestSampler:
             best = logits.max()
             token = int(np.nonzero(logits == best)[0].max())
         else:
-            entries = distribution(logits, p.temperature, p.top_k, p.top_p)
-            if p.sampler == "murmur3_gumbel":
-                scored = [(np.float32(math.log(prob)) + np.float32(gumbel_noise(murmur_hash(p.seed, position, tok))),
-                           -tok, tok) for tok, prob in entries]
-                token = max(scored)[2]
-            elif len(entries) == 1:
-                token = entries[0][0]
-            else:
-                sample, cumulative, token = self.random.uniform(), 0.0, entries[-1][0]
-                for tok, prob in entries:
-                    cumulative += prob
-                    if sample < cumulative:
-                        token = tok
-                        break
+            token = self._draw(distribution(logits, p.temperature, p.top_k, p.top_p), position)
         self.accept(token)
+        return token
+
+    def _draw(self, entries: list, position: int) -> int:
+        """One token from sorted [(token, probability)]."""
+        p = self.params
+        if p.sampler == "murmur3_gumbel":
+            scored = [(np.float32(math.log(prob)) + np.float32(gumbel_noise(murmur_hash(p.seed, position, tok))),
+                       -tok, tok) for tok, prob in entries]
+            return max(scored)[2]
+        if len(entries) == 1:
+            return entries[0][0]
+        sample, cumulative, token = self.random.uniform(), 0.0, entries[-1][0]
+        for tok, prob in entries:
+            cumulative += prob
+            if sample < cumulative:
+                token = tok
+                break
         return token
 
     def accept(self, token: int) -> None:

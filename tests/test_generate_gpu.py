@@ -59,6 +59,15 @@ def test_temperature_sampling_is_seeded_and_independent_of_batching(tiny_models)
             entries = plain_impl.distribution(row.float().tolist(), 0.8, 0, 1.0)
             assert plain_impl.draw(entries, rng) == token
             sequence.append(token)
+    # with top_k the device hands over only the best candidates of a row: the same draws as from the whole row
+    kept = g.generate(prompts, max_tokens=12, temperature=1.3, top_k=5, top_p=0.9, seed=6)
+    assert g.last_scheduler.stats["candidate_steps"] > 0
+    for prompt, tokens in zip(prompts, kept):
+        rng, sequence = plain_impl.MT19937(6), list(prompt)
+        for token in tokens:
+            row = helpers.plain_logits(model, sequence, "float32")[-1]
+            assert plain_impl.draw(plain_impl.distribution(row.float().tolist(), 1.3, 5, 0.9), rng) == token
+            sequence.append(token)
     # position-keyed Gumbel noise on the device: the same draws alone, together, and in small portions
     together = g.generate(prompts, max_tokens=12, temperature=0.8, seed=5, sampler="murmur3_gumbel")
     alone = [g.generate([p], max_tokens=12, temperature=0.8, seed=5, sampler="murmur3_gumbel")[0] for p in prompts]

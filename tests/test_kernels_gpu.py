@@ -219,6 +219,36 @@ def test_select_tokens_greedy_ties_and_gumbel_matches_the_host_rule():
     assert torch.allclose(freq.cpu(), torch.tensor([1 / 8, 2 / 8, 5 / 8], dtype=torch.float64), atol=0.03)
 
 
+@pytest.mark.parametrize("rows,vocab,k", [(1, 300, 1), (3, 300, 20), (8, 73448, 20), (5, 5000, 32), (9, 2049, 7), (2, 40, 32)])
+def test_select_candidates_are_the_best_of_every_row_in_the_sampling_rules_order(rows, vocab, k):
+    """The best k logits of a row, larger logit first and among equal ones the larger id; minus infinity is no
+    candidate; NaN and infinities are counted."""
+    import numpy as np
+    torch.manual_seed(rows + vocab + k)
+    logits = torch.randn(rows, vocab, device=DEV)
+    logits[:, ::7] = logits[:, 3:4]                       # many equal values, across the ranges a row is cut into
+    logits[0, : vocab // 2] = float("-inf")
+    if rows > 1:
+        logits[1, 5:] = float("-inf")                     # fewer candidates than asked for
+    values = torch.empty(rows, k, device=DEV)
+    ids = torch.empty(rows, k, dtype=torch.int32, device=DEV)
+    odd = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().select_candidates(logits, k, values, ids, odd)
+    host = logits.cpu().numpy()
+    for r in range(rows):
+        finite = np.nonzero(~np.isneginf(host[r]))[0]
+        order = np.lexsort((-finite, -host[r][finite].astype(np.float64)))
+        want = finite[order][:k]
+        got = ids[r].cpu().numpy()
+        assert list(got[:want.size]) == list(want), r
+        assert (got[want.size:] == -1).all()
+        assert np.array_equal(values[r].cpu().numpy()[:want.size], host[r][want])
+    assert odd.item() == int(np.isinf(host).sum())
+    logits[rows - 1, 2] = float("nan")
+    ops().select_candidates(logits, k, values, ids, odd)                     # the counter adds up over calls
+    assert odd.item() == int(np.isinf(host).sum()) + int((~np.isfinite(logits.cpu().numpy())).sum())
+
+
 @pytest.mark.parametrize("M", [1, 8, 40, 64, 100, 300, 1000])
 @pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (15000, 520)])
 def test_gemm_tc_all_epilogues_against_64_bit(M, N, K):

@@ -88,3 +88,41 @@ def test_request_fields_defaults_and_refusals():
     with pytest.raises(ValueError, match="LIA_SAMPLER"):
         Sampling.from_request({}, environ={"LIA_SAMPLER": "xorshift"})
     assert Sampling(temperature=0.9, sampler="murmur3_gumbel").on_device and not Sampling(temperature=0.9).on_device
+
+
+def host_candidates(logits, k):
+    """The best k entries of a row in the order the sampling rule sorts by: larger logit, then larger id."""
+    logits = np.asarray(logits, dtype=np.float32)
+    ids = np.nonzero(~np.isneginf(logits))[0]
+    order = np.lexsort((-ids, -logits[ids].astype(np.float64)))
+    ids = ids[order][:k]
+    out_ids = np.full(k, -1, dtype=np.int32)
+    out_values = np.full(k, -np.inf, dtype=np.float32)
+    out_ids[:ids.size] = ids
+    out_values[:ids.size] = logits[ids]
+    return out_ids, out_values
+
+
+@pytest.mark.parametrize("sampler", ["mt19937", "murmur3_gumbel"])
+@pytest.mark.parametrize("top_k,top_p,temperature", [(1, 1.0, 0.7), (5, 0.9, 1.3), (20, 0.95, 0.6), (20, 1.0, 2.0), (3, 0.2, 1.0)])
+def test_sampling_from_the_best_candidates_equals_sampling_from_the_row(sampler, top_k, top_p, temperature):
+    """A rule that keeps at most top_k tokens needs only the row's best top_k (or more) logits: the same draws,
+    token by token, with ties between equal logits and with more candidates than the rule keeps."""
+    from lia_rs_b200.sampling import RequestSampler, Sampling
+    rng = np.random.default_rng(top_k * 7 + int(top_p * 10))
+    params = Sampling(temperature=temperature, top_k=top_k, top_p=top_p, seed=11, sampler=sampler)
+    whole, few = RequestSampler(params), RequestSampler(params)
+    for position in range(40):
+        logits = rng.normal(size=300).astype(np.float32)
+        logits[rng.integers(0, 300, size=6)] = logits.max()              # ties at the top
+        ids, values = host_candidates(logits, max(top_k, int(rng.integers(top_k, 33))))
+        assert few.sample_candidates(ids, values, position) == whole.sample(logits, position)
+    greedy_whole, greedy_few = RequestSampler(Sampling()), RequestSampler(Sampling())
+    logits = rng.normal(size=50).astype(np.float32)
+    logits[[7, 31]] = logits.max() + 1.0
+    ids, values = host_candidates(logits, 4)
+    assert greedy_few.sample_candidates(ids, values, 0) == greedy_whole.sample(logits, 0) == 31
+    with pytest.raises(ValueError):
+        RequestSampler(Sampling(temperature=1.0, top_k=5, presence_penalty=0.5)).sample_candidates(ids, values, 0)
+    with pytest.raises(ValueError):
+        RequestSampler(Sampling(temperature=1.0, top_k=20)).sample_candidates(ids, values, 0)      # 4 candidates do not cover 20

@@ -166,31 +166,57 @@ def gumbel_noise(word: int) -> float:
     return float(-np.log(negative_log, dtype=np.float32))
 
 
-def distribution(logits: np.ndarray, temperature: float, top_k: int, top_p: float) -> list:
-    """Sorted [(token, probability)] as described in the module's header."""
+def _best_first(logits: np.ndarray, ids: np.ndarray, at_least: int) -> np.ndarray:
+    """A prefix of `ids` in the rule's order (larger logit first, among equal ones the larger id) that holds at
+    least the `at_least` best: everything not below the at_least-th largest logit, so no tie is cut."""
+    values = logits[ids]
+    if at_least < ids.size:
+        bound = np.partition(values, ids.size - at_least)[ids.size - at_least]
+        chosen = values >= bound
+        ids, values = ids[chosen], values[chosen]
+    return ids[np.lexsort((-ids, -values.astype(np.float64)))]
+
+
+def distribution_arrays(logits: np.ndarray, temperature: float, top_k: int, top_p: float):
+    """(tokens, probabilities) of the kept entries, best first, as described in the module's header.  Only as
+    much of the row is sorted as the kept prefix needs: without top_k the total mass is summed over the row as it
+    lies, and the best 256, 4,096, ... entries are sorted until their running mass reaches top_p of it."""
     logits = np.asarray(logits, dtype=np.float32)
     if np.isnan(logits).any() or np.isposinf(logits).any():
         raise ValueError("invalid sampling logits")
     ids = np.nonzero(~np.isneginf(logits))[0]
     if ids.size == 0:
         raise ValueError("empty sampling distribution")
-    order = np.lexsort((-ids, -logits[ids].astype(np.float64)))      # descending logit, then larger id
-    ids = ids[order]
-    if top_k and ids.size > top_k:
-        ids = ids[:top_k]
-    values = logits[ids].astype(np.float64)
-    weights = np.exp((values - values[0]) / temperature)
-    total = float(weights.sum())
-    mass = np.cumsum(weights)
-    reach = np.nonzero(mass >= top_p * total)[0]
-    keep = int(reach[0]) + 1 if reach.size else ids.size
+    if top_k:
+        best = _best_first(logits, ids, top_k)[:top_k]
+        weights = np.exp((logits[best].astype(np.float64) - float(logits[best[0]])) / temperature)
+        mass = np.cumsum(weights)
+        reach = np.nonzero(mass >= top_p * float(weights.sum()))[0]
+    else:
+        largest = float(logits[ids].max())
+        total = float(np.exp((logits[ids].astype(np.float64) - largest) / temperature).sum())
+        sorted_so_far = 256 if top_p < 1.0 else ids.size          # the whole mass is reached at the end only
+        while True:
+            best = _best_first(logits, ids, sorted_so_far)
+            weights = np.exp((logits[best].astype(np.float64) - largest) / temperature)
+            mass = np.cumsum(weights)
+            reach = np.nonzero(mass >= top_p * total)[0]
+            if reach.size or best.size == ids.size:
+                break
+            sorted_so_far *= 16
+    keep = int(reach[0]) + 1 if reach.size else best.size
     weights = weights[:keep]
-    weights = weights / float(weights.sum())
-    return list(zip((int(i) for i in ids[:keep]), (float(w) for w in weights)))
+    return best[:keep], weights / float(weights.sum())
 
 
-def distribution_of_candidates(ids, values, temperature: float, top_k: int, top_p: float) -> list:
-    """`distribution` for a row of which only the best candidates are known: `ids` and `values` hold at least
+def distribution(logits: np.ndarray, temperature: float, top_k: int, top_p: float) -> list:
+    """Sorted [(token, probability)] as described in the module's header."""
+    tokens, probabilities = distribution_arrays(logits, temperature, top_k, top_p)
+    return list(zip((int(i) for i in tokens), (float(w) for w in probabilities)))
+
+
+def distribution_of_candidates(ids, values, temperature: float, top_k: int, top_p: float):
+    """`distribution_arrays` for a row of which only the best candidates are known: `ids` and `values` hold at least
     top_k of them (or all that are not minus infinity), best first in the order `distribution` sorts by (larger
     logit, then larger id; an id of -1 ends the list).  The same arithmetic on the same numbers."""
     ids = np.asarray(ids)
@@ -208,8 +234,7 @@ def distribution_of_candidates(ids, values, temperature: float, top_k: int, top_
     reach = np.nonzero(mass >= top_p * total)[0]
     keep = int(reach[0]) + 1 if reach.size else ids.size
     weights = weights[:keep]
-    weights = weights / float(weights.sum())
-    return list(zip((int(i) for i in ids[:keep]), (float(w) for w in weights)))
+    return ids[:keep], weights / float(weights.sum())
 
 
 class RequestSampler:
@@ -253,26 +278,23 @@ class RequestSampler:
             best = logits.max()
             token = int(np.nonzero(logits == best)[0].max())
         else:
-            token = self._draw(distribution(logits, p.temperature, p.top_k, p.top_p), position)
+            token = self._draw(distribution_arrays(logits, p.temperature, p.top_k, p.top_p), position)
         self.accept(token)
         return token
 
-    def _draw(self, entries: list, position: int) -> int:
-        """One token from sorted [(token, probability)]."""
+    def _draw(self, entries, position: int) -> int:
+        """One token from (tokens, probabilities), best first."""
         p = self.params
+        tokens, probabilities = entries
         if p.sampler == "murmur3_gumbel":
-            scored = [(np.float32(math.log(prob)) + np.float32(gumbel_noise(murmur_hash(p.seed, position, tok))),
-                       -tok, tok) for tok, prob in entries]
+            scored = [(np.float32(math.log(prob)) + np.float32(gumbel_noise(murmur_hash(p.seed, position, int(tok)))),
+                       -int(tok), int(tok)) for tok, prob in zip(tokens, probabilities)]
             return max(scored)[2]
-        if len(entries) == 1:
-            return entries[0][0]
-        sample, cumulative, token = self.random.uniform(), 0.0, entries[-1][0]
-        for tok, prob in entries:
-            cumulative += prob
-            if sample < cumulative:
-                token = tok
-                break
-        return token
+        if len(tokens) == 1:
+            return int(tokens[0])
+        # the first entry whose running sum (added up one by one, in order) exceeds the sample; else the last
+        beyond = np.searchsorted(np.cumsum(probabilities), self.random.uniform(), side="right")
+        return int(tokens[min(int(beyond), len(tokens) - 1)])
 
     def accept(self, token: int) -> None:
         self.generated.add(int(token))

@@ -52,6 +52,27 @@ def test_matches_the_plain_sampler_draw_by_draw():
             assert ours.sample(logits, 0) == want
 
 
+@pytest.mark.parametrize("top_p", [0.3, 0.9, 0.999, 1.0])
+@pytest.mark.parametrize("spread", [0.05, 3.0])
+def test_a_row_sorted_only_as_far_as_the_kept_prefix_needs_gives_the_plain_distribution(top_p, spread):
+    """A long row, flat or peaked, with runs of equal logits that straddle where the partial sorts cut."""
+    rng = np.random.default_rng(int(top_p * 1000) + int(spread * 100))
+    logits = (rng.normal(size=6000) * spread).astype(np.float32)
+    order = np.argsort(-logits)
+    logits[order[250:262]] = logits[order[250]]                    # a tie across the 256 best
+    logits[order[4090:4100]] = logits[order[4090]]                 # and across the 4,096 best
+    logits[rng.integers(0, 6000, 50)] = -np.inf
+    want = plain_impl.distribution(logits, 0.9, 0, top_p)
+    got = distribution(logits, 0.9, 0, top_p)
+    assert [t for t, _ in got] == [t for t, _ in want]
+    assert np.allclose([p for _, p in got], [p for _, p in want], rtol=1e-12, atol=0)
+    logits[np.isneginf(logits)] = -40.0                            # a row to sample from holds finite logits only
+    want = plain_impl.distribution(logits, 0.9, 0, top_p)
+    ours, theirs = RequestSampler(Sampling(temperature=0.9, top_p=top_p, seed=5)), plain_impl.MT19937(5)
+    for _ in range(20):
+        assert ours.sample(logits, 0) == plain_impl.draw(want, theirs)
+
+
 def test_greedy_keeps_the_last_maximum_and_presence_penalty():
     s = RequestSampler(Sampling())
     assert s.sample(np.array([1, 5, 5, 2], dtype=np.float32), 0) == 2

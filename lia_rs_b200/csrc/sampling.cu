@@ -88,6 +88,19 @@ __device__ Best block_best(Best mine, Best* scratch) {
     return total;
 }
 
+// The sum of a value over the CTA, in a fixed tree (every thread calls it; every thread gets the sum).
+__device__ double block_sum(double mine, double* warp_sums) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    __syncthreads();
+    if (lane == 0) warp_sums[warp] = mine;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[w];
+    return total;
+}
+
 // A row is cut into `parts` ranges of `chunk` tokens, a CTA each, so that a handful of rows still keeps many SMs
 // busy; the CTA that finishes a row last (a counter that it leaves at zero again) picks among the ranges' bests.
 // `better` is a total order (value, then id), so the pick does not depend on which CTA that is.
@@ -162,9 +175,11 @@ select_part_kernel(const float* __restrict__ logits, int ld, int vocab, const fl
 __global__ void __launch_bounds__(PART_THREADS)
 candidates_kernel(const float* __restrict__ logits, int ld, int vocab, int k, float* __restrict__ out_value,
                   int* __restrict__ out_index, int* __restrict__ nonfinite, int parts, int chunk,
-                  int* __restrict__ counters, float* __restrict__ part_value, int* __restrict__ part_index) {
+                  int* __restrict__ counters, float* __restrict__ part_value, int* __restrict__ part_index,
+                  const double* __restrict__ temperature, double* __restrict__ mass, double* __restrict__ part_mass) {
     extern __shared__ float held[];                     // the range's logits; later the row's parts * k candidates
     __shared__ Best scratch[32];
+    __shared__ double sums[PART_THREADS / 32];
     __shared__ int last;
     pdl_launch_dependents();
     pdl_wait();
@@ -179,6 +194,24 @@ candidates_kernel(const float* __restrict__ logits, int ld, int vocab, int k, fl
     }
     if (odd) atomicAdd(nonfinite, odd);
     __syncthreads();
+    if (mass) {
+        // the range's share of the row's softmax mass at the row's temperature, in 64-bit: its largest logit and
+        // the sum of exp((x - largest) / T) over it, added up in an order that depends on nothing but the sizes
+        Best mine{0.f, -1};
+        for (int i = threadIdx.x; i < count; i += PART_THREADS)
+            if (held[i] != -INFINITY) mine = better<true>(mine, Best{held[i], begin + i});
+        const Best top = block_best<true>(mine, scratch);
+        const double t = temperature[r];
+        double sum = 0.0;
+        if (top.index >= 0 && t > 0.0)
+            for (int i = threadIdx.x; i < count; i += PART_THREADS)
+                if (held[i] != -INFINITY) sum += exp(((double)held[i] - (double)top.value) / t);
+        sum = block_sum(sum, sums);
+        if (threadIdx.x == 0) {
+            part_mass[((size_t)r * parts + part) * 2] = top.index >= 0 ? (double)top.value : -INFINITY;
+            part_mass[((size_t)r * parts + part) * 2 + 1] = sum;
+        }
+    }
     for (int n = 0; n < k; ++n) {
         Best mine{0.f, -1};
         for (int i = threadIdx.x; i < count; i += PART_THREADS)
@@ -200,6 +233,23 @@ candidates_kernel(const float* __restrict__ logits, int ld, int vocab, int k, fl
     __syncthreads();
     if (!last) return;
     __threadfence();
+    if (mass) {
+        // the ranges' shares brought to the row's largest logit: total = sum_p sum_p * exp((largest_p - largest) / T)
+        const double t = temperature[r];
+        double largest = -INFINITY;
+        for (int p = 0; p < parts; ++p) largest = fmax(largest, __ldcg(part_mass + ((size_t)r * parts + p) * 2));
+        double term = 0.0;
+        for (int p = threadIdx.x; p < parts; p += PART_THREADS) {
+            const double share = __ldcg(part_mass + ((size_t)r * parts + p) * 2 + 1);
+            if (share > 0.0 || share != share)
+                term += share * exp((__ldcg(part_mass + ((size_t)r * parts + p) * 2) - largest) / t);
+        }
+        term = block_sum(term, sums);
+        if (threadIdx.x == 0) {
+            mass[(size_t)r * 2] = largest;
+            mass[(size_t)r * 2 + 1] = term;
+        }
+    }
     const int all = parts * k;                            // at most 64 * 32 candidates: they fit where the range lay (see the launch)
     int* held_index = reinterpret_cast<int*>(held + all);
     for (int i = threadIdx.x; i < all; i += PART_THREADS) {
@@ -262,16 +312,19 @@ LIA_EXPORT int lia_select_candidates_max() { return 32; }
 
 // Floats of scratch for lia_select_candidates (zero before the first call; the counters at its head stay zero).
 LIA_EXPORT long long lia_select_candidates_scratch_floats(int rows, int vocab, int k) {
-    return (long long)MAX_ROWS + 2LL * rows * select_parts(vocab) * k;
+    return (long long)MAX_ROWS + 1 + 2LL * rows * select_parts(vocab) * k + 4LL * rows * select_parts(vocab);
 }
 
 // logits [rows, ld >= vocab] 32-bit; out_value, out_index [rows, k], 1 <= k <= 32; nonfinite: one int32 that the
-// kernel adds to.
+// kernel adds to.  With `temperature` [rows] and `mass` [rows, 2] (64-bit, both or neither): mass[r] = (the row's
+// largest logit, the sum over the row of exp((x - largest) / temperature[r])), 0 where the temperature is 0.
 LIA_EXPORT int lia_select_candidates(const float* logits, int ld, int vocab, int rows, int k, float* out_value,
-                                     int* out_index, int* nonfinite, float* scratch, long long scratch_floats,
-                                     cudaStream_t stream) {
+                                     int* out_index, int* nonfinite, const double* temperature, double* mass,
+                                     float* scratch, long long scratch_floats, cudaStream_t stream) {
     if (rows <= 0) return LIA_OK;
     if (vocab <= 0 || ld < vocab || rows > MAX_ROWS || k < 1 || k > 32 || !nonfinite) return LIA_ERR_SIZE;
+    if ((temperature == nullptr) != (mass == nullptr)) return LIA_ERR_SIZE;
+    if (reinterpret_cast<uintptr_t>(scratch) % 8) return LIA_ERR_SIZE;
     if (!scratch || scratch_floats < lia_select_candidates_scratch_floats(rows, vocab, k)) return LIA_ERR_SIZE;
     const int parts = select_parts(vocab);
     const int chunk = (vocab + parts - 1) / parts;
@@ -287,6 +340,8 @@ LIA_EXPORT int lia_select_candidates(const float* logits, int ld, int vocab, int
     int* counters = reinterpret_cast<int*>(scratch);
     float* part_value = scratch + MAX_ROWS;
     int* part_index = reinterpret_cast<int*>(part_value + (size_t)rows * parts * k);
+    const size_t words = (size_t)MAX_ROWS + 2 * (size_t)rows * parts * k;
+    double* part_mass = reinterpret_cast<double*>(scratch + words + (words & 1));      // on an 8-byte boundary
     return lia_launch(candidates_kernel, dim3(parts, rows), dim3(PART_THREADS), smem, stream, logits, ld, vocab, k, out_value,
-                      out_index, nonfinite, parts, chunk, counters, part_value, part_index);
+                      out_index, nonfinite, parts, chunk, counters, part_value, part_index, temperature, mass, part_mass);
 }

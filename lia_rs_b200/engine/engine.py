@@ -202,21 +202,33 @@ class Engine:
         event.record()
         return PendingTokens(self, out, host[:rows], event)
 
-    def select_candidates(self, logits: torch.Tensor, k: int):
+    def select_candidates(self, logits: torch.Tensor, k: int, temperatures=None):
         """The best `k` logits of every row and their token ids on the host (float32 [rows, k], int32 [rows, k],
         best first, ids of -1 where a row has fewer): all that a sampling rule which keeps at most k tokens needs
-        of a row, instead of the row.  Raises if a logit is not finite, as the host's rule would."""
+        of a row, instead of the row.  With `temperatures` (one a row, 0 where none is needed) a third result,
+        float64 [rows, 2]: each row's largest logit and the 64-bit sum of exp((x - largest) / temperature) over the
+        whole row, by which a rule without top_k can tell whether its kept tokens lie within the candidates.
+        Raises if a logit is not finite, as the host's rule would."""
         rows = logits.shape[0]
-        values = self._workspace("select.candidate_values", (max(rows, self.max_seqs), k), torch.float32)[:rows]
-        ids = self._workspace("select.candidate_ids", (max(rows, self.max_seqs), k), torch.int32)[:rows]
+        most = max(rows, self.max_seqs)
+        values = self._workspace("select.candidate_values", (most, k), torch.float32)[:rows]
+        ids = self._workspace("select.candidate_ids", (most, k), torch.int32)[:rows]
         odd = self._workspace("select.nonfinite", (1, 1), torch.int32)
         odd.zero_()
-        ops.select_candidates(logits, k, values, ids, odd[0])
+        if temperatures is None:
+            ops.select_candidates(logits, k, values, ids, odd[0])
+            host_mass = None
+        else:
+            wanted = self._workspace("select.temperatures", (1, most), torch.float64)[0, :rows]
+            wanted.copy_(torch.tensor([float(t) for t in temperatures], dtype=torch.float64))
+            mass = self._workspace("select.mass", (most, 2), torch.float64)[:rows]
+            ops.select_candidates(logits, k, values, ids, odd[0], wanted, mass)
+            host_mass = mass.cpu().numpy()
         host_values, host_ids, count = values.cpu().numpy(), ids.cpu().numpy(), int(odd.item())
         self._raise_device_errors()
         if count:
             raise ValueError("nonfinite output logits")
-        return host_values, host_ids
+        return (host_values, host_ids) if temperatures is None else (host_values, host_ids, host_mass)
 
     def logits_to_host(self, logits: torch.Tensor):
         rows = logits.float().cpu().numpy()

@@ -70,6 +70,8 @@ class Request:
 
 
 class Scheduler:
+    NUCLEUS_CANDIDATES = 32                              # candidates asked of the device for a rule without top_k
+
     def __init__(self, engine, max_batch_tokens: int = 512, even_split: bool = False, eos_token_ids=(),
                  context: Optional[int] = None, pipeline: bool = True):
         self.engine = engine
@@ -84,7 +86,7 @@ class Scheduler:
         self.active = [None] * self.cache.max_slots      # by slot
         self.finished = []
         self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0, "admitted": 0,
-                      "pipelined_steps": 0, "candidate_steps": 0}
+                      "pipelined_steps": 0, "candidate_steps": 0, "whole_row_draws": 0}
         self.pipeline = bool(pipeline) and hasattr(engine, "select_tokens_start")
         self._pending = None                             # (tokens on their way to the host, the requests they belong to)
 
@@ -329,14 +331,29 @@ class Scheduler:
                 request.sampler.accept(int(token))
             return tokens
         # rules that keep at most top_k tokens (and greedy ones) need only the row's best candidates, which the
-        # device extracts: a few hundred bytes to the host instead of the rows (the reference's top-20 extraction,
-        # src/gpu/kernels/llama_nucleus.rs:17-124)
+        # device extracts: a few hundred bytes to the host instead of the rows.  A rule without top_k but with
+        # top_p < 1 takes the best candidates too, and the row's whole softmax mass: when its kept tokens lie
+        # within them it draws from them, else from the whole row (the reference's extraction of candidates and
+        # normalisers with its fall-back, src/gpu/kernels/llama_nucleus.rs:17-124, src/sampling/nucleus.rs:48-91)
+        rules = [r.sampling for r in requests]
+        open_ended = [not s.greedy and s.top_k == 0 for s in rules]
         if hasattr(self.engine, "select_candidates") and all(
-                r.sampling.presence_penalty == 0.0 and (r.sampling.greedy or r.sampling.top_k >= 1) for r in requests):
-            k = max([r.sampling.top_k for r in requests if not r.sampling.greedy] + [1])
-            values, ids = self.engine.select_candidates(logits, k)
+                s.presence_penalty == 0.0 and (s.greedy or s.top_k >= 1 or s.top_p < 1.0) for s in rules):
+            k = max([s.top_k for s in rules if not s.greedy] + [self.NUCLEUS_CANDIDATES if any(open_ended) else 1])
             self.stats["candidate_steps"] += 1
-            return [r.sampler.sample_candidates(ids[i], values[i], positions[i]) for i, r in enumerate(requests)]
+            if any(open_ended):
+                values, ids, mass = self.engine.select_candidates(
+                    logits, k, [s.temperature if o else 0.0 for s, o in zip(rules, open_ended)])
+            else:
+                (values, ids), mass = self.engine.select_candidates(logits, k), [None] * len(requests)
+            tokens = [r.sampler.sample_candidates(ids[i], values[i], positions[i], mass[i]) for i, r in enumerate(requests)]
+            if any(t is None for t in tokens):
+                rows = self.engine.logits_to_host(logits)
+                for i, r in enumerate(requests):
+                    if tokens[i] is None:
+                        self.stats["whole_row_draws"] += 1
+                        tokens[i] = r.sampler.sample(rows[i], positions[i])
+            return tokens
         rows = self.engine.logits_to_host(logits)
         return [r.sampler.sample(rows[i], positions[i]) for i, r in enumerate(requests)]
 

@@ -73,8 +73,8 @@ class _Signatures:
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p]
     lia_select_tokens_scratch_floats = [c_int, c_int]
-    lia_select_candidates = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                             ctypes.c_longlong, c_void_p]
+    lia_select_candidates = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, ctypes.c_longlong, c_void_p]
     lia_select_candidates_scratch_floats = [c_int, c_int, c_int]
 
 
@@ -379,12 +379,21 @@ def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
 CANDIDATES_MAX = 32
 
 
-def select_candidates(logits, k: int, out_values, out_ids, nonfinite):
+def select_candidates(logits, k: int, out_values, out_ids, nonfinite, temperature=None, mass=None):
     """The best k logits of every row and their token ids, best first (larger logit, then larger id; minus
     infinity is no candidate, missing ones have id -1): what the host's sampling rule needs of a row when it
-    keeps at most k tokens.  `nonfinite` (int32[1]) is increased by the number of NaN and infinite logits."""
+    keeps at most k tokens.  `nonfinite` (int32[1]) is increased by the number of NaN and infinite logits.
+    With `temperature` (float64 [rows]) also `mass` (float64 [rows, 2]): the row's largest logit and the sum of
+    exp((x - largest) / temperature) over the whole row in 64-bit, which bounds what the candidates leave out."""
     _cuda(logits, out_values, out_ids, nonfinite)
     rows, vocab = logits.shape
+    if (temperature is None) != (mass is None):
+        raise KernelError("select_candidates: temperature and mass come together")
+    if temperature is not None:
+        _cuda(temperature, mass)
+        if temperature.dtype != torch.float64 or mass.dtype != torch.float64 or temperature.numel() != rows \
+                or tuple(mass.shape) != (rows, 2) or not mass.is_contiguous() or not temperature.is_contiguous():
+            raise KernelError("select_candidates: temperature is float64 [rows], mass float64 [rows, 2]")
     if logits.dtype != torch.float32 or out_values.dtype != torch.float32 or out_ids.dtype != torch.int32:
         raise KernelError("select_candidates takes 32-bit logits and writes float32 values and int32 ids")
     if tuple(out_values.shape) != (rows, k) or tuple(out_ids.shape) != (rows, k) or nonfinite.dtype != torch.int32:
@@ -397,7 +406,8 @@ def select_candidates(logits, k: int, out_values, out_ids, nonfinite):
     if scratch is None or scratch.numel() < need:
         scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
     _check(lib().lia_select_candidates(_p(logits), logits.stride(0), vocab, rows, k, _p(out_values), _p(out_ids),
-                                       _p(nonfinite), _p(scratch), scratch.numel(), _stream()), "select_candidates")
+                                       _p(nonfinite), _p(temperature), _p(mass), _p(scratch), scratch.numel(),
+                                       _stream()), "select_candidates")
 
 
 def decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits) -> bool:

@@ -203,7 +203,11 @@ def distribution_arrays(logits: np.ndarray, temperature: float, top_k: int, top_
             reach = np.nonzero(mass >= top_p * total)[0]
             if reach.size or best.size == ids.size:
                 break
-            sorted_so_far *= 16
+            # sixteen times as many next time; all of them when that is most of the row, or when the best so far
+            # hold so little of the mass that the kept prefix must be long
+            sorted_so_far = sorted_so_far * 16 if float(mass[-1]) * 4 >= top_p * total else ids.size
+            if sorted_so_far * 4 >= ids.size:
+                sorted_so_far = ids.size
     keep = int(reach[0]) + 1 if reach.size else best.size
     weights = weights[:keep]
     return best[:keep], weights / float(weights.sum())
@@ -237,6 +241,39 @@ def distribution_of_candidates(ids, values, temperature: float, top_k: int, top_
     return ids[:keep], weights / float(weights.sum())
 
 
+def nucleus_of_candidates(ids, values, largest: float, total: float, temperature: float, top_p: float):
+    """`distribution_arrays` of a rule WITHOUT top_k for a row of which the best candidates are known (as in
+    `distribution_of_candidates`) together with the row's largest logit and its whole mass
+    total = sum_x exp((x - largest) / temperature), which the device summed in 64-bit (the reference extracts
+    candidates and normalisers in the same way: src/gpu/kernels/llama_nucleus.rs:17-124).  Returns None when the
+    candidates do not settle it and the whole row is needed: top_p = 1; a kept prefix that is longer than the
+    candidates; or a cut so close to top_p * total (within 1e-10 of the total, the margin of
+    src/sampling/nucleus.rs:82-88) that another order of summation could place it elsewhere.  Otherwise the same
+    tokens and, number for number, the same probabilities as from the whole row."""
+    ids = np.asarray(ids)
+    values = np.asarray(values, dtype=np.float32)
+    present = int((ids >= 0).sum())
+    if present == 0:
+        raise ValueError("empty sampling distribution")
+    if not (math.isfinite(total) and total > 0.0 and math.isfinite(largest)) or float(values[0]) != largest:
+        raise ValueError("invalid softmax mass of a row")
+    if top_p >= 1.0:
+        return None
+    weights = np.exp((values[:present].astype(np.float64) - largest) / temperature)
+    mass = np.cumsum(weights)
+    target = top_p * total
+    reach = np.nonzero(mass >= target)[0]
+    if not reach.size:
+        return None
+    keep = int(reach[0]) + 1
+    margin = abs(total) * 1e-10
+    before = float(mass[keep - 2]) if keep > 1 else 0.0
+    if before >= target - margin or float(mass[keep - 1]) <= target + margin:
+        return None
+    weights = weights[:keep]
+    return ids[:keep], weights / float(weights.sum())
+
+
 class RequestSampler:
     """The sampling state of one request."""
 
@@ -252,17 +289,26 @@ class RequestSampler:
         out[sorted(self.generated)] -= np.float32(self.params.presence_penalty)
         return out
 
-    def sample_candidates(self, ids, values, position: int) -> int:
+    def sample_candidates(self, ids, values, position: int, mass=None):
         """`sample` for a row of which the device extracted the best candidates (see
-        `distribution_of_candidates`): for rules without a presence penalty that are greedy or keep at most
-        len(ids) tokens.  The same token as `sample` on the whole row."""
+        `distribution_of_candidates`): for rules without a presence penalty that are greedy, keep at most len(ids)
+        tokens, or (with `mass`, the row's largest logit and whole softmax mass) have no top_k but a top_p below 1.
+        The same token as `sample` on the whole row, or None if the candidates do not settle it (no random number
+        is drawn then): the caller samples from the whole row."""
         p = self.params
         if p.presence_penalty != 0.0:
             raise ValueError("a presence penalty needs the whole row")
         if p.greedy:
             token = int(ids[0])
-        else:
+        elif p.top_k >= 1:
             token = self._draw(distribution_of_candidates(ids, values, p.temperature, p.top_k, p.top_p), position)
+        else:
+            if mass is None:
+                raise ValueError("a rule without top_k needs the row's softmax mass beside the candidates")
+            entries = nucleus_of_candidates(ids, values, float(mass[0]), float(mass[1]), p.temperature, p.top_p)
+            if entries is None:
+                return None
+            token = self._draw(entries, position)
         self.accept(token)
         return token
 

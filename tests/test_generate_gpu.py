@@ -68,6 +68,19 @@ def test_temperature_sampling_is_seeded_and_independent_of_batching(tiny_models)
             row = helpers.plain_logits(model, sequence, "float32")[-1]
             assert plain_impl.draw(plain_impl.distribution(row.float().tolist(), 1.3, 5, 0.9), rng) == token
             sequence.append(token)
+    # without top_k the candidates come with the row's whole softmax mass: cold draws are settled by them, warm ones
+    # fetch the row; both give the draws of the whole row
+    for temperature, seed in ((0.02, 8), (1.0, 9)):
+        kept = g.generate(prompts, max_tokens=12, temperature=temperature, top_p=0.9, seed=seed)
+        stats = g.last_scheduler.stats
+        assert stats["candidate_steps"] > 0
+        assert stats["whole_row_draws"] < 36 if temperature < 1.0 else stats["whole_row_draws"] == 36
+        for prompt, tokens in zip(prompts, kept):
+            rng, sequence = plain_impl.MT19937(seed), list(prompt)
+            for token in tokens:
+                row = helpers.plain_logits(model, sequence, "float32")[-1]
+                assert plain_impl.draw(plain_impl.distribution(row.float().tolist(), temperature, 0, 0.9), rng) == token
+                sequence.append(token)
     # position-keyed Gumbel noise on the device: the same draws alone, together, and in small portions
     together = g.generate(prompts, max_tokens=12, temperature=0.8, seed=5, sampler="murmur3_gumbel")
     alone = [g.generate([p], max_tokens=12, temperature=0.8, seed=5, sampler="murmur3_gumbel")[0] for p in prompts]

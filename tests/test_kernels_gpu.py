@@ -244,6 +244,20 @@ def test_select_candidates_are_the_best_of_every_row_in_the_sampling_rules_order
         assert (got[want.size:] == -1).all()
         assert np.array_equal(values[r].cpu().numpy()[:want.size], host[r][want])
     assert odd.item() == int(np.isinf(host).sum())
+    # with temperatures: also each row's largest logit and its whole softmax mass in 64-bit
+    temperature = torch.tensor([0.0 if r == 2 else 0.3 + 0.45 * r for r in range(rows)], dtype=torch.float64, device=DEV)
+    mass = torch.full((rows, 2), -1.0, dtype=torch.float64, device=DEV)
+    again = torch.empty_like(ids)
+    ops().select_candidates(logits, k, values, again, odd, temperature, mass)
+    assert torch.equal(again, ids)
+    for r in range(rows):
+        finite = host[r][~np.isneginf(host[r])].astype(np.float64)
+        assert mass[r, 0].item() == finite.max()
+        t = temperature[r].item()
+        want = np.exp((finite - finite.max()) / t).sum() if t else 0.0
+        assert abs(mass[r, 1].item() - want) <= 1e-12 * max(want, 1.0), (r, mass[r, 1].item(), want)
+    odd.zero_()
+    ops().select_candidates(logits, k, values, ids, odd)
     logits[rows - 1, 2] = float("nan")
     ops().select_candidates(logits, k, values, ids, odd)                     # the counter adds up over calls
     assert odd.item() == int(np.isinf(host).sum()) + int((~np.isfinite(logits.cpu().numpy())).sum())

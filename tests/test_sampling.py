@@ -147,3 +147,40 @@ def test_sampling_from_the_best_candidates_equals_sampling_from_the_row(sampler,
         RequestSampler(Sampling(temperature=1.0, top_k=5, presence_penalty=0.5)).sample_candidates(ids, values, 0)
     with pytest.raises(ValueError):
         RequestSampler(Sampling(temperature=1.0, top_k=20)).sample_candidates(ids, values, 0)      # 4 candidates do not cover 20
+
+
+def test_a_rule_without_top_k_draws_from_the_candidates_when_they_hold_what_it_keeps():
+    """Candidates plus the row's whole softmax mass (summed elsewhere, in another order) give the draws of the whole
+    row, or None (and use no random number) when they cannot: a kept prefix longer than the candidates, top_p = 1,
+    a cut that lies on top_p * total."""
+    from lia_rs_b200.sampling import RequestSampler, Sampling
+    from lia_rs_b200.sampling.sampler import nucleus_of_candidates
+    rng = np.random.default_rng(3)
+    params = Sampling(temperature=0.7, top_k=0, top_p=0.9, seed=21)
+    whole, few = RequestSampler(params), RequestSampler(params)
+    settled = unsettled = 0
+    for position in range(60):
+        spread = 8.0 if position % 3 else 0.5                       # peaked rows, and flat ones that keep hundreds
+        logits = (rng.normal(size=3000) * spread).astype(np.float32)
+        logits[rng.integers(0, 3000, 5)] = logits.max()             # equal logits at the top
+        ids, values = host_candidates(logits, 32)
+        shifted = (logits.astype(np.float64)[::-1] - float(logits.max())) / 0.7
+        mass = (float(logits.max()), math.fsum(np.exp(shifted).tolist()))
+        token = few.sample_candidates(ids, values, position, mass)
+        if token is None:
+            unsettled += 1
+            token = few.sample(logits, position)
+        else:
+            settled += 1
+        assert token == whole.sample(logits, position)
+    assert settled >= 20 and unsettled >= 10
+    two = np.array([0, 1], dtype=np.int32), np.array([0.0, 0.0], dtype=np.float32)
+    assert nucleus_of_candidates(*two, 0.0, 2.0, 1.0, 0.5) is None                 # the first token's mass IS top_p * total
+    assert [int(t) for t in nucleus_of_candidates(*two, 0.0, 2.0, 1.0, 0.4)[0]] == [0]
+    assert [int(t) for t in nucleus_of_candidates(*two, 0.0, 2.0, 1.0, 0.6)[0]] == [0, 1]
+    assert nucleus_of_candidates(*two, 0.0, 2.0, 1.0, 1.0) is None
+    assert nucleus_of_candidates(*two, 0.0, 40.0, 1.0, 0.5) is None                # most of the mass lies outside
+    with pytest.raises(ValueError):
+        nucleus_of_candidates(*two, 0.0, float("nan"), 1.0, 0.5)
+    with pytest.raises(ValueError):
+        RequestSampler(params).sample_candidates(*two, 0)                          # no mass given

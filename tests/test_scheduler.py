@@ -164,6 +164,38 @@ def test_host_sampling_is_used_when_the_rule_needs_it():
     assert len(r.generated) == 5 and len(g.generated) == 5
 
 
+class CandidateStandIn(StandInEngine):
+    """The stand-in with the engine's extraction of a row's best candidates and softmax mass."""
+
+    def select_candidates(self, logits, k, temperatures=None):
+        rows = logits.numpy()
+        order = np.stack([np.lexsort((-np.arange(VOCAB), -row.astype(np.float64)))[:k] for row in rows])
+        values = np.take_along_axis(rows, order, axis=1)
+        if temperatures is None:
+            return values, order.astype(np.int32)
+        mass = [(float(row.max()), float(np.exp((row.astype(np.float64) - float(row.max())) / t).sum()) if t else 0.0)
+                for row, t in zip(rows, temperatures)]
+        return values, order.astype(np.int32), np.array(mass)
+
+
+def test_rules_without_top_k_draw_from_candidates_or_fall_back_to_the_row_with_the_same_tokens():
+    """Cold requests keep one token (settled by the candidates), warm ones keep most of the vocabulary (the whole
+    row is fetched); beside them a greedy one and one with top_k.  The same tokens as without the extraction."""
+    rules = [Sampling(temperature=0.2, top_p=0.9, seed=1), Sampling(temperature=0.9, top_p=0.9, seed=2), Sampling(),
+             Sampling(temperature=0.9, top_k=7, top_p=0.8, seed=3)]
+    results = []
+    for engine_type in (StandInEngine, CandidateStandIn):
+        engine = engine_type(num_pages=64)
+        s = Scheduler(engine, max_batch_tokens=16)
+        requests = [s.add(i, [3 + i, 5, 8], rule, max_tokens=9) for i, rule in enumerate(rules)]
+        s.run()
+        results.append([list(r.generated) for r in requests])
+        if engine_type is CandidateStandIn:
+            assert s.stats["candidate_steps"] > 0 and s.stats["whole_row_draws"] >= 9
+            assert s.stats["whole_row_draws"] <= 9 * 2          # never for the cold, the greedy or the top_k request
+    assert results[0] == results[1] and all(len(g) == 9 for g in results[0])
+
+
 class PipelinedStandIn(StandInEngine):
     """The stand-in with the engine's non-waiting selection: tokens become readable only through
     `tokens()`, and a fed step takes them where the device would, from the last selection."""

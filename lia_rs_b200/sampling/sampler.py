@@ -64,10 +64,11 @@ class Sampling:
         return self.sampler == "murmur3_gumbel" and self.top_k == 0 and self.top_p == 1.0
 
     @classmethod
-    def from_request(cls, request: dict, environ=None) -> "Sampling":
+    def from_request(cls, request: dict, environ=None, top_k_when_absent: int = 20) -> "Sampling":
         """Build from a request's JSON fields with the reference's names, defaults and refusals
         (src/server/sampling.rs:32-90).  LIA_DEFAULT_TEMPERATURE, LIA_DEFAULT_PRESENCE_PENALTY and
-        LIA_SAMPLER are honoured as there."""
+        LIA_SAMPLER are honoured as there.  A request without top_k gets 20; the paged service of this
+        architecture passes `top_k_when_absent=0`, unrestricted (src/server/paged/request.rs:49-52)."""
         environ = os.environ if environ is None else environ
 
         def number(name, default):
@@ -97,7 +98,7 @@ class Sampling:
         sampler = environ.get("LIA_SAMPLER", "mt19937")
         if sampler not in SAMPLERS:
             raise ValueError(f"invalid LIA_SAMPLER: {sampler}")
-        return cls(temperature=number("temperature", default_temperature), top_k=integer("top_k", 20),
+        return cls(temperature=number("temperature", default_temperature), top_k=integer("top_k", top_k_when_absent),
                    top_p=number("top_p", 0.95), seed=integer("seed", 42),
                    presence_penalty=number("presence_penalty", default_presence), sampler=sampler)
 

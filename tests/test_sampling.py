@@ -101,6 +101,8 @@ def test_request_fields_defaults_and_refusals():
     s = Sampling.from_request({}, environ={})
     assert (s.temperature, s.top_k, s.top_p, s.seed, s.presence_penalty) == (1.0, 20, 0.95, 42, 0.0)
     assert Sampling.from_request({"temperature": 0}, environ={}).greedy
+    assert Sampling.from_request({}, environ={}, top_k_when_absent=0).top_k == 0
+    assert Sampling.from_request({"top_k": 5}, environ={}, top_k_when_absent=0).top_k == 5
     assert Sampling.from_request({}, environ={"LIA_SAMPLER": "murmur3_gumbel"}).sampler == "murmur3_gumbel"
     for bad in ({"frequency_penalty": 0.5}, {"repetition_penalty": 1.1}, {"min_p": 0.1}, {"top_k": 21},
                 {"top_p": 0.0}, {"presence_penalty": 3}, {"temperature": -1}):

@@ -89,13 +89,22 @@ REAL_WIDTHS = {
 }
 
 
+# Two of the tiny configurations with room for more than a thousand positions: decode steps are captured and
+# replayed within a bucket of context lengths (the first ends at 1,024), so a request that decodes across that
+# length changes the captured step, the number of ranges its keys are cut into, and the merge.
+LONG = {
+    "long-B": dict(TINY["tiny-B"], config=dict(TINY["tiny-B"]["config"], max_position_embeddings=1280)),
+    "long-E": dict(TINY["tiny-E"], config=dict(TINY["tiny-E"]["config"], max_position_embeddings=1280)),
+}
+
+
 def make_model(folder: str, name: str) -> dict:
     """Write the folder through the package's random-weights mode, then sharpen q/k and rewrite.
     Returns {dir, config (dict), weights (dict by checkpoint name, as stored), page_size}."""
     from safetensors.torch import load_file, save_file
 
     from lia_rs_b200 import LlamaConfig, write_random_model
-    entry = TINY[name] if name in TINY else REAL_WIDTHS[name]
+    entry = TINY[name] if name in TINY else LONG[name] if name in LONG else REAL_WIDTHS[name]
     write_random_model(LlamaConfig.from_dict(entry["config"]), folder, seed=entry["seed"])
     path = os.path.join(folder, "model.safetensors")
     weights = load_file(path)            # the safetensors library, independent of the package's reader

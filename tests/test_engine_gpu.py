@@ -144,6 +144,33 @@ def test_long_decoding(tiny_models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(helpers.LONG))
+def test_decoding_across_the_end_of_a_context_bucket(tmp_path, name, dtype):
+    """A long request decodes from position 1,010 to 1,050 beside a short one: the captured decode step of the
+    first bucket of context lengths gives way to the next one's (more ranges of keys per token) at 1,024, and
+    the short request's rows ride along through the change."""
+    model = helpers.make_model(str(tmp_path / name), name)
+    vocab = model["config"]["vocab_size"]
+    long_one, short_one = helpers.random_tokens(vocab, 1050, 5), helpers.random_tokens(vocab, 60, 6)
+    from lia_rs_b200.engine import Engine
+    engine = Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=1280, max_seqs=2,
+                    max_batch_tokens=512)
+    replay = helpers.Replayer(engine)
+    replay.step([("long", long_one[:500], [])])
+    replay.step([("long", long_one[500:1010], []), ("short", short_one[:2], [])])
+    rows_long, rows_short = [], []
+    for i in range(40):
+        both = replay.step([("short", [short_one[2 + i]], [0]), ("long", [long_one[1010 + i]], [0])])
+        rows_short.append(both[0:1])
+        rows_long.append(both[1:2])
+    assert {key for key in engine._graphs} == {(2, 2, 1024), (2, 2, 2048)} and engine.stats["graph_replays"] >= 36
+    helpers.assert_close(np.concatenate(rows_long), helpers.plain_logits(model, long_one, dtype)[1010:], dtype,
+                         f"{name} across the bucket, long request")
+    helpers.assert_close(np.concatenate(rows_short), helpers.plain_logits(model, short_one[:42], dtype)[2:], dtype,
+                         f"{name} across the bucket, short request")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
 def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
     model = tiny_models[name]

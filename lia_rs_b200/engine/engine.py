@@ -50,8 +50,8 @@ class Engine:
         up to 16 tokens through the persistent kernel over all layers when the model's parts allow it
         (csrc/decode_stack.cu).  Off unless asked for (here, or with the environment variable
         LIA_DECODE_STACK=1): on a B200 the part-by-part kernels under a CUDA graph are some 8% faster;
-        `cuda_graphs`: capture decode steps
-        (every entry a single token) in CUDA graphs, one per batch size, and replay them."""
+        `cuda_graphs`: capture steps (decoded tokens, prompt portions, both) in CUDA graphs, one per
+        shape of a step, when a shape comes a second time, and replay them."""
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be one of {sorted(_DTYPES)}")
         if not torch.cuda.is_available():
@@ -87,7 +87,9 @@ class Engine:
             decode_stack = os.environ.get("LIA_DECODE_STACK", "0") == "1"
         self.model.use_decode_stack = bool(decode_stack)
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
-        self._graphs = {}              # (tokens, wanted, context bucket) -> None (seen once) | (graph, logits, kernels, generation)
+        # (tokens, wanted, context bucket, tokens of each entry) -> None (seen once) | (graph, logits, kernels, generation),
+        # least recently used first
+        self._graphs = {}
 
     @classmethod
     def random(cls, config, seed: int = 0, **options) -> "Engine":
@@ -131,7 +133,7 @@ class Engine:
             return self.runtime_step.logits(0, self.spec.vocab_size)
         with torch.cuda.device(self.device):
             ctx = self.runtime_step.begin(entries, feed=None if feed is None else feed.device_tokens)
-            if self.cuda_graphs and ctx.decode_only:
+            if self.cuda_graphs:
                 logits = self._replay(ctx)
             else:
                 logits = self._launch(ctx)
@@ -146,16 +148,23 @@ class Engine:
         self.stats["kernels"] += ops.kernel_launches() - before
         return logits
 
+    MAX_GRAPHS = 64
+
     def _replay(self, ctx) -> torch.Tensor:
-        """A decode step through its CUDA graph.  The step's metadata (token ids, positions, slots,
-        wanted rows) and the block tables already lie in fixed device buffers, so a graph captured for
-        (tokens, wanted, context bucket) serves every later step of that shape and bucket.  The first step of a shape runs launch
-        by launch (it allocates the workspace); the second is captured; a reallocation of any buffer
-        makes the captured graphs stale."""
-        key = (ctx.n_tokens, ctx.n_out, ctx.context_bucket)
-        entry = self._graphs.get(key, False)
+        """A step through its CUDA graph.  The step's metadata (token ids, positions, slots, wanted rows,
+        the portions' starts) and the block tables lie in fixed device buffers, and what the host decides about
+        a step's launches follows from the number of tokens of each entry, the number of wanted rows and the
+        context bucket; so a graph captured for these serves every later step of that shape: every decode step
+        of a batch, and every portion of a long prompt that a scheduler cuts under the same budget.  The first
+        step of a shape runs launch by launch (it allocates the workspace); the second is captured; a
+        reallocation of any buffer makes the captured graphs stale.  The least recently used graphs go when
+        there are more than MAX_GRAPHS shapes."""
+        key = (ctx.n_tokens, ctx.n_out, ctx.context_bucket, tuple(count for _, _, count, _ in ctx.segments))
+        entry = self._graphs.pop(key, False)
         if entry is False:
             self._graphs[key] = None
+            while len(self._graphs) > self.MAX_GRAPHS:
+                del self._graphs[next(iter(self._graphs))]
             return self._launch(ctx)
         if entry is None or entry[3] != self.runtime_step.generation:
             graph = torch.cuda.CUDAGraph()
@@ -163,7 +172,7 @@ class Engine:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
             entry = (graph, logits, ops.kernel_launches() - before, self.runtime_step.generation)
-            self._graphs[key] = entry
+        self._graphs[key] = entry                        # most recently used last
         graph, logits, kernels, _ = entry
         graph.replay()
         self.stats["kernels"] += kernels

@@ -66,11 +66,12 @@ class Part:
     `prefix`); `__init__` receives them already on the device, in their storage element type.
 
     `graph_safe`: the part's `forward` launches the same kernels with the same arguments in every step
-    that has the same number of tokens and of wanted rows; whatever differs between such steps
-    (token ids, positions, slots, pages) it reads on the device, from `ctx.tokens`, `ctx.positions`,
-    `ctx.slots` and the block tables, never on the host.  Only when every part of a model says so are
-    its decode steps captured in CUDA graphs and replayed; a part that looks at `ctx.segments` in
-    Python, or allocates, leaves this False and the model runs launch by launch."""
+    whose entries have the same numbers of tokens, with the same number of wanted rows and the same
+    `ctx.context_bucket`; whatever else differs between such steps (token ids, positions, the portions'
+    starts, slots, pages) it reads on the device, from `ctx.tokens`, `ctx.positions`, `ctx.slots`,
+    `ctx.prefill_segments` and the block tables, never on the host.  Only when every part of a model says
+    so are its steps captured in CUDA graphs and replayed; a part that looks at the starts in
+    `ctx.segments` in Python, or allocates, leaves this False and the model runs launch by launch."""
 
     graph_safe = False
 

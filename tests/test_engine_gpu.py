@@ -163,7 +163,8 @@ def test_decoding_across_the_end_of_a_context_bucket(tmp_path, name, dtype):
         both = replay.step([("short", [short_one[2 + i]], [0]), ("long", [long_one[1010 + i]], [0])])
         rows_short.append(both[0:1])
         rows_long.append(both[1:2])
-    assert {key for key in engine._graphs} == {(2, 2, 1024), (2, 2, 2048)} and engine.stats["graph_replays"] >= 36
+    decode_shapes = {key[:3] for key in engine._graphs if key[3] == (1, 1)}
+    assert decode_shapes == {(2, 2, 1024), (2, 2, 2048)} and engine.stats["graph_replays"] >= 36
     helpers.assert_close(np.concatenate(rows_long), helpers.plain_logits(model, long_one, dtype)[1010:], dtype,
                          f"{name} across the bucket, long request")
     helpers.assert_close(np.concatenate(rows_short), helpers.plain_logits(model, short_one[:42], dtype)[2:], dtype,

@@ -7,20 +7,14 @@
 // The kernel is persistent: at most one CTA per SM, each walking a list of work units
 // (tile, K range) round-robin.  Inside a CTA the warps have fixed roles and never wait for one another
 // except through mbarriers:
-//   warp 0      one lane issues the TMA loads of W: per 64-wide K block one box (two for the fused
-//               gate/up product), 128-byte swizzled, into a ring of shared-memory stages.  The ring
-//               runs on across units, so the memory pipeline never drains.
-//   warp 7      one lane issues the TMA loads of X into the same stages (a thread issues a TMA load in
-//               0.1 us or more, so one thread for both operands sets the pace of a narrow tile's K block).
+//   warp 0      one lane issues the TMA loads: per 64-wide K block one box of W (two for the fused
+//               gate/up product) and one box of X, 128-byte swizzled, into a ring of shared-memory
+//               stages.  The ring runs on across units, so the memory pipeline never drains.
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma (M 128, N n_tile, K 16, four per stage)
 //               into one of TWO accumulator buffers in TMEM and commits each stage's mbarrier when its
 //               operands have been read, and the buffer's mbarrier when the unit is complete.
 //   warps 2..5  the epilogue: they read a finished buffer with tcgen05.ld (each warp its 32 TMEM lanes
 //               = 32 features) while the MMA warp already fills the other buffer.
-//   warp 6      for tiles of at most 128 tokens a second MMA issuer: issuing one tcgen05.mma costs its thread
-//               about 130 cycles whatever the tile's width, which for a narrow tile is longer than the MMA
-//               itself, so the K blocks of a unit alternate between two threads, each with an accumulator of
-//               its own in TMEM, and the epilogue adds the two.
 // Epilogues: STORE out = alpha*acc; ACCUM out += alpha*acc (32-bit residual stream);
 // SWIGLU out = up * gate/(1+exp(-gate)) with gate and up accumulated side by side in TMEM.
 // With many tokens the tile goes through shared memory and leaves by TMA (bulk store, or bulk
@@ -50,7 +44,7 @@ using namespace tc5;
 #define GEMM_SWIGLU 2
 
 namespace {
-constexpr int THREADS = 256;
+constexpr int THREADS = 192;
 constexpr int MAX_STAGES = 12;
 constexpr int SMEM_BYTES = 226 * 1024;         // dynamic shared memory asked for (a CTA may have 227 KB; 1 KB is static)
 constexpr int STAGING_TOKENS = 32;             // tokens per TMA store of the epilogue
@@ -68,7 +62,6 @@ struct Shape {
     int acc_cols;             // TMEM columns of one accumulator buffer
     int tmem_cols;            // TMEM columns allocated (all buffers, a power of two >= 32)
     int acc_buffers;          // 2: the epilogue drains one accumulator while the next unit fills the other; 1: they take turns
-    int chains;               // 2: a second thread issues every other K block's MMAs into an accumulator of its own
     int via_tma;              // 1: the epilogue leaves through shared memory and TMA
     int ldo;
     float alpha;
@@ -125,7 +118,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_init(smem_u32(&empty_bar[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&acc_full[i]), (uint32_t)s.chains);   // one commit per issuing thread
+            mbar_init(smem_u32(&acc_full[i]), 1);
             mbar_init(smem_u32(&acc_empty[i]), 4);         // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -181,6 +174,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
                     if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
                 }
+                tma_load_2d(dst + A_TILES * a_bytes, &map_x, kb * BLOCK_K, u.t0, full);
+                if (s.x_box < s.n_tile)
+                    tma_load_2d(dst + A_TILES * a_bytes + (uint32_t)s.x_box * 128u, &map_x, kb * BLOCK_K, u.t0 + s.x_box, full);
                 issued = it + 1;
             }
         }
@@ -190,30 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int i = max(0, issued - s.stages); i < issued; ++i)
                 mbar_wait(smem_u32(&full_bar[i % s.stages]), (uint32_t)(i / s.stages) & 1u);
         }
-    } else if (warp == 7 && lane == 0) {
-        // ---- TMA producer of X: the same stages and barriers; its bytes are part of what the W producer told the
-        // stage's barrier to expect (they may land before that, the barrier's pending arrival keeps the phase open) ----
-        pdl_wait();
-        bool ok = true;
-        int it = 0;
-        for (int index = first_unit; index < units && ok; index += stride) {
-            const Unit u = unit_at(s, index);
-            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-                const int st = it % s.stages;
-                const uint32_t full = smem_u32(&full_bar[st]);
-                const uint32_t dst = smem_base + (uint32_t)st * stage_bytes + A_TILES * a_bytes;
-                if (it >= s.stages) {
-                    const uint32_t phase = (uint32_t)(it / s.stages) & 1u;
-                    if (!mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u)) { ok = false; break; }
-                }
-                tma_load_2d(dst, &map_x, kb * BLOCK_K, u.t0, full);
-                if (s.x_box < s.n_tile) tma_load_2d(dst + (uint32_t)s.x_box * 128u, &map_x, kb * BLOCK_K, u.t0 + s.x_box, full);
-            }
-        }
-        if (!ok && s.error_flag) atomicExch(s.error_flag, 3);
-    } else if ((warp == 1 || (warp == 6 && s.chains == 2)) && lane == 0) {
-        // ---- MMA issuer (warp 1: the unit's K blocks 0, 2, 4, .. or all of them; warp 6: 1, 3, 5, ..) ----
-        const int chain = warp == 1 ? 0 : 1;
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
         // a tile of more than 256 tokens takes two MMAs per K step: 256 tokens, then the rest
         const int n_first = s.n_tile > 256 ? 256 : s.n_tile, n_rest = s.n_tile - n_first;
         const uint32_t idesc = instr_desc(TILE_F, n_first), idesc_rest = instr_desc(TILE_F, n_rest > 0 ? n_rest : 16);
@@ -225,10 +199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t use = s.acc_buffers == 2 ? (uint32_t)n_unit >> 1 : (uint32_t)n_unit;
             if (!mbar_wait(smem_u32(&acc_empty[buf]), (use & 1u) ^ 1u)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t acc = tmem_base + (uint32_t)((buf * s.chains + chain) * s.acc_cols);
-            const int kb_first = u.kb_begin + chain;           // this thread's first K block of the unit
+            const uint32_t acc = tmem_base + (uint32_t)(buf * s.acc_cols);
             for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-                if (s.chains == 2 && ((kb - u.kb_begin) & 1) != chain) continue;
                 const int st = it % s.stages;
                 if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
                 tc_fence_after();
@@ -240,7 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / 16; ++k) {
                         const uint64_t db = smem_desc(b_addr + k * 32);
-                        const uint32_t accumulate = (kb > kb_first || k > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
                         tc_mma(acc, smem_desc(a_addr + k * 32), db, idesc, accumulate);
                         if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
                     }
@@ -258,8 +230,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (ok) tc_commit(smem_u32(&acc_full[buf]));  // the accumulator is complete
         }
         if (!ok && s.error_flag) atomicExch(s.error_flag, 3);
-    } else if (warp >= 2 && warp <= 5) {
-        // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 (warp 6 has no part in it: its other lanes idle) ----
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 ----
         const int group = warp & 3;
         const int epi_thread = threadIdx.x - 64;          // 0..127
         pdl_wait();
@@ -273,10 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const bool empty_range = u.kb_end <= u.kb_begin;           // cannot happen (splits <= kblocks)
             if (!empty_range && !mbar_wait(smem_u32(&acc_full[buf]), use & 1u)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(group * 32) << 16) + (uint32_t)(buf * s.chains * s.acc_cols);
-            // the second issuer's accumulator, where it has one and the unit gave it a K block
-            const bool second = s.chains == 2 && u.kb_end - u.kb_begin >= 2;
-            const uint32_t lane_addr2 = lane_addr + (uint32_t)s.acc_cols;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(group * 32) << 16) + (uint32_t)(buf * s.acc_cols);
 
             if (s.splits > 1) {
                 // raw accumulator to scratch [split][t][n_total]
@@ -286,17 +255,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
-                    if (second) {
-                        float other[16];
-                        tmem_load16(lane_addr2 + (uint32_t)c0, other);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) acc[c] += other[c];
-                        if (MODE == GEMM_SWIGLU) {
-                            tmem_load16(lane_addr2 + (uint32_t)(s.n_tile + c0), other);
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) up[c] += other[c];
-                        }
-                    }
                     if (f < s.N) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
@@ -364,19 +322,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tmem_load32_nowait(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load32_nowait(lane_addr + (uint32_t)(s.n_tile + c0), up);
                     tmem_load_wait();
-                    if (second) {
-                        float other[32];
-                        tmem_load32_nowait(lane_addr2 + (uint32_t)c0, other);
-                        tmem_load_wait();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) acc[c] += other[c];
-                        if (MODE == GEMM_SWIGLU) {
-                            tmem_load32_nowait(lane_addr2 + (uint32_t)(s.n_tile + c0), other);
-                            tmem_load_wait();
-#pragma unroll
-                            for (int c = 0; c < 32; ++c) up[c] += other[c];
-                        }
-                    }
                     const int sbuf = chunk_count & 1;
                     ++chunk_count;
                     // the store that last read this staging buffer must be done reading it
@@ -409,17 +354,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
-                    if (second) {
-                        float other[16];
-                        tmem_load16(lane_addr2 + (uint32_t)c0, other);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) acc[c] += other[c];
-                        if (MODE == GEMM_SWIGLU) {
-                            tmem_load16(lane_addr2 + (uint32_t)(s.n_tile + c0), other);
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) up[c] += other[c];
-                        }
-                    }
                     if (f < s.N) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
@@ -469,9 +403,9 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
         while (p.n_tile < M) p.n_tile *= 2;
     } else {
         // many tokens: the tile width (a multiple of 32, the epilogue's step) that leaves the SMs least idle: rounds of
-        // tiles times the time of one.  Measured on a B200: a tile takes 5.5 us plus, per K block, the longer of its
-        // MMAs (0.43 us at 256 tokens, in proportion below; twice that for the gated product's two accumulators) and
-        // of its operands' way into shared memory (16 KB of weights, 32 KB gated, and 128 B a token at 112 GB/s).
+        // tiles times the time of one.  Measured on a B200: a tile takes 5.5 us plus, per K block, its MMAs' time (0.43 us
+        // at 256 tokens, in proportion below; twice that for the gated product's two accumulators) but no less than
+        // what its issuing threads need whatever the width (0.36 us: four MMAs and two TMA loads; 0.58 us gated).
         // Ties go to the wider tile (fewer bytes through shared memory per flop).  Up to 512 tokens wide (all of
         // TMEM, so one buffer: the epilogue and the next tile take turns), 256 for the gated product, where that saves
         // a round: 2,048 tokens x 2,560 features are 140 tiles of 320 tokens, one round, against 260 of 160.  Down
@@ -485,8 +419,8 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
         for (int n = widest; n >= 32; n -= 32) {
             const long long tiles = (long long)p.f_tiles * ((M + n - 1) / n);
             const long long rounds = (tiles + sm_count - 1) / sm_count;
-            const double mma = weights * 0.43 * n / 256.0, load = (weights * 16384.0 + 128.0 * n) / 112000.0;
-            const double cost = (double)rounds * (5.5 + kblocks * std::max(mma, load));
+            const double mma = weights * 0.43 * n / 256.0, issue = swiglu ? 0.58 : 0.36;
+            const double cost = (double)rounds * (5.5 + kblocks * std::max(mma, issue));
             if (best < 0 || cost < best) { best = cost; p.n_tile = n; }
         }
     }
@@ -543,9 +477,8 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
     s.x_box = plan.n_tile > 256 ? plan.n_tile / 2 : plan.n_tile;
     s.acc_cols = swiglu ? 2 * plan.n_tile : plan.n_tile;
-    s.chains = (plan.n_tile <= 128 && s.kblocks / plan.splits >= 2) ? 2 : 1;
-    s.acc_buffers = 2 * s.chains * s.acc_cols <= 512 ? 2 : 1;
-    s.tmem_cols = pow2_at_least(s.acc_buffers * s.chains * s.acc_cols);
+    s.acc_buffers = 2 * s.acc_cols <= 512 ? 2 : 1;
+    s.tmem_cols = pow2_at_least(s.acc_buffers * s.acc_cols);
     s.ldo = ldo; s.alpha = alpha; s.error_flag = error_flag;
     s.counters = reinterpret_cast<int*>(scratch);
     s.partial = scratch ? scratch + COUNTER_WORDS : nullptr;

@@ -9,9 +9,8 @@
   (csrc/gemm_skinny.cu); beyond that, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
   while it applies (16 tokens of a 2B-class layer: 58 us with the few-token kernel, 63 us with the cluster
   kernel; 24 tokens: 82 against 66; 32 tokens: 91 against 70: every CTA of the few-token kernel reads all the
-  tokens' rows from L2), up to 256 tokens; beyond that the persistent tcgen05 kernel, which for more than 128
-  tokens cuts the tokens into tiles as narrow as fills the SMs and K not at all (a 2,048 x 2,048 product at 512
-  tokens: 13 us against the cluster kernel's 18 us; at 256 tokens 12.9 against 12.4);
+  tokens' rows from L2); then the persistent tcgen05 kernel, which cuts K through scratch memory up to 128
+  tokens and beyond that cuts the tokens into tiles as narrow as fills the SMs;
 * what TMA cannot address goes to the few-token kernel if it can take it, else, and always for the 32-bit
   path, to the product on the 32-bit pipes (csrc/gemm_simt.cu)."""
 from __future__ import annotations
@@ -28,7 +27,6 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 
 
 SKINNY_BEST_TOKENS = 16
-CLUSTER_BEST_TOKENS = 256
 
 
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
@@ -41,7 +39,7 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
         ops.gemm_tc(mode, a, w, out, alpha)
     elif few and a.shape[0] <= SKINNY_BEST_TOKENS:
         ops.gemm_skinny(mode, a, w, out, alpha)
-    elif tensor_cores and a.shape[0] <= CLUSTER_BEST_TOKENS and ops.gemm_cluster_accepts(mode, a, w, out):
+    elif tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
         ops.gemm_cluster(mode, a, w, out, alpha)
     elif tensor_cores:
         ops.gemm_tc(mode, a, w, out, alpha)

@@ -18,6 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Sequence
 
+import numpy as np
 import torch
 
 from ..kernels import ops
@@ -87,6 +88,7 @@ class StepRuntime:
         self.device = torch.device(device)
         cap = self.max_batch_tokens
         self._meta_host = torch.zeros(7 * cap, dtype=torch.int32, pin_memory=True)
+        self._meta_view = self._meta_host.numpy()       # the same memory, for writing slices without a tensor each
         self._meta_device = torch.zeros(7 * cap, dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -148,8 +150,9 @@ class StepRuntime:
         """Check the batch, stage its metadata and the changed block-table rows on the device,
         and return the context for the model.  `feed` (int32, on the device): the token of entry i is
         feed[i] (every entry then brings one token, whose id in the entry only stands in)."""
-        tokens, positions, slots, out_rows, segments = [], [], [], [], []
+        out_rows, segments = [], []
         seen = set()
+        n = 0
         for entry in entries:
             count = len(entry.tokens)
             if count == 0:
@@ -162,32 +165,46 @@ class StepRuntime:
             if entry.start < 0 or entry.start + count > self.cache.length[entry.slot]:
                 raise StepError(f"slot {entry.slot}: positions [{entry.start}, {entry.start + count}) have no "
                                 f"reserved pages (reserved up to {self.cache.length[entry.slot]})")
-            low, high = min(entry.tokens), max(entry.tokens)
+            low, high = (entry.tokens[0], entry.tokens[0]) if count == 1 else (min(entry.tokens), max(entry.tokens))
             if low < 0 or high >= self.vocab_size:
                 raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
                                 f"{self.vocab_size}")
-            offset = len(tokens)
             for w in entry.want:
                 if not 0 <= w < count:
                     raise StepError(f"wanted index {w} is outside the entry's {count} tokens")
-                out_rows.append(offset + w)
-            segments.append((entry.slot, entry.start, count, offset))
-            tokens.extend(entry.tokens)
-            positions.extend(range(entry.start, entry.start + count))
-            slots.extend([entry.slot] * count)
-        decode_rows = [offset for _, _, count, offset in segments if count == 1]
-        prefill_rows = [offset + i for _, _, count, offset in segments if count > 1 for i in range(count)]
-        n, n_out = len(tokens), len(out_rows)
+                out_rows.append(n + w)
+            segments.append((entry.slot, entry.start, count, n))
+            n += count
+        n_out = len(out_rows)
         if n > self.max_batch_tokens:
             raise StepError(f"{n} tokens in one step exceed max_batch_tokens={self.max_batch_tokens}")
         self._copy_event.synchronize()               # the staging buffer of the last step is free again
         self.raise_device_errors()
+        # the metadata is written straight into the pinned staging buffer, a slice per entry:
+        # [tokens n][positions n][slots n][wanted rows][rows of single tokens][rows of portions][portions: row, start, count]
         host = self._meta_host
+        view = self._meta_view
+        token_part, position_part, slot_part = view[0:n], view[n:2 * n], view[2 * n:3 * n]
+        for entry, (slot, start, count, offset) in zip(entries, segments):
+            if count == 1:
+                token_part[offset], position_part[offset], slot_part[offset] = entry.tokens[0], start, slot
+            else:
+                token_part[offset:offset + count] = entry.tokens
+                position_part[offset:offset + count] = np.arange(start, start + count, dtype=np.int32)
+                slot_part[offset:offset + count] = slot
+        decode_rows = [offset for _, _, count, offset in segments if count == 1]
+        at = 3 * n
+        view[at:at + n_out] = out_rows
+        at += n_out
+        view[at:at + len(decode_rows)] = decode_rows
+        at += len(decode_rows)
+        for _, _, count, offset in segments:
+            if count > 1:
+                view[at:at + count] = np.arange(offset, offset + count, dtype=np.int32)
+                at += count
         prefill_segments = [x for _, start, count, offset in segments if count > 1 for x in (offset, start, count)]
-        packed = torch.tensor(tokens + positions + slots + out_rows + decode_rows + prefill_rows
-                              + prefill_segments, dtype=torch.int32)
+        view[at:at + len(prefill_segments)] = prefill_segments
         total = 4 * n + n_out + len(prefill_segments)
-        host[:total] = packed
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
         if feed is not None:
             if any(count != 1 for _, _, count, _ in segments) or feed.numel() < n or feed.dtype != torch.int32:

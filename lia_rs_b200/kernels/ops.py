@@ -96,7 +96,14 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream's handle.  Asked for at every launch (a graph capture runs on a stream of its own), so through
+    torch's direct call where this torch has it: building a Stream object each time cost several microseconds a launch."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -165,7 +172,7 @@ _sm_count = {}
 
 
 def _device_scratch(device):
-    key = torch.device(device).index or 0
+    key = (device.index if isinstance(device, torch.device) else torch.device(device).index) or 0
     if key not in _scratch:
         # zeroed: the first words are tile counters that every product leaves at zero again
         _scratch[key] = torch.zeros(_SCRATCH_FLOATS, dtype=torch.float32, device=device)

@@ -29,21 +29,39 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 SKINNY_BEST_TOKENS = 16
 
 
+_TC, _SKINNY, _CLUSTER, _SIMT = range(4)
+_choices = {}          # what decides the choice -> the kernel chosen (the checks cost more than the lookup)
+
+
+def _choose(mode, a, w, out) -> int:
+    tensor_cores = ops.gemm_tc_accepts(mode, a, w, out)
+    few = ops.gemm_skinny_accepts(mode, a, w, out)
+    if tensor_cores and ops.gemm_tc_tiles_fill_the_sms(a, out):
+        return _TC
+    if few and a.shape[0] <= SKINNY_BEST_TOKENS:
+        return _SKINNY
+    if tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
+        return _CLUSTER
+    if tensor_cores:
+        return _TC
+    return _SKINNY if few else _SIMT
+
+
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
     if a.dtype != torch.bfloat16:
         ops.gemm_simt(mode, a, w, out, alpha)
         return
-    tensor_cores = ops.gemm_tc_accepts(mode, a, w, out)
-    few = ops.gemm_skinny_accepts(mode, a, w, out)
-    if tensor_cores and ops.gemm_tc_tiles_fill_the_sms(a, out):
+    # everything the kernels' acceptance looks at: sizes, row strides, element types, 16-byte alignment of the bases
+    key = (mode, a.shape, a.stride(), a.data_ptr() & 15, w.shape, w.stride(), w.dtype, w.data_ptr() & 15,
+           out.shape[1], out.stride(), out.dtype, out.data_ptr() & 15, a.device.index)
+    choice = _choices.get(key)
+    if choice is None:
+        choice = _choices[key] = _choose(mode, a, w, out)
+    if choice == _TC:
         ops.gemm_tc(mode, a, w, out, alpha)
-    elif few and a.shape[0] <= SKINNY_BEST_TOKENS:
+    elif choice == _SKINNY:
         ops.gemm_skinny(mode, a, w, out, alpha)
-    elif tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
+    elif choice == _CLUSTER:
         ops.gemm_cluster(mode, a, w, out, alpha)
-    elif tensor_cores:
-        ops.gemm_tc(mode, a, w, out, alpha)
-    elif few:
-        ops.gemm_skinny(mode, a, w, out, alpha)
     else:
         ops.gemm_simt(mode, a, w, out, alpha)

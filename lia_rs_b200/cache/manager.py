@@ -52,6 +52,7 @@ class CacheGroup:
         self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
         pin = torch.device(device).type == "cuda"
         self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, pin_memory=pin)
+        self.host_view = self.host_table.numpy()           # the same memory: single entries are written through this
         self.device_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, device=device)
         self.dirty = {}                                    # slot -> (lo, hi) block range to copy
 
@@ -93,7 +94,7 @@ class CacheGroup:
         for b in give_back:
             self.pool.release(table[b])
             table[b] = -1
-            self.host_table[slot, b] = -1
+            self.host_view[slot, b] = -1
             self._mark(slot, b)
         self.first_block[slot] = max(self.first_block[slot], min(keep_from, len(table)))
         for b in allocate:
@@ -101,7 +102,7 @@ class CacheGroup:
                 table.append(-1)
             page = self.pool.allocate()
             table[b] = page
-            self.host_table[slot, b] = page
+            self.host_view[slot, b] = page
             self._mark(slot, b)
 
     def release_slot(self, slot):
@@ -110,7 +111,7 @@ class CacheGroup:
             if page >= 0:
                 self.pool.release(page)
         if table:
-            self.host_table[slot, :len(table)] = -1
+            self.host_view[slot, :len(table)] = -1
             self.dirty[slot] = (0, max(len(table), self.dirty.get(slot, (0, 0))[1]))
         self.tables[slot] = []
         self.first_block[slot] = 0
@@ -182,6 +183,8 @@ class CacheManager:
     def pages_for(self, slot: int, start: int, end: int) -> int:
         """How many free pages `ensure(slot, start, end)` would need in the tightest group,
         counting the pages it would first give back."""
+        if all(group.window is None and (end - 1) // group.page_size < len(group.tables[slot]) for group in self.groups):
+            return 0                                              # every position already has its page
         worst = 0
         for group in self.groups:
             allocate, give_back, _ = group.pages_needed(slot, start, end)
@@ -195,6 +198,9 @@ class CacheManager:
             raise PageError(f"slot {slot} is not live")
         if not 0 <= start < end or end > self.max_context:
             raise PageError(f"positions [{start}, {end}) are outside the context of {self.max_context}")
+        if all(group.window is None and (end - 1) // group.page_size < len(group.tables[slot]) for group in self.groups):
+            self.length[slot] = max(self.length[slot], end)      # every position already has its page (most decode steps)
+            return True
         plans = []
         for group in self.groups:
             allocate, give_back, keep_from = group.pages_needed(slot, start, end)

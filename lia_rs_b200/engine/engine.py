@@ -21,7 +21,7 @@ from ..kernels import ops
 from ..models import DecoderModel
 from ..parts import Runtime
 from ..weights import load_weights
-from .step import StepEntry, StepError, StepRuntime
+from .step import StepRuntime
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 

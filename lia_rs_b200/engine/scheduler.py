@@ -39,8 +39,6 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Optional
 
-import numpy as np
-
 from ..sampling import RequestSampler, Sampling
 from .step import StepEntry
 

@@ -23,8 +23,6 @@ import json
 import os
 import sys
 
-import numpy as np
-
 MAX_LIVE = 4
 
 

@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from ..parts import LayerSpec, NORMS, PartSpec, build_layer, layer_tensor_specs, lookup, MIXERS
+from ..parts import NORMS, PartSpec, build_layer, layer_tensor_specs, lookup, MIXERS
 from ..parts.linear import STORE, linear, prepare_weight
 from ..weights import TensorSpec
 

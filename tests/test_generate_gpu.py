@@ -3,9 +3,7 @@ import os
 import subprocess
 import sys
 
-import numpy as np
 import pytest
-import torch
 
 import helpers
 import plain_impl

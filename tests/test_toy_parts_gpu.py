@@ -2,8 +2,6 @@
 stepped without a change to the framework's files: they prove the interfaces for a new feed-forward and
 a new position encoding (the toy mixer with state of its own is in test_toy_mixer_gpu.py).  Neither is a
 model of anyone's."""
-import math
-
 import numpy as np
 import pytest
 import torch

@@ -4,7 +4,6 @@ The entry point serves hosts that must not call cudaMalloc when they need a prod
 pool, a plug-in whose host owns device memory): its split-K scratch is a static array inside the
 library.  This file is collected last on purpose: if it fails, a run that stops at the first failure has
 already run every other test.  It must pass alone in a fresh process and after the other tests."""
-import ctypes
 import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
 

@@ -49,15 +49,15 @@ class PagePool:
     def check(self, held_pages) -> None:
         """Invariant: every page is either on the free list once or held by exactly the given
         holders.  `held_pages` lists the pages that the block tables hold (with repetition)."""
-        held = sorted(held_pages)
-        if len(set(self._free)) != len(self._free):
+        free = set(self._free)
+        if len(free) != len(self._free):
             raise PageError("a page is on the free list twice")
         counts = {}
-        for page in held:
+        for page in held_pages:
             counts[page] = counts.get(page, 0) + 1
         for page in range(self.num_pages):
             expected = counts.get(page, 0)
             if self._users[page] != expected:
                 raise PageError(f"page {page}: {self._users[page]} users recorded, {expected} holders found")
-            if (expected == 0) != (page in set(self._free)):
+            if (expected == 0) != (page in free):
                 raise PageError(f"page {page} is lost or both held and free")

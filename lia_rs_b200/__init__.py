@@ -7,11 +7,11 @@ from .config import ConfigError, LlamaConfig, register_architecture, resolve_arc
 from .weights import WeightError, write_random_model
 
 __all__ = ["ConfigError", "LlamaConfig", "register_architecture", "resolve_architecture", "WeightError",
-           "write_random_model", "Engine", "StepEntry", "generate", "Sampling"]
+           "write_random_model", "Engine", "StepEntry", "generate", "replay", "Sampling"]
 
 
 def __getattr__(name):
-    if name in ("Engine", "StepEntry", "StepError"):
+    if name in ("Engine", "StepEntry", "StepError", "replay"):
         from . import engine
         return getattr(engine, name)
     if name in ("generate", "Generator"):

@@ -12,7 +12,11 @@ pages per kind of need, and slots of fixed-size per-request state.
   wholly before `start - window + 1` are given back first: no later token can see them.
 * `release(slot)` gives everything back (request finished, aborted or preempted:
   src/server/paged/schedule.rs:134, preempt.rs:73,108).
-* Block tables live on the host (pinned) and on the device; `flush()` copies the rows that changed.
+* Block tables live on the host and on the device; `flush()` copies the rows that changed.  The copies are
+  asynchronous and read a snapshot of those rows taken at `flush()` (a small ring of pinned staging buffers,
+  each guarded by an event), never the live table: the host may go on changing the table (reserve pages for
+  the step after, release a request that ended) while the copies of an earlier step are still queued.  The
+  reference uploads the whole table before each step and waits (src/inference/paging.rs:224-237).
   A table entry of -1 means "no page" (never allocated, or passed by the window).
 
 The manager is pure bookkeeping plus tensors; it runs on the CPU device too, which is how its
@@ -40,7 +44,19 @@ class KVView:
     group: int
 
 
+class _NoFence:
+    """Stands in for a CUDA event where copies are synchronous (the CPU device of the manager's tests)."""
+
+    def record(self):
+        pass
+
+    def synchronize(self):
+        pass
+
+
 class CacheGroup:
+    RING = 3          # staging snapshots in flight: one per step the host may run ahead of the device, and one to spare
+
     def __init__(self, index, request, cache_ids, num_pages, page_size, max_slots, max_blocks, dtype, device):
         self.index, self.request, self.cache_ids = index, request, list(cache_ids)
         self.page_size, self.window = page_size, request.window
@@ -51,10 +67,15 @@ class CacheGroup:
         self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
         self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
         pin = torch.device(device).type == "cuda"
-        self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, pin_memory=pin)
+        self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32)      # the live table
         self.host_view = self.host_table.numpy()           # the same memory: single entries are written through this
         self.device_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, device=device)
         self.dirty = {}                                    # slot -> (lo, hi) block range to copy
+        # what the asynchronous copies read: snapshots of the dirty ranges, taken at flush()
+        self._staging = [torch.empty(max_slots * max_blocks, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self._staging_views = [t.numpy() for t in self._staging]
+        self._fences = [torch.cuda.Event() if pin else _NoFence() for _ in range(self.RING)]
+        self._turn = 0
 
     def _mark(self, slot, block):
         lo, hi = self.dirty.get(slot, (block, block + 1))
@@ -119,9 +140,23 @@ class CacheGroup:
     def held_pages(self):
         return [p for table in self.tables for p in table if p >= 0]
 
+    @staticmethod
+    def _copy(destination, source):
+        destination.copy_(source, non_blocking=True)
+
     def flush(self):
+        if not self.dirty:
+            return
+        self._turn = (self._turn + 1) % self.RING
+        staging, view, fence = self._staging[self._turn], self._staging_views[self._turn], self._fences[self._turn]
+        fence.synchronize()                                # the copies that read this buffer last have run
+        at = 0
         for slot, (lo, hi) in self.dirty.items():
-            self.device_table[slot, lo:hi].copy_(self.host_table[slot, lo:hi], non_blocking=True)
+            count = hi - lo
+            view[at:at + count] = self.host_view[slot, lo:hi]
+            self._copy(self.device_table[slot, lo:hi], staging[at:at + count])
+            at += count
+        fence.record()
         self.dirty = {}
 
 

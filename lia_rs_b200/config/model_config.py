@@ -175,8 +175,6 @@ class LlamaConfig:
             raise ConfigError("num_attention_heads must be a multiple of num_key_value_heads")
         if self.head_dim % 2:
             raise ConfigError("head_dim must be even (rotate-half rotary encoding)")
-        if self.head_dim % 16 or self.head_dim > 256:
-            raise ConfigError("head_dim must be a multiple of 16, at most 256 (attention kernels)")
         for name in ("scale_emb", "scale_depth", "dim_model_base"):
             v = getattr(self, name)
             if v is not None and (not math.isfinite(v) or v <= 0):

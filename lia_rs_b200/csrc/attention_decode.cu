@@ -108,20 +108,17 @@ attention_decode_kernel(Params p) {
     // `left_out`: a key whose row of the tile no copy touches (this CTA writes it into the tile itself)
     auto load_tile = [&](int stage, int key0, int left_out) {
         const uint32_t ks = smem_base + (uint32_t)stage * 2 * T::BYTES + piece_offset, vs = ks + T::BYTES;
+        constexpr int LEFT_OUT = -2147483647 - 1;         // no row of the cache: cache_row_of gives -1 or a row >= 0
         int my_row = -1;
         if (piece < PASSES) {
             const int key = key0 + row_base + piece * ROWS_PER_PASS;
-            if (key == left_out) {
-                my_row = -2;
-            } else if (key < key_end) {
-                const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
-                my_row = table[page] * p.page_size + (key - page * p.page_size);
-            }
+            if (key == left_out) my_row = LEFT_OUT;
+            else if (key < key_end) my_row = cache_row_of(table, key, p.page_size, p.page_shift, p.num_pages, p.error_flag);
         }
 #pragma unroll
         for (int i = 0; i < PASSES; ++i) {
             const int row = __shfl_sync(0xffffffffu, my_row, sub * CHUNKS + i);
-            if (row == -2) continue;
+            if (row == LEFT_OUT) continue;
             const bool valid = row >= 0;
             const size_t src = ((size_t)(valid ? row : 0) * p.nkv + kvh) * D + piece * 8;
             cp_async_16(ks + (uint32_t)(i * ROWS_PER_PASS * CHUNKS * 16), p.k_pages + src, valid);

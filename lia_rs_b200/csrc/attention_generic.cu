@@ -21,7 +21,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          const int* __restrict__ slots, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ rows, T* __restrict__ out, int n_tokens,
                          int nq, int nkv, int d,
-                         int page_size, int window, float scale) {
+                         int page_size, int window, float scale, int num_pages, int* __restrict__ error_flag) {
     __shared__ float q_shared[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -46,11 +46,15 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 
     for (int base = first; base <= pos; base += 32) {
         const int j = base + lane;
-        const bool valid = j <= pos;
+        bool valid = j <= pos;
         int row = 0;
         float score = -INFINITY;
         if (valid) {
-            row = table[j / page_size] * page_size + j % page_size;
+            row = cache_row_of(table, j, page_size, -1, num_pages, error_flag);
+            valid = row >= 0;                       // a key without a page counts for nothing (and the flag is up)
+            row = valid ? row : 0;
+        }
+        if (valid) {
             const T* krow = k_pages + ((size_t)row * nkv + kvh) * d;
             float dot = 0.f;
             for (int i = 0; i < d; ++i) dot = fmaf(q_shared[warp][i], to_float(krow[i]), dot);
@@ -92,7 +96,8 @@ LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const v
                                      const int* positions, const int* slots, const int* block_table,
                                      int table_stride, const int* rows, void* out, int n_tokens, int nq,
                                      int nkv, int d,
-                                     int page_size, int window, float scale, cudaStream_t stream) {
+                                     int page_size, int window, float scale, int num_pages, int* error_flag,
+                                     cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || d > MAX_D || d % 16 || page_size <= 0)
         return LIA_ERR_SIZE;
@@ -102,12 +107,12 @@ LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const v
     if (dtype == LIA_F32)
         attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, slots, block_table,
-            table_stride, rows, (float*)out, n_tokens, nq, nkv, d, page_size, window, scale);
+            table_stride, rows, (float*)out, n_tokens, nq, nkv, d, page_size, window, scale, num_pages, error_flag);
     else if (dtype == LIA_BF16)
         attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, positions,
             slots, block_table, table_stride, rows, (__nv_bfloat16*)out, n_tokens, nq, nkv, d, page_size, window,
-            scale);
+            scale, num_pages, error_flag);
     else
         return LIA_ERR_DTYPE;
     return lia_check_launch();

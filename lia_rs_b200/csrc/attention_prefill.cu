@@ -39,6 +39,8 @@ struct PrefillParams {
     __nv_bfloat16* out;              // [tokens, nq, D]
     int n_segments, table_stride, nq, nkv, page_size, page_shift, window, tokens_per_tile;
     float scale_log2;
+    int num_pages;
+    int* error_flag;                 // raised to 2 when a visible key has no page
 };
 
 template <int D>
@@ -123,10 +125,7 @@ attention_prefill_kernel(PrefillParams p) {
         int my_row = -1;
         if (piece < PASSES) {
             const int key = key0 + row_base + piece * ROWS_PER_PASS;
-            if (key < key_end) {
-                const int page = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
-                my_row = table[page] * p.page_size + (key - page * p.page_size);
-            }
+            if (key < key_end) my_row = cache_row_of(table, key, p.page_size, p.page_shift, p.num_pages, p.error_flag);
         }
 #pragma unroll
         for (int i = 0; i < PASSES; ++i) {
@@ -285,7 +284,7 @@ LIA_EXPORT int lia_attention_prefill_tokens_per_tile(int group) {
 LIA_EXPORT int lia_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                      int n_segments, int n_tiles, const int* slots, const int* block_table,
                                      int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
-                                     float scale, cudaStream_t stream) {
+                                     float scale, int num_pages, int* error_flag, cudaStream_t stream) {
     if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
     const int per_tile = lia_attention_prefill_tokens_per_tile(nq / nkv);
@@ -295,6 +294,7 @@ LIA_EXPORT int lia_attention_prefill(const void* q, const void* k_pages, const v
     p.segments = segments; p.slots = slots; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
     p.n_segments = n_segments; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E;
+    p.num_pages = num_pages; p.error_flag = error_flag;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -66,6 +66,21 @@ static inline int lia_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
 }
 
+// Row of the paged cache [pages * page_size] that holds position `key` of a request whose block-table row is
+// `table`; -1, with error flag 2 raised, when the table names no page of the pool there (the caller then reads
+// zeros in place of the key: never memory outside the pool, never what an earlier tile left behind).
+// `page_shift` >= 0: page_size is that power of two.
+__device__ __forceinline__ int cache_row_of(const int* __restrict__ table, int key, int page_size, int page_shift,
+                                            int num_pages, int* __restrict__ error_flag) {
+    const int block = page_shift >= 0 ? key >> page_shift : key / page_size;
+    const int page = table[block];
+    if (page < 0 || page >= num_pages) {
+        if (error_flag) atomicExch(error_flag, 2);
+        return -1;
+    }
+    return page * page_size + (key - block * page_size);
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 

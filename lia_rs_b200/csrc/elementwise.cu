@@ -304,3 +304,48 @@ LIA_EXPORT int lia_rope_kv_write(const float* qkv, const int* positions, const i
 #undef LIA_ROPE
     return LIA_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------
+// Gather of rows: dst[r, :] = src[index[r], :], rows of `row_bytes` bytes copied as they are (any element
+// type); a negative index gives a row of zeros.  The reference gathers the rows whose logits are wanted
+// before the last layer's feed-forward (src/gpu/kernels/llama.rs:185-198).
+template <typename V>
+__global__ void gather_rows_kernel(const V* __restrict__ src, const int* __restrict__ index, V* __restrict__ dst,
+                                   int rows, int src_rows, long long src_stride, long long dst_stride, int words) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int from = index[r];
+    V* out = dst + (size_t)r * dst_stride;
+    if (from < 0 || from >= src_rows) {
+        V zero;
+        memset(&zero, 0, sizeof(V));
+        for (int i = threadIdx.x; i < words; i += blockDim.x) out[i] = zero;
+        return;
+    }
+    const V* in = src + (size_t)from * src_stride;
+    for (int i = threadIdx.x; i < words; i += blockDim.x) out[i] = in[i];
+}
+
+// src [src_rows, src_stride_bytes a row], dst [rows, dst_stride_bytes a row], row_bytes copied per row.
+LIA_EXPORT int lia_gather_rows(const void* src, const int* index, void* dst, int rows, int src_rows,
+                               long long src_stride_bytes, long long dst_stride_bytes, long long row_bytes,
+                               cudaStream_t stream) {
+    if (rows <= 0 || row_bytes <= 0) return LIA_OK;
+    if (src_rows <= 0 || src_stride_bytes < row_bytes || dst_stride_bytes < row_bytes || row_bytes > (1LL << 30))
+        return LIA_ERR_SIZE;
+    const uintptr_t together = (uintptr_t)src | (uintptr_t)dst | (uintptr_t)src_stride_bytes |
+                               (uintptr_t)dst_stride_bytes | (uintptr_t)row_bytes;
+    const int threads = row_bytes >= 4096 ? 256 : 128;
+    if ((together & 15u) == 0)
+        return lia_launch(gather_rows_kernel<uint4>, dim3(rows), dim3(threads), 0, stream, (const uint4*)src, index,
+                          (uint4*)dst, rows, src_rows, src_stride_bytes / 16, dst_stride_bytes / 16, (int)(row_bytes / 16));
+    if ((together & 3u) == 0)
+        return lia_launch(gather_rows_kernel<uint32_t>, dim3(rows), dim3(threads), 0, stream, (const uint32_t*)src, index,
+                          (uint32_t*)dst, rows, src_rows, src_stride_bytes / 4, dst_stride_bytes / 4, (int)(row_bytes / 4));
+    if ((together & 1u) == 0)
+        return lia_launch(gather_rows_kernel<uint16_t>, dim3(rows), dim3(threads), 0, stream, (const uint16_t*)src, index,
+                          (uint16_t*)dst, rows, src_rows, src_stride_bytes / 2, dst_stride_bytes / 2, (int)(row_bytes / 2));
+    return LIA_ERR_ALIGN;
+}

@@ -560,3 +560,17 @@ LIA_EXPORT int lia_gemm_tc_noalloc(int mode, const void* X, int ldx, const void*
     return lia_gemm_tc(mode, X, ldx, W, ldw, out, out_dtype, ldo, M, N, K, alpha, scratch, NOALLOC_FLOATS,
                        sm_count, error_flag, stream);
 }
+
+// Puts the tile counters at the head of the array back to zero, in stream order.  For use after a call whose
+// kernel gave up on a wait (error flag 3): it may have left counters mid-count, and every later split-K product
+// of the device would then add its ranges at the wrong moment.  Allocates nothing.
+LIA_EXPORT int lia_gemm_tc_noalloc_reset(cudaStream_t stream) {
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc != LIA_OK) return rc;
+    if (cudaMemsetAsync(scratch, 0, COUNTER_WORDS * sizeof(int), stream) != cudaSuccess) {
+        cudaGetLastError();
+        return LIA_ERR_LAUNCH;
+    }
+    return LIA_OK;
+}

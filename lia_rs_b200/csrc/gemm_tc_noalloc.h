@@ -30,7 +30,13 @@
 //    arrived, so a call that ran to its end leaves them ready for the next.  Two calls that overlap on
 //    one GPU (different streams, or different threads) race on counters and sums alike: keep calls to
 //    this entry point on one device in one stream order.
-//  * Return codes are those of lia_gemm_tc (0 = launched) plus LIA_ERR_SCRATCH.
+//  * If a call's kernel gives up on one of its bounded waits it raises `*error_flag` to 3 and may leave tile
+//    counters mid-count.  The caller cannot reach the array, so lia_gemm_tc_noalloc_reset(stream) zeroes the
+//    counters for it (a cudaMemsetAsync in stream order, no allocation): call it after seeing that flag, before
+//    the next product.
+//  * Return codes are those of lia_gemm_tc (0 = launched) plus LIA_ERR_SCRATCH.  LIA_ERR_DRIVER (-4) from the
+//    first call on a device means the address lookup failed, whatever the cause (a stream capture in progress
+//    is one).
 #pragma once
 #include <cuda_runtime.h>
 
@@ -47,6 +53,9 @@ int lia_gemm_tc_noalloc(int mode, const void* X, int ldx, const void* W, int ldw
 
 // Floats of scratch the product of these sizes would use (0: it does not split K).
 long long lia_gemm_tc_noalloc_scratch_floats(int mode, int M, int N, int K, int sm_count);
+
+// Zero the tile counters at the head of the array, in stream order (after a call that raised error flag 3).
+int lia_gemm_tc_noalloc_reset(cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -11,8 +11,6 @@ whole model in true 32-bit: 32-bit weights, activations, cache, and products on 
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..cache import CacheManager
@@ -20,7 +18,7 @@ from ..config import read_config_json, resolve_architecture
 from ..kernels import ops
 from ..models import DecoderModel
 from ..parts import Runtime
-from ..weights import load_weights
+from ..weights import adopt_tensors, load_weights, random_tensors
 from .step import StepRuntime
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -42,14 +40,14 @@ class PendingTokens:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
-                 max_context: int = None, cuda_graphs: bool = True, decode_stack: bool = None, _random=None):
+                 max_context: int = None, cuda_graphs: bool = True, profile: bool = False, _random=None):
         """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
         `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
         `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
-        request (default: the model's max_position_embeddings); `decode_stack`: run decode steps of
-        up to 16 tokens through the persistent kernel over all layers when the model's parts allow it
-        (csrc/decode_stack.cu).  Off unless asked for (here, or with the environment variable
-        LIA_DECODE_STACK=1): on a B200 the part-by-part kernels under a CUDA graph are some 8% faster;
+        request (default: the model's max_position_embeddings);
+        `profile`: time every kernel class with CUDA events (`profile_summary()`); steps then run launch by launch,
+        never as graphs (the reference's LIA_PROFILE likewise: src/inference/huggingface/minicpm5.rs:14-17).  It can
+        be switched at any time by setting `engine.profile`;
         `cuda_graphs`: capture steps (decoded tokens, prompt portions, both) in CUDA graphs, one per
         shape of a step, when a shape comes a second time, and replay them."""
         if dtype not in _DTYPES:
@@ -66,7 +64,8 @@ class Engine:
         self.device = self.runtime.device
         torch.cuda.set_device(self.device)
         if _random:
-            tensors = self._random_tensors(_random[1])
+            std = float(getattr(self.config, "initializer_range", 0.02))
+            tensors = adopt_tensors(random_tensors(self.spec.tensor_specs(), _random[1], std), self.spec.tensor_specs())
         else:
             tensors = load_weights(model_dir, self.spec.tensor_specs())
         self.model = DecoderModel(self.spec, tensors, self.runtime)
@@ -83,33 +82,19 @@ class Engine:
                                   self.device)
         self.runtime_step = StepRuntime(self.cache, self.spec.vocab_size, self.max_batch_tokens, self.device)
         self.stats = {"steps": 0, "tokens": 0, "kernels": 0, "graph_replays": 0}
-        if decode_stack is None:
-            decode_stack = os.environ.get("LIA_DECODE_STACK", "0") == "1"
-        self.model.use_decode_stack = bool(decode_stack)
         self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
+        self.profile = bool(profile)
+        self.profiler = ops.Profiler()
         # (tokens, wanted, context bucket, tokens of each entry) -> None (seen once) | (graph, logits, kernels, generation),
         # least recently used first
         self._graphs = {}
 
     @classmethod
     def random(cls, config, seed: int = 0, **options) -> "Engine":
-        """An engine whose weights are drawn on the device from `seed` (N(0, initializer_range),
-        norm weights 1), without writing a folder: for benchmarks of sizes that would take long to
-        write.  `weights.write_random_model` is the mode that writes a folder."""
+        """An engine with the weights that `weights.write_random_model(config, folder, seed)` would write (the
+        same generator, the same values, through the loader's checks), without the folder: for sizes whose
+        file would take long to write and read back."""
         return cls(None, _random=(config, seed), **options)
-
-    def _random_tensors(self, seed: int) -> dict:
-        generator = torch.Generator(device=self.device)
-        generator.manual_seed(int(seed))
-        std = float(getattr(self.config, "initializer_range", 0.02))
-        out = {}
-        for spec in self.spec.tensor_specs():
-            if spec.kind == "norm":
-                out[spec.name] = torch.ones(spec.shape, dtype=torch.bfloat16, device=self.device)
-            else:
-                out[spec.name] = (torch.randn(spec.shape, generator=generator, device=self.device,
-                                              dtype=torch.float32) * std).to(torch.bfloat16)
-        return out
 
     # ---- requests and pages (thin faces of the cache manager) ----
     def admit(self) -> int:
@@ -133,7 +118,13 @@ class Engine:
             return self.runtime_step.logits(0, self.spec.vocab_size)
         with torch.cuda.device(self.device):
             ctx = self.runtime_step.begin(entries, feed=None if feed is None else feed.device_tokens)
-            if self.cuda_graphs:
+            if self.profile:
+                ops.set_profiler(self.profiler)
+                try:
+                    logits = self._launch(ctx)
+                finally:
+                    ops.set_profiler(None)
+            elif self.cuda_graphs:
                 logits = self._replay(ctx)
             else:
                 logits = self._launch(ctx)
@@ -243,6 +234,13 @@ class Engine:
         rows = logits.float().cpu().numpy()
         self._raise_device_errors()
         return rows
+
+    def profile_summary(self) -> dict:
+        """kernel class -> {calls, ms, bytes, flops} of the steps run with `profile` on since the last call.
+        Classes are the library's kernels, products further told apart by what they are to the layer
+        ("gemm_skinny:qkv"); bytes and flops are what a roofline counts (every operand once; for attention
+        the cache of the single-token rows, or the flops of the prompt portions)."""
+        return self.profiler.summary()
 
     def synchronize(self) -> None:
         """Wait for the device and raise if a kernel flagged an error."""

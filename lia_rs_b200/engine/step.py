@@ -10,8 +10,8 @@ twice in a step, every token id is in the vocabulary, pages exist for every row.
 
 `StepRuntime` owns what a step needs besides the model: the cache manager, the staging of the
 step's metadata (host pinned -> device, one copy), the workspace that parts take their buffers
-from, the device error flag, and the choice of attention kernel.  `StepContext` is the view of
-one step that the parts see.
+from, and the device error flag.  `StepContext` is the view of one step that the parts see.  Which
+attention kernel serves which rows is the mixer's side (parts/paged_attention.py).
 """
 from __future__ import annotations
 
@@ -70,14 +70,16 @@ class StepContext:
         return self.runtime.cache.state(state_id)
 
     def attention(self, q, kv, out, nq, nkv, d, window, scale):
-        """out = causal attention of q over the cache `kv`, for the tokens of this step."""
-        self.runtime.attention(self, q, kv, out, nq, nkv, d, window, scale)
-
-    def attention_with_rotary(self, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq) -> bool:
-        """For a step of single decoded tokens: rotary encoding of q and k (rotary_dim 0: none), append of
-        k and v to `kv`, and attention, in one kernel.  Returns False, having done nothing, when the step
-        or the sizes are not the ones that kernel takes; the caller then encodes and attends separately."""
-        return self.runtime.attention_with_rotary(self, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq)
+        """out = causal softmax attention of the encoded queries q over the cache `kv`, for the tokens of this
+        step: a convenience for a mixer that keeps no `parts.PagedAttention` of its own (one is built, and its
+        kernels chosen, the first time these sizes are asked for; a head size that no kernel takes raises
+        ValueError with the kernels' limits)."""
+        from ..parts.paged_attention import PagedAttention
+        key = (q.dtype, nq, nkv, d, window, float(scale))
+        attention = self.runtime._attentions.get(key)
+        if attention is None:
+            attention = self.runtime._attentions[key] = PagedAttention(q.dtype, nq, nkv, d, window, scale)
+        attention.forward(self, q, kv, out)
 
 
 class StepRuntime:
@@ -95,6 +97,7 @@ class StepRuntime:
         self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._copy_event = torch.cuda.Event()
         self._buffers = {}
+        self._attentions = {}
         self._logits_buffer = None
         self.generation = 0            # grows whenever a buffer is (re)allocated: captured graphs are stale then
 
@@ -126,16 +129,6 @@ class StepRuntime:
             self._buffers["counters"] = buf
             self.generation += 1
         return buf[:count]
-
-    def stack_barrier(self):
-        """Two 64-bit words of grid-barrier state for the persistent decode kernel: zero at first, kept
-        consistent by every launch that ends well, zeroed again after a device error."""
-        buf = self._buffers.get("stack.barrier")
-        if buf is None:
-            buf = torch.zeros(2, dtype=torch.int64, device=self.device)
-            self._buffers["stack.barrier"] = buf
-            self.generation += 1
-        return buf
 
     def logits(self, rows, vocab):
         buf = self._logits_buffer
@@ -227,66 +220,9 @@ class StepRuntime:
         if code:
             self._error_host[0] = 0
             self.error_flag.zero_()
-            for name in ("stack.barrier", "counters"):       # a kernel that gave up may have left these mid-count
-                if name in self._buffers:
-                    self._buffers[name].zero_()
+            if "counters" in self._buffers:                  # a kernel that gave up may have left these mid-count
+                self._buffers["counters"].zero_()
+            ops.reset_scratch(self.device)                   # and the split-K tile counters of the products
             raise StepError({1: "a token id outside the vocabulary reached the embedding kernel",
                              2: "a token's block table entry has no page",
                              3: "a kernel gave up waiting on an mbarrier"}.get(code, f"device error {code}"))
-
-    # ---- attention ----
-    def attention(self, ctx, q, kv, out, nq, nkv, d, window, scale):
-        """With a bfloat16 cache and a head size the tensor-core kernels are built for, single decoded
-        tokens go to the split-key kernel and prompt portions to the prefill kernel; everything else
-        goes to the kernel for every size."""
-        if not (q.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS):
-            ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
-                                  nq, nkv, d, window, scale)
-            return
-        if ctx.decode_rows.numel():
-            n_splits = self.decode_splits(ctx.decode_rows.numel(), nq, nkv, ctx.context_bucket)
-            partial = counters = None
-            if n_splits > 1:
-                partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
-                counters = self.counters(ctx.decode_rows.numel() * nkv * ((nq // nkv + 15) // 16))
-            ops.attention_decode(q, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots,
-                                 kv.block_table, out, partial, nq, nkv, d, window, scale, 0, n_splits, counters)
-        if ctx.n_prefill_segments:
-            # prompt portions: the tcgen05 kernel where it takes the head size and group, else the mma.sync kernel,
-            # else (groups above 64) the kernel for every size
-            per_tile_tc = ops.attention_prefill_tc_tokens_per_tile(nq // nkv, d)
-            per_tile = per_tile_tc or ops.attention_prefill_tokens_per_tile(nq // nkv)
-            if per_tile:
-                tiles = sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1)
-                kernel = ops.attention_prefill_tc if per_tile_tc else ops.attention_prefill
-                extra = (ctx.error_flag,) if per_tile_tc else ()
-                kernel(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles, ctx.slots,
-                       kv.block_table, out, nq, nkv, d, window, scale, *extra)
-            else:
-                ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out,
-                                      nq, nkv, d, window, scale, rows=ctx.prefill_rows)
-
-    def attention_with_rotary(self, ctx, qkv, kv, out, nq, nkv, d, window, scale, rotary_dim, inv_freq) -> bool:
-        if not (ctx.decode_only and out.dtype == torch.bfloat16 and kv.k_pages.dtype == torch.bfloat16
-                and d in ops.DECODE_HEAD_DIMS and nq // nkv <= 16):
-            return False
-        n_splits = self.decode_splits(ctx.n_tokens, nq, nkv, ctx.context_bucket)
-        partial = counters = None
-        if n_splits > 1:
-            partial = self.scratch("attn.partial", ctx.n_tokens * nq * n_splits * (d + 1), torch.float32)
-            counters = self.counters(ctx.n_tokens * nkv)
-        ops.attention_decode(None, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table,
-                             out, partial, nq, nkv, d, window, scale, 0, n_splits, counters, qkv=qkv,
-                             inv_freq=inv_freq, rotary_dim=rotary_dim, write_kv=kv.writes, error_flag=ctx.error_flag)
-        return True
-
-    def decode_splits(self, rows, nq, nkv, context_bucket):
-        """Into how many ranges the decode attention cuts each token's keys: as many as fill the two
-        CTAs that an SM holds, in one round; no more than 32 (the last CTA of a token reads them all)
-        and none shorter than 256 keys at the step's longest context.  It depends on the number of
-        decoded tokens and on the context bucket alone (each token then cuts its own span, on the
-        device), so a captured step serves every step of its shape and bucket."""
-        groups = nkv * ((nq // nkv + 15) // 16)
-        ctas = max(1, rows * groups)
-        wanted = (2 * self.sm_count) // ctas
-        return max(1, min(wanted, 32, context_bucket // 256))

@@ -42,7 +42,8 @@ def sources() -> list:
 
 def _digest() -> str:
     h = hashlib.sha256()
-    for path in sources() + sorted(glob.glob(os.path.join(CSRC_DIR, "*.cuh"))):
+    headers = sorted(glob.glob(os.path.join(CSRC_DIR, "*.cuh")) + glob.glob(os.path.join(CSRC_DIR, "*.h")))
+    for path in sources() + headers:
         h.update(os.path.basename(path).encode())
         with open(path, "rb") as f:
             h.update(f.read())

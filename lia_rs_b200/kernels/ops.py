@@ -45,7 +45,10 @@ class _Signatures:
     lia_gemm_simt = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
                      c_int, c_int, c_float, c_void_p]
     lia_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+    lia_gather_rows = [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,
+                       ctypes.c_longlong, c_void_p]
+    lia_wait_probe = [c_int, c_void_p, c_void_p, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -54,21 +57,12 @@ class _Signatures:
     lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_int, c_void_p, c_void_p]
     lia_gemm_cluster_splits = [c_int, c_int, c_int, c_int, c_int]
-    lia_gemm_pair = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                     c_int, c_void_p, c_void_p]
-    lia_gemm_pair_accepts = [c_int, c_int, c_int, c_int, c_int]
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
-    lia_decode_stack_set_layer = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
-    lia_decode_stack_accepts = [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]
-    lia_decode_stack = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float,
-                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                        c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p]
@@ -122,11 +116,87 @@ def _check(code: int, what: str):
         raise KernelError(f"{what}: {_ERRORS.get(code, code)}")
 
 
+class Profiler:
+    """Device time per kernel class, from CUDA events around every launch of this library while it is
+    installed (`set_profiler`).  The reference's counterpart is LIA_PROFILE: a synchronisation and a host timer
+    around every product, name, shape and seconds printed (src/inference/operations.rs:85-90,303-310); like it,
+    this cannot run under a captured graph.  Events between launches also keep a kernel from starting under its
+    predecessor's tail, so the times are those of a launch-by-launch step: read them as shares."""
+
+    def __init__(self):
+        self.records = []                        # (class, start event, end event, bytes, flops)
+
+    def summary(self) -> dict:
+        """class -> {calls, ms, bytes, flops} over what was recorded since the last call; waits for the device."""
+        torch.cuda.synchronize()
+        out = {}
+        for key, start, end, nbytes, flops in self.records:
+            entry = out.setdefault(key, {"calls": 0, "ms": 0.0, "bytes": 0, "flops": 0})
+            entry["calls"] += 1
+            entry["ms"] += start.elapsed_time(end)
+            entry["bytes"] += int(nbytes)
+            entry["flops"] += int(flops)
+        self.records = []
+        return out
+
+
+class _Timed:
+    __slots__ = ("key", "nbytes", "flops", "start")
+
+    def __init__(self, key, nbytes, flops):
+        self.key, self.nbytes, self.flops = key, nbytes, flops
+
+    def __enter__(self):
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+
+    def __exit__(self, *exc):
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        if _profiler is not None:
+            _profiler.records.append((self.key, self.start, end, self.nbytes, self.flops))
+        return False
+
+
+class _NotTimed:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_profiler = None
+_NOT_TIMED = _NotTimed()
+
+
+def set_profiler(profiler) -> None:
+    """Install (or, with None, remove) the profiler that every launch of this library reports to."""
+    global _profiler
+    _profiler = profiler
+
+
+def _timed(kernel: str, label=None, nbytes=0, flops=0, work=None):
+    """`work`: a function giving (bytes, flops), asked only while a profiler listens."""
+    if _profiler is None:
+        return _NOT_TIMED
+    if work is not None:
+        nbytes, flops = work()
+    return _Timed(f"{kernel}:{label}" if label else kernel, nbytes, flops)
+
+
+def _gemm_work(a, w, out):
+    """(bytes, flops) of a product as the roofline counts them: every operand once."""
+    return (a.numel() * a.element_size() + w.numel() * w.element_size() + out.numel() * out.element_size(),
+            2 * a.shape[0] * w.shape[0] * a.shape[1])
+
+
 def embedding(tokens, table, out, scale: float, error_flag=None):
     _cuda(tokens, table, out, error_flag)
     n, hidden = out.shape
-    _check(lib().lia_embedding(_p(tokens), _p(table), dtype_code(table.dtype), _p(out), n, hidden,
-                               table.shape[0], scale, _p(error_flag), _stream()), "embedding")
+    with _timed("embedding"):
+        _check(lib().lia_embedding(_p(tokens), _p(table), dtype_code(table.dtype), _p(out), n, hidden,
+                                   table.shape[0], scale, _p(error_flag), _stream()), "embedding")
 
 
 def rmsnorm(x, weight, out, eps: float, out_scale: float = 1.0, rows_index=None):
@@ -134,8 +204,9 @@ def rmsnorm(x, weight, out, eps: float, out_scale: float = 1.0, rows_index=None)
     rows, hidden = out.shape
     if x.dtype != torch.float32 or x.shape[1] != hidden:
         raise KernelError("rmsnorm takes 32-bit rows of the same width as its output")
-    _check(lib().lia_rmsnorm(_p(x), _p(rows_index), _p(weight), dtype_code(weight.dtype), _p(out),
-                             dtype_code(out.dtype), rows, hidden, eps, out_scale, _stream()), "rmsnorm")
+    with _timed("rmsnorm"):
+        _check(lib().lia_rmsnorm(_p(x), _p(rows_index), _p(weight), dtype_code(weight.dtype), _p(out),
+                                 dtype_code(out.dtype), rows, hidden, eps, out_scale, _stream()), "rmsnorm")
 
 
 def rope_kv_write(qkv, positions, slots, block_table, q_out, k_pages, v_pages, nq, nkv, d, rotary_dim,
@@ -147,13 +218,43 @@ def rope_kv_write(qkv, positions, slots, block_table, q_out, k_pages, v_pages, n
     if q_out.dtype != k_pages.dtype or k_pages.dtype != v_pages.dtype:
         raise KernelError("rope_kv_write: q and the cache must have one element type")
     num_pages, page_size = k_pages.shape[0], k_pages.shape[1]
-    _check(lib().lia_rope_kv_write(_p(qkv), _p(positions), _p(slots), _p(block_table), block_table.shape[1],
-                                   _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), n, nq, nkv, d,
-                                   rotary_dim, _p(inv_freq), page_size, num_pages, 1 if write_kv else 0,
-                                   _p(error_flag), _stream()), "rope_kv_write")
+    with _timed("rope_kv_write"):
+        _check(lib().lia_rope_kv_write(_p(qkv), _p(positions), _p(slots), _p(block_table), block_table.shape[1],
+                                       _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), n, nq, nkv, d,
+                                       rotary_dim, _p(inv_freq), page_size, num_pages, 1 if write_kv else 0,
+                                       _p(error_flag), _stream()), "rope_kv_write")
 
 
-def gemm_simt(mode, a, w, out, alpha: float = 1.0):
+def gather_rows(src, index, dst):
+    """dst[r] = src[index[r]] for 2-D tensors of one element type and width (rows copied as they are; a negative
+    index gives zeros); see csrc/elementwise.cu."""
+    _cuda(index)
+    if not (src.is_cuda and dst.is_cuda) or src.dim() != 2 or dst.dim() != 2 or src.dtype != dst.dtype \
+            or src.shape[1] != dst.shape[1] or src.stride(1) != 1 or dst.stride(1) != 1 or index.dtype != torch.int32 \
+            or index.numel() < dst.shape[0]:
+        raise KernelError("gather_rows: 2-D CUDA tensors of one type and width, int32 index of at least dst's rows")
+    size = src.element_size()
+    with _timed("gather_rows"):
+        _check(lib().lia_gather_rows(_p(src), _p(index), _p(dst), dst.shape[0], src.shape[0], src.stride(0) * size,
+                                     dst.stride(0) * size, src.shape[1] * size, _stream()), "gather_rows")
+
+
+def wait_probe(polls: int, error_flag, gave_up=None):
+    """One thread waits on an mbarrier that nobody arrives at, gives up after `polls` polls (at most 65,536) and
+    raises error flag 3, exactly as the tensor-core kernels' bounded waits do; see csrc/library.cu."""
+    _cuda(error_flag, gave_up)
+    _check(lib().lia_wait_probe(int(polls), _p(error_flag), _p(gave_up), _stream()), "wait_probe")
+
+
+def reset_scratch(device) -> None:
+    """Zero the counters at the head of this device's split-K scratch: a product that gave up may have left
+    them mid-count (every product that runs to its end leaves them at zero)."""
+    key = torch.device(device).index or 0
+    if key in _scratch:
+        _scratch[key][:COUNTER_WORDS].zero_()
+
+
+def gemm_simt(mode, a, w, out, alpha: float = 1.0, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the 32-bit pipes; see csrc/gemm_simt.cu."""
     _cuda(a, w, out)
     M, K = a.shape
@@ -161,12 +262,14 @@ def gemm_simt(mode, a, w, out, alpha: float = 1.0):
     rows_w = w.shape[0]
     if w.shape[1] != K or out.shape[0] != M or rows_w != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    _check(lib().lia_gemm_simt(mode, _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
-                               w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0), M, N, K, alpha,
-                               _stream()), "gemm_simt")
+    with _timed("gemm_simt", label, work=lambda: _gemm_work(a, w, out)):
+        _check(lib().lia_gemm_simt(mode, _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
+                                   w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0), M, N, K, alpha,
+                                   _stream()), "gemm_simt")
 
 
 _SCRATCH_FLOATS = 16 << 20          # 64 MB of split-K scratch per device, allocated (zeroed) at first use
+COUNTER_WORDS = 4096                # its first words are the split-K tile counters (csrc/gemm_tc.cu)
 _scratch = {}
 _sm_count = {}
 
@@ -198,7 +301,7 @@ def gemm_tc_tiles_fill_the_sms(a, out) -> bool:
     return 4 * ((out.shape[1] + 127) // 128) >= 3 * sms
 
 
-def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores; see csrc/gemm_tc.cu.  Products
     with few tiles split K and use this device's scratch, so calls on one device must not overlap."""
     M, K = a.shape
@@ -206,9 +309,10 @@ def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None):
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     scratch, sms = _device_scratch(a.device)
-    _check(lib().lia_gemm_tc(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
-                             out.stride(0), M, N, K, alpha, _p(scratch), scratch.numel(), sms, _p(error_flag),
-                             _stream()), "gemm_tc")
+    with _timed("gemm_tc", label, work=lambda: _gemm_work(a, w, out)):
+        _check(lib().lia_gemm_tc(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                                 out.stride(0), M, N, K, alpha, _p(scratch), scratch.numel(), sms, _p(error_flag),
+                                 _stream()), "gemm_tc")
 
 
 def gemm_cluster_accepts(mode, a, w, out) -> bool:
@@ -220,7 +324,7 @@ def gemm_cluster_accepts(mode, a, w, out) -> bool:
     return lib().lia_gemm_cluster_splits(mode, a.shape[0], out.shape[1], a.shape[1], sms) >= 2
 
 
-def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores with K cut over the CTAs of a
     thread-block cluster, partial sums meeting in distributed shared memory; see csrc/gemm_cluster.cu."""
     M, K = a.shape
@@ -228,31 +332,9 @@ def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None):
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _, sms = _device_scratch(a.device)
-    _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
-                                  out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
-
-
-def gemm_pair_accepts(mode, a, w, out) -> bool:
-    """Whether the two-CTA tcgen05 kernel takes this product: what the tcgen05 kernel takes, many tokens,
-    and an output that TMA can address (16-byte aligned base and rows)."""
-    if not gemm_tc_accepts(mode, a, w, out) or out.stride(1) != 1:
-        return False
-    if out.data_ptr() % 16 or (out.stride(0) * out.element_size()) % 16:
-        return False
-    _, sms = _device_scratch(a.device)
-    return bool(lib().lia_gemm_pair_accepts(mode, a.shape[0], out.shape[1], a.shape[1], sms))
-
-
-def gemm_pair(mode, a, w, out, alpha: float = 1.0, error_flag=None):
-    """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on pairs of SMs (tcgen05 with cta_group::2); see
-    csrc/gemm_pair.cu."""
-    M, K = a.shape
-    N = out.shape[1]
-    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
-        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    _, sms = _device_scratch(a.device)
-    _check(lib().lia_gemm_pair(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
-                               out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_pair")
+    with _timed("gemm_cluster", label, work=lambda: _gemm_work(a, w, out)):
+        _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                                      out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
 
 
 SKINNY_MAX_TOKENS = 32
@@ -268,28 +350,36 @@ def gemm_skinny_accepts(mode, a, w, out) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None):
+def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T for M <= 32 tokens: each CTA streams 16 rows of w over
     the whole of K; see csrc/gemm_skinny.cu."""
     M, K = a.shape
     N = out.shape[1]
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
-                                 out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
+    with _timed("gemm_skinny", label, work=lambda: _gemm_work(a, w, out)):
+        _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+                                     out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
+
+
+ATTENTION_HEAD_DIM_STEP, ATTENTION_HEAD_DIM_MAX = 16, 256      # what csrc/attention_generic.cu takes
 
 
 def attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, window, scale,
-                      rows=None):
-    """Attention for every token of the batch, or for the tokens whose batch indices `rows` lists."""
-    _cuda(q, k_pages, v_pages, positions, slots, block_table, out, rows)
+                      rows=None, error_flag=None, label=None, work_bytes=0):
+    """Attention for every token of the batch, or for the tokens whose batch indices `rows` lists (row t of
+    `out` is written for token t either way).  A visible key whose block-table entry names no page counts
+    for nothing and raises error flag 2."""
+    _cuda(q, k_pages, v_pages, positions, slots, block_table, out, rows, error_flag)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
         raise KernelError("attention: q, cache and out must have one element type")
     n = q.shape[0] if rows is None else rows.shape[0]
-    _check(lib().lia_attention_generic(_p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(positions),
-                                       _p(slots), _p(block_table), block_table.shape[1], _p(rows), _p(out), n, nq,
-                                       nkv, d, k_pages.shape[1], int(window or 0), scale, _stream()),
-           "attention_generic")
+    with _timed("attention_generic", label, work_bytes):
+        _check(lib().lia_attention_generic(_p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(positions),
+                                           _p(slots), _p(block_table), block_table.shape[1], _p(rows), _p(out), n, nq,
+                                           nkv, d, k_pages.shape[1], int(window or 0), scale, k_pages.shape[0],
+                                           _p(error_flag), _stream()),
+               "attention_generic")
 
 
 DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention kernels are built for
@@ -297,7 +387,7 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
-                     error_flag=None):
+                     error_flag=None, label=None, work_bytes=0):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
@@ -317,12 +407,13 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
         raise KernelError("attention_decode: counters must be int32, one per row and head group")
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_decode is a bfloat16 kernel")
-    _check(lib().lia_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(rows), rows.shape[0], _p(positions),
-                                      _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
-                                      0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
-                                      k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
-                                      int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], _p(error_flag), _stream()),
-           "attention_decode")
+    with _timed("attention_decode", label, work_bytes):
+        _check(lib().lia_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(rows), rows.shape[0], _p(positions),
+                                          _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
+                                          0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
+                                          k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
+                                          int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], _p(error_flag), _stream()),
+               "attention_decode")
 
 
 def attention_prefill_tokens_per_tile(group: int) -> int:
@@ -331,15 +422,17 @@ def attention_prefill_tokens_per_tile(group: int) -> int:
 
 
 def attention_prefill(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                      window, scale):
+                      window, scale, error_flag=None, label=None, work_flops=0):
     """Tensor-core attention (bfloat16) for the prompt portions listed in `segments`
     ([n_segments, 3] int32: first batch index, first position, count); see csrc/attention_prefill.cu."""
-    _cuda(q, k_pages, v_pages, segments, slots, block_table, out)
+    _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_prefill is a bfloat16 kernel")
-    _check(lib().lia_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
-                                       _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
-                                       k_pages.shape[1], int(window or 0), scale, _stream()), "attention_prefill")
+    with _timed("attention_prefill", label, 0, work_flops):
+        _check(lib().lia_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
+                                           _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
+                                           k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], _p(error_flag),
+                                           _stream()), "attention_prefill")
 
 
 def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
@@ -349,16 +442,18 @@ def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                         window, scale, error_flag=None):
+                         window, scale, error_flag=None, label=None, work_flops=0):
     """Prompt-portion attention on the tcgen05 tensor cores (bfloat16, head size 64 or 128, heads per kv head a
     divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`."""
     _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_prefill_tc is a bfloat16 kernel")
-    _check(lib().lia_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
-                                          _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
-                                          k_pages.shape[1], int(window or 0), scale, _p(error_flag), _stream()),
-           "attention_prefill_tc")
+    with _timed("attention_prefill_tc", label, 0, work_flops):
+        _check(lib().lia_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
+                                              _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
+                                              k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], _p(error_flag),
+                                              _stream()),
+               "attention_prefill_tc")
 
 
 _select_scratch = {}
@@ -379,8 +474,9 @@ def select_tokens(logits, out, temperature=None, seeds=None, positions=None):
     if scratch is None or scratch.numel() < need:
         # zeroed: its head holds the rows' counters, which every call leaves at zero
         scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
-    _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
-                                   _p(positions), _p(out), rows, _p(scratch), scratch.numel(), _stream()), "select_tokens")
+    with _timed("select_tokens"):
+        _check(lib().lia_select_tokens(_p(logits), logits.stride(0), vocab, _p(temperature), _p(seeds),
+                                       _p(positions), _p(out), rows, _p(scratch), scratch.numel(), _stream()), "select_tokens")
 
 
 CANDIDATES_MAX = 32
@@ -412,49 +508,7 @@ def select_candidates(logits, k: int, out_values, out_ids, nonfinite, temperatur
     scratch = _select_scratch.get(key)
     if scratch is None or scratch.numel() < need:
         scratch = _select_scratch[key] = torch.zeros(max(need, 1 << 18), dtype=torch.float32, device=logits.device)
-    _check(lib().lia_select_candidates(_p(logits), logits.stride(0), vocab, rows, k, _p(out_values), _p(out_ids),
-                                       _p(nonfinite), _p(temperature), _p(mass), _p(scratch), scratch.numel(),
-                                       _stream()), "select_candidates")
-
-
-def decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits) -> bool:
-    """Whether the persistent decode kernel (csrc/decode_stack.cu) takes these sizes."""
-    return bool(lib().lia_decode_stack_accepts(tokens, hidden, nq, nkv, d, intermediate, rotary_dim, n_splits))
-
-
-def decode_stack_layers(records, device) -> torch.Tensor:
-    """The device array of per-layer records for `decode_stack`.  Each record is a dict with the tensors
-    norm1, norm2, wqkv, wo, wgu, wd, k_pages, v_pages, block_table and the numbers window, writes."""
-    fn = lib().lia_decode_stack_layer_bytes
-    fn.restype, fn.argtypes = c_int, []
-    size = int(fn())
-    host = (ctypes.c_ubyte * (size * len(records)))()
-    for index, r in enumerate(records):
-        _cuda(r["norm1"], r["norm2"], r["wqkv"], r["wo"], r["wgu"], r["wd"], r["k_pages"], r["v_pages"], r["block_table"])
-        if r["norm1"].dtype != r["norm2"].dtype or r["norm1"].dtype not in (torch.float32, torch.bfloat16):
-            raise KernelError("decode_stack: norm weights must both be bfloat16 or both 32-bit")
-        _check(lib().lia_decode_stack_set_layer(
-            ctypes.addressof(host), index, _p(r["norm1"]), _p(r["norm2"]), 1 if r["norm1"].dtype == torch.float32 else 0,
-            _p(r["wqkv"]), _p(r["wo"]), _p(r["wgu"]), _p(r["wd"]), _p(r["k_pages"]), _p(r["v_pages"]),
-            _p(r["block_table"]), r["block_table"].shape[1], r["k_pages"].shape[1], r["k_pages"].shape[0],
-            int(r["window"] or 0), 1 if r["writes"] else 0), "decode_stack_set_layer")
-    return torch.frombuffer(bytearray(host), dtype=torch.uint8).to(device)
-
-
-def decode_stack(layers, n_layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, nq, nkv, d,
-                 intermediate, rotary_dim, inv_freq, eps, residual_scale, attn_scale, n_splits, grid, error_flag=None,
-                 timeline=None):
-    """All `n_layers` pre-norm layers of a decode step in one persistent cooperative kernel; see
-    csrc/decode_stack.cu.  `h` [tokens, hidden] 32-bit is the residual stream, updated in place."""
-    _cuda(layers, h, qkv, attn, act, partial, counters, positions, slots, barrier, inv_freq, error_flag)
-    tokens, hidden = h.shape
-    if h.dtype != torch.float32 or qkv.dtype != torch.float32 or attn.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
-        raise KernelError("decode_stack: 32-bit residual and q|k|v, bfloat16 attention output and activation")
-    if (qkv.shape != (tokens, (nq + 2 * nkv) * d) or attn.shape != (tokens, nq * d) or act.shape != (tokens, intermediate)
-            or partial.numel() < tokens * nq * n_splits * (d + 1) or counters.numel() < tokens * nkv
-            or barrier.numel() < 2 or barrier.dtype != torch.int64 or counters.dtype != torch.int32):
-        raise KernelError("decode_stack: a scratch buffer has the wrong shape or type")
-    _check(lib().lia_decode_stack(_p(layers), n_layers, tokens, hidden, nq, nkv, d, intermediate, rotary_dim,
-                                  _p(inv_freq), eps, residual_scale, attn_scale, _p(h), _p(qkv), _p(attn), _p(act),
-                                  _p(partial), n_splits, _p(counters), _p(positions), _p(slots), _p(barrier),
-                                  _p(error_flag), _p(timeline), grid, _stream()), "decode_stack")
+    with _timed("select_candidates"):
+        _check(lib().lia_select_candidates(_p(logits), logits.stride(0), vocab, rows, k, _p(out_values), _p(out_ids),
+                                           _p(nonfinite), _p(temperature), _p(mass), _p(scratch), scratch.numel(),
+                                           _stream()), "select_candidates")

@@ -18,11 +18,19 @@ import torch
 from ..weights import TensorSpec
 from .base import KVCacheRequest, Mixer, POSITION_ENCODINGS, lookup, register_mixer
 from .linear import ACCUM, STORE, linear, prepare_weight
+from .paged_attention import PagedAttention
 
 
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
     graph_safe = True
+    supports_rows = True
+
+    @staticmethod
+    def check_params(params):
+        PagedAttention.check(int(params["heads"]), int(params["kv_heads"]), int(params["head_dim"]))
+        position = params["position"]
+        lookup(POSITION_ENCODINGS, position.kind, "position encoding").check_params(position.params)
 
     @staticmethod
     def tensor_specs(params, prefix):
@@ -40,8 +48,6 @@ class GQAttention(Mixer):
         super().__init__(params, tensors, prefix, runtime)
         self.hidden = int(params["hidden"])
         self.nq, self.nkv, self.d = int(params["heads"]), int(params["kv_heads"]), int(params["head_dim"])
-        if self.nq % self.nkv:
-            raise ValueError("heads must be a multiple of kv_heads")
         self.window = params.get("window")
         self.scale = 1.0 / math.sqrt(self.d)
         self.w_qkv = prepare_weight(torch.cat([tensors[prefix + "q_proj.weight"],
@@ -52,24 +58,34 @@ class GQAttention(Mixer):
         self.position = lookup(POSITION_ENCODINGS, position.kind, "position encoding")(
             position.params, tensors, prefix, runtime)
         self.graph_safe = bool(self.position.graph_safe)
+        # the kernels that will serve this attention are chosen here, once; sizes they cannot take are refused here
+        self.attention = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale,
+                                        rotate_half=self.position.rotate_half())
 
-    def stack_record(self):
-        position = self.position.stack_record()
-        if position is None:
-            return None
-        return dict(kind="gqa_attention", wqkv=self.w_qkv, wo=self.w_o, heads=self.nq, kv_heads=self.nkv,
-                    head_dim=self.d, window=self.window, attn_scale=self.scale, **position)
-
-    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+    def forward(self, ctx, x, residual, scale, kv=None, state=None, rows=None, n_rows=None):
+        """`rows` (device int32, `n_rows` of them): only these tokens' outputs are needed.  `residual` then holds
+        those rows alone ([n_rows, hidden]); keys and values of every token are still appended."""
         rt, n = self.runtime, x.shape[0]
         nq, nkv, d = self.nq, self.nkv, self.d
+        flag = ctx.error_flag
         qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * d), torch.float32)
-        linear(rt, STORE, x, self.w_qkv, qkv)
+        linear(rt, STORE, x, self.w_qkv, qkv, error_flag=flag, name="qkv")
         o = ctx.buffer("attn.o", (n, nq * d), rt.compute_dtype)
-        rotary = self.position.stack_record()           # a rotary (or no) encoding can ride in the decode attention kernel
-        if rotary is None or not ctx.attention_with_rotary(qkv, kv, o, nq, nkv, d, self.window, self.scale,
-                                                           rotary["rotary_dim"], rotary["inv_freq"]):
-            q = ctx.buffer("attn.q", (n, nq * d), rt.compute_dtype)
-            self.position.encode_and_store(ctx, qkv, q, kv, nq, nkv, d)
-            ctx.attention(q, kv, o, nq, nkv, d, self.window, self.scale)
-        linear(rt, ACCUM, o, self.w_o, residual, scale)
+        if rows is None:
+            if not self.attention.forward_fused(ctx, qkv, kv, o):
+                q = ctx.buffer("attn.q", (n, nq * d), rt.compute_dtype)
+                self.position.encode_and_store(ctx, qkv, q, kv, nq, nkv, d)
+                self.attention.forward(ctx, q, kv, o)
+            linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+            return
+        q = ctx.buffer("attn.q", (n, nq * d), rt.compute_dtype)
+        self.position.encode_and_store(ctx, qkv, q, kv, nq, nkv, d)       # the cache takes every token
+        if n_rows == 0:
+            return
+        if n_rows * 8 <= n:
+            self.attention.forward(ctx, q, kv, o, rows=rows, n_rows=n_rows)   # few rows: only they attend
+        else:
+            self.attention.forward(ctx, q, kv, o)
+        picked = ctx.buffer("attn.o_rows", (n_rows, nq * d), rt.compute_dtype)
+        rt.ops.gather_rows(o, rows, picked)
+        linear(rt, ACCUM, picked, self.w_o, residual, scale, error_flag=flag, name="o")

@@ -83,11 +83,11 @@ class Part:
         self.params = params
         self.runtime = runtime
 
-    def stack_record(self):
-        """What a fused kernel over a whole stack of layers needs of this part (its kind, its prepared
-        tensors and constants), or None when the part can only be run through `forward`.  A part that
-        does not offer a record simply keeps its layer, and so the model, on the part-by-part path."""
-        return None
+    @staticmethod
+    def check_params(params: dict) -> None:
+        """Raise ValueError for parameters this part (or the kernels behind it) cannot take.  Called when a
+        model's description is put together, before any tensor is read and without a device, so that an
+        unsupported size is refused with its reason at the earliest place."""
 
 
 class Norm(Part):
@@ -102,8 +102,21 @@ class PositionEncoding(Part):
     def encode_and_store(self, ctx, qkv: torch.Tensor, q_out: torch.Tensor, kv, nq: int, nkv: int, d: int):
         raise NotImplementedError
 
+    def rotate_half(self):
+        """`(rotary_dim, inv_freq)` if this encoding is exactly "rotate-half over the first rotary_dim elements
+        of every q and k head by angle position * inv_freq[i]" (rotary_dim 0, inv_freq None: nothing is
+        encoded), else None.  The decode attention kernel can apply such an encoding itself, together with
+        the append to the cache; every other encoding (interleaved pairs, sections, learned tables) answers
+        None and runs its own `encode_and_store` ahead of the attention kernel, at every step."""
+        return None
+
 
 class Mixer(Part):
+    # True: `forward` takes `rows` / `n_rows` (only those tokens' outputs are needed, `residual` holds those rows
+    # alone; cache and state are still updated for every token).  False: the arrangement runs the mixer for every
+    # token and picks the rows afterwards.
+    supports_rows = False
+
     @staticmethod
     def cache_request(params: dict) -> Optional[KVCacheRequest]:
         return None
@@ -137,13 +150,16 @@ class Arrangement:
     def __init__(self, layer_spec, tensors: dict, prefix: str, runtime: Runtime):
         raise NotImplementedError
 
-    def forward(self, ctx, residual: torch.Tensor, kv=None, state=None):
-        raise NotImplementedError
+    # True: `forward` takes `rows` / `n_rows` and then returns the residual rows of those tokens alone.
+    supports_rows = False
 
-    def stack_record(self):
-        """The layer as one record for a fused kernel over a stack of layers (see `Part.stack_record`),
-        or None."""
-        return None
+    def forward(self, ctx, residual: torch.Tensor, kv=None, state=None, rows=None, n_rows=None):
+        """Run the layer on the residual stream in place.  With `rows` (device int32 batch indices, `n_rows` of
+        them; only an arrangement that says `supports_rows` is given them) nothing after this layer needs the
+        other tokens: the layer still brings cache and state up to date for every token, but may compute the
+        rest for these rows only, and returns their residual rows [n_rows, hidden] in the order of `rows`.
+        Without `rows` it returns None."""
+        raise NotImplementedError
 
 
 MIXERS: dict = {}

@@ -14,56 +14,90 @@ from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Arrangement, Part
 
 @dataclass(frozen=True)
 class LayerSpec:
+    """`norm` is the norm at every place of the arrangement; `norms` names other norms for single places
+    (for the pre-norm arrangement the places are "norm1" and "norm2")."""
     mixer: PartSpec
     feed_forward: PartSpec
     norm: PartSpec
     arrangement: str = "prenorm"
     residual_scale: float = 1.0
+    norms: dict = field(default_factory=dict, hash=False, compare=False)
     names: dict = field(default_factory=lambda: {"norm1": "input_layernorm.", "mixer": "self_attn.",
                                                  "norm2": "post_attention_layernorm.", "feed_forward": "mlp."},
                         hash=False, compare=False)
 
+    def norm_at(self, place: str) -> PartSpec:
+        return self.norms.get(place, self.norm)
+
 
 @register_arrangement("prenorm")
 class PreNormBlock(Arrangement):
+    supports_rows = True
+
+    @staticmethod
+    def _classes(spec: LayerSpec):
+        norm1, norm2 = spec.norm_at("norm1"), spec.norm_at("norm2")
+        return ((lookup(NORMS, norm1.kind, "norm"), norm1.params), (lookup(MIXERS, spec.mixer.kind, "mixer"), spec.mixer.params),
+                (lookup(NORMS, norm2.kind, "norm"), norm2.params),
+                (lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward"), spec.feed_forward.params))
+
+    @staticmethod
+    def check(spec: LayerSpec) -> None:
+        for cls, params in PreNormBlock._classes(spec):
+            cls.check_params(params)
+
     @staticmethod
     def tensor_specs(spec: LayerSpec, prefix: str) -> list:
         n = spec.names
-        return (lookup(NORMS, spec.norm.kind, "norm").tensor_specs(spec.norm.params, prefix + n["norm1"])
-                + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_specs(spec.mixer.params, prefix + n["mixer"])
-                + lookup(NORMS, spec.norm.kind, "norm").tensor_specs(spec.norm.params, prefix + n["norm2"])
-                + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_specs(
-                    spec.feed_forward.params, prefix + n["feed_forward"]))
+        places = (n["norm1"], n["mixer"], n["norm2"], n["feed_forward"])
+        return [t for (cls, params), place in zip(PreNormBlock._classes(spec), places)
+                for t in cls.tensor_specs(params, prefix + place)]
 
     def __init__(self, spec: LayerSpec, tensors: dict, prefix: str, runtime):
         n = spec.names
         self.runtime = runtime
         self.scale = float(spec.residual_scale)
-        self.norm1 = lookup(NORMS, spec.norm.kind, "norm")(spec.norm.params, tensors, prefix + n["norm1"], runtime)
-        self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer.params, tensors, prefix + n["mixer"], runtime)
-        self.norm2 = lookup(NORMS, spec.norm.kind, "norm")(spec.norm.params, tensors, prefix + n["norm2"], runtime)
-        self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
-            spec.feed_forward.params, tensors, prefix + n["feed_forward"], runtime)
+        places = (n["norm1"], n["mixer"], n["norm2"], n["feed_forward"])
+        self.norm1, self.mixer, self.norm2, self.feed_forward = (
+            cls(params, tensors, prefix + place, runtime) for (cls, params), place in zip(self._classes(spec), places))
         self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
-    def stack_record(self):
-        parts = [self.norm1.stack_record(), self.mixer.stack_record(), self.norm2.stack_record(),
-                 self.feed_forward.stack_record()]
-        if any(part is None for part in parts):
-            return None
-        return dict(kind="prenorm", norm1=parts[0], mixer=parts[1], norm2=parts[2], feed_forward=parts[3],
-                    residual_scale=self.scale)
-
-    def forward(self, ctx, residual, kv=None, state=None):
+    def forward(self, ctx, residual, kv=None, state=None, rows=None, n_rows=None):
         x = ctx.buffer("block.x", tuple(residual.shape), self.runtime.compute_dtype)
         self.norm1.forward(ctx, residual, x)
-        self.mixer.forward(ctx, x, residual, self.scale, kv=kv, state=state)
-        self.norm2.forward(ctx, residual, x)
-        self.feed_forward.forward(ctx, x, residual, self.scale)
+        if rows is None:
+            self.mixer.forward(ctx, x, residual, self.scale, kv=kv, state=state)
+            self.norm2.forward(ctx, residual, x)
+            self.feed_forward.forward(ctx, x, residual, self.scale)
+            return None
+        # Only `rows` matter after this layer (the reference prunes the last layer the same way:
+        # src/inference/llama_fusion.rs:45-60): the mixer brings the cache up to date for every token; the output
+        # projection, the second norm, the feed-forward and both residual sums run on the picked rows alone.
+        picked = ctx.buffer("block.picked", (n_rows, residual.shape[1]), residual.dtype)
+        if n_rows and self.mixer.supports_rows:
+            self.runtime.ops.gather_rows(residual, rows, picked)
+        if self.mixer.supports_rows:
+            self.mixer.forward(ctx, x, picked, self.scale, kv=kv, state=state, rows=rows, n_rows=n_rows)
+        else:
+            self.mixer.forward(ctx, x, residual, self.scale, kv=kv, state=state)
+            if n_rows:
+                self.runtime.ops.gather_rows(residual, rows, picked)
+        if n_rows:
+            x = x[:n_rows]
+            self.norm2.forward(ctx, picked, x)
+            self.feed_forward.forward(ctx, x, picked, self.scale)
+        return picked
 
 
 def build_layer(spec: LayerSpec, tensors: dict, prefix: str, runtime):
     return lookup(ARRANGEMENTS, spec.arrangement, "arrangement")(spec, tensors, prefix, runtime)
+
+
+def check_layer(spec: LayerSpec) -> None:
+    """Raise ValueError if a part of the layer refuses its parameters (no device needed)."""
+    arrangement = lookup(ARRANGEMENTS, spec.arrangement, "arrangement")
+    if hasattr(arrangement, "check"):
+        arrangement.check(spec)
 
 
 def layer_tensor_specs(spec: LayerSpec, prefix: str) -> list:

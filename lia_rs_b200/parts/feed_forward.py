@@ -30,11 +30,8 @@ class SwiGLU(FeedForward):
                                                    tensors[prefix + "up_proj.weight"]], dim=0), runtime)
         self.w_down = prepare_weight(tensors[prefix + "down_proj.weight"], runtime)
 
-    def stack_record(self):
-        return dict(kind="swiglu", wgu=self.w_gate_up, wd=self.w_down, intermediate=self.intermediate)
-
     def forward(self, ctx, x, residual, scale):
         rt, n = self.runtime, x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
-        linear(rt, SWIGLU, x, self.w_gate_up, act)
-        linear(rt, ACCUM, act, self.w_down, residual, scale)
+        linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
+        linear(rt, ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")

@@ -47,9 +47,13 @@ def _choose(mode, a, w, out) -> int:
     return _SKINNY if few else _SIMT
 
 
-def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0):
+def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
+           error_flag=None, name=None):
+    """`name`: what the product is to its caller ("qkv", "down", ...), for the per-kernel-class profile.
+    `error_flag` (int32[1] on the device, a step's `ctx.error_flag`): a tensor-core kernel that gives up on one
+    of its bounded waits raises it to 3, and the step's caller then learns that the result is not to be used."""
     if a.dtype != torch.bfloat16:
-        ops.gemm_simt(mode, a, w, out, alpha)
+        ops.gemm_simt(mode, a, w, out, alpha, label=name)
         return
     # everything the kernels' acceptance looks at: sizes, row strides, element types, 16-byte alignment of the bases
     key = (mode, a.shape, a.stride(), a.data_ptr() & 15, w.shape, w.stride(), w.dtype, w.data_ptr() & 15,
@@ -58,10 +62,10 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     if choice is None:
         choice = _choices[key] = _choose(mode, a, w, out)
     if choice == _TC:
-        ops.gemm_tc(mode, a, w, out, alpha)
+        ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _SKINNY:
-        ops.gemm_skinny(mode, a, w, out, alpha)
+        ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _CLUSTER:
-        ops.gemm_cluster(mode, a, w, out, alpha)
+        ops.gemm_cluster(mode, a, w, out, alpha, error_flag, label=name)
     else:
-        ops.gemm_simt(mode, a, w, out, alpha)
+        ops.gemm_simt(mode, a, w, out, alpha, label=name)

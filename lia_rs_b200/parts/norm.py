@@ -22,6 +22,3 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, out, rows_index=None, out_scale=1.0):
         self.runtime.ops.rmsnorm(x, self.weight, out, self.eps, out_scale, rows_index)
-
-    def stack_record(self):
-        return dict(kind="rmsnorm", weight=self.weight, eps=self.eps)

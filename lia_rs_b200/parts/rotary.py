@@ -14,18 +14,23 @@ from .base import PositionEncoding, register_position_encoding
 class RotaryEncoding(PositionEncoding):
     graph_safe = True
 
+    @staticmethod
+    def check_params(params):
+        rotary_dim, theta = int(params["rotary_dim"]), float(params["theta"])
+        if rotary_dim % 2 or rotary_dim <= 0 or not theta > 0:
+            raise ValueError("rotary encoding needs an even positive rotary_dim and theta > 0")
+
     def __init__(self, params, tensors, prefix, runtime):
         super().__init__(params, tensors, prefix, runtime)
+        self.check_params(params)
         self.rotary_dim = int(params["rotary_dim"])
         theta = float(params["theta"])
-        if self.rotary_dim % 2 or self.rotary_dim <= 0 or not theta > 0:
-            raise ValueError("rotary encoding needs an even positive rotary_dim and theta > 0")
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         inv = 1.0 / (theta ** (2.0 * i / self.rotary_dim))
         self.inv_freq = inv.to(torch.float32).to(runtime.device)
 
-    def stack_record(self):
-        return dict(rotary_dim=self.rotary_dim, inv_freq=self.inv_freq)
+    def rotate_half(self):
+        return self.rotary_dim, self.inv_freq
 
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d):
         self.runtime.ops.rope_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,
@@ -37,8 +42,8 @@ class RotaryEncoding(PositionEncoding):
 class NoEncoding(PositionEncoding):
     graph_safe = True
 
-    def stack_record(self):
-        return dict(rotary_dim=0, inv_freq=None)
+    def rotate_half(self):
+        return 0, None
 
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d):
         self.runtime.ops.rope_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,

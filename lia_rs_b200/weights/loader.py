@@ -53,23 +53,25 @@ def storage_dtype(dtype: torch.dtype) -> torch.dtype:
     return torch.int32
 
 
-def load_weights(model_dir: str, specs) -> dict:
-    archive = Archive(model_dir)
-    names = set(archive.names())
+def _check_names_and_shapes(shapes: dict, specs) -> dict:
+    """`shapes`: name -> shape of what is on offer.  Raises the one WeightError; returns name -> spec."""
+    names = set(shapes)
     wanted = {s.name: s for s in specs}
     missing = [n for n, s in wanted.items() if n not in names and not s.optional]
     unexpected = sorted(names - set(wanted))
-    wrong = []
-    for name, spec in wanted.items():
-        if name in names and tuple(archive.entry(name).shape) != tuple(spec.shape):
-            wrong.append((name, spec.shape, archive.entry(name).shape))
+    wrong = [(name, spec.shape, tuple(shapes[name])) for name, spec in wanted.items()
+             if name in names and tuple(shapes[name]) != tuple(spec.shape)]
     if missing or unexpected or wrong:
         raise WeightError(sorted(missing), unexpected, wrong)
+    return wanted
+
+
+def _store(read, wanted: dict, names) -> dict:
     out, bad = {}, []
     for name in wanted:
         if name not in names:
             continue
-        t = archive.read(name)
+        t = read(name)
         t = t.to(storage_dtype(t.dtype))
         if t.is_floating_point() and not torch.isfinite(t.float()).all():
             bad.append(f"non-finite values in {name}")
@@ -77,3 +79,17 @@ def load_weights(model_dir: str, specs) -> dict:
     if bad:
         raise WeightError([], [], [], bad)
     return out
+
+
+def load_weights(model_dir: str, specs) -> dict:
+    archive = Archive(model_dir)
+    names = set(archive.names())
+    wanted = _check_names_and_shapes({n: archive.entry(n).shape for n in names}, specs)
+    return _store(archive.read, wanted, names)
+
+
+def adopt_tensors(tensors: dict, specs) -> dict:
+    """The same checks and storage rule for tensors that are already in memory (the random-weights mode
+    without a folder)."""
+    wanted = _check_names_and_shapes({n: t.shape for n, t in tensors.items()}, specs)
+    return _store(tensors.__getitem__, wanted, set(tensors))

@@ -23,3 +23,11 @@ def tiny_models(tmp_path_factory):
     import helpers
     root = tmp_path_factory.mktemp("models")
     return {name: helpers.make_model(str(root / name), name) for name in helpers.TINY}
+
+
+@pytest.fixture(autouse=True)
+def _no_model_carried_over():
+    """The 32-bit tolerance follows the model that the test last asked the plain implementation about."""
+    import helpers
+    helpers._LAST_MODEL["longest_sum"] = None
+    yield

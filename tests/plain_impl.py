@@ -80,23 +80,26 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window, store=N
     nkv = k.shape[1]
     g = nq // nkv
     pos = torch.arange(T)
-    visible = pos[None, :] <= pos[:, None]
-    if window is not None:
-        visible &= pos[None, :] > (pos[:, None] - window)
     out = torch.empty_like(q)
-    for h in range(nq):
-        kh = h // g
-        scores = (q[:, h, :] @ k[:, kh, :].T) * (1.0 / math.sqrt(d))
-        scores = scores.masked_fill(~visible, float("-inf"))
-        if store is None:
-            out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, kh, :]
-        else:
-            # the serving path feeds 16-bit probabilities to the tensor cores and divides by the
-            # 32-bit sum afterwards; it takes the exponentials in base 2 against a whole-number
-            # reference point, so that the 16-bit mantissas do not depend on how the keys are tiled
-            log2_scores = scores * math.log2(math.e)
-            p = torch.exp2(log2_scores - torch.ceil(log2_scores.max(dim=-1, keepdim=True).values))
-            out[:, h, :] = (store(p) @ v[:, kh, :]) / p.sum(dim=-1, keepdim=True)
+    rows_at_a_time = 1024          # of a long sequence the score matrix is made a band of query rows at a time (memory only)
+    for begin in range(0, T, rows_at_a_time):
+        rows = pos[begin:begin + rows_at_a_time]
+        visible = pos[None, :] <= rows[:, None]
+        if window is not None:
+            visible &= pos[None, :] > (rows[:, None] - window)
+        for h in range(nq):
+            kh = h // g
+            scores = (q[rows, h, :] @ k[:, kh, :].T) * (1.0 / math.sqrt(d))
+            scores = scores.masked_fill(~visible, float("-inf"))
+            if store is None:
+                out[rows, h, :] = torch.softmax(scores, dim=-1) @ v[:, kh, :]
+            else:
+                # the serving path feeds 16-bit probabilities to the tensor cores and divides by the
+                # 32-bit sum afterwards; it takes the exponentials in base 2 against a whole-number
+                # reference point, so that the 16-bit mantissas do not depend on how the keys are tiled
+                log2_scores = scores * math.log2(math.e)
+                p = torch.exp2(log2_scores - torch.ceil(log2_scores.max(dim=-1, keepdim=True).values))
+                out[rows, h, :] = (store(p) @ v[:, kh, :]) / p.sum(dim=-1, keepdim=True)
     return out
 
 

@@ -119,3 +119,81 @@ def test_random_orders_of_requests(seed):
         m.release(slot)
     m.check()
     assert all(g.pool.in_use() == 0 for g in m.groups) and m.free_slots() == 4
+
+
+class DeferredDevice:
+    """A stand-in for the stream: copies queued by `flush` run only when asked to (or when a fence that was
+    recorded after them is waited for), and they read their source THEN, as an asynchronous copy does."""
+
+    def __init__(self):
+        self.queue = []          # ("copy", destination, source) | ("fence", fence)
+
+    def copy(self, destination, source):
+        self.queue.append(("copy", destination, source))
+
+    def fence(self):
+        device = self
+
+        class Fence:
+            recorded = False
+
+            def record(self):
+                self.recorded = True
+                device.queue.append(("fence", self))
+
+            def synchronize(self):
+                if self.recorded and any(item[0] == "fence" and item[1] is self for item in device.queue):
+                    device.run_until(self)
+        return Fence()
+
+    def run_until(self, fence=None):
+        while self.queue:
+            item = self.queue.pop(0)
+            if item[0] == "copy":
+                item[1].copy_(item[2])
+            elif item[1] is fence:
+                return
+
+
+def deferred(m):
+    device = DeferredDevice()
+    for group in m.groups:
+        group._copy = device.copy
+        group._fences = [device.fence() for _ in group._fences]
+    return device
+
+
+def test_queued_table_copies_see_the_table_of_flush_time_whatever_the_host_does_next():
+    """The pipelined scheduler flushes for step N+1, then learns that a request of step N ended and releases
+    it, which resets its row on the host, before the queued copy has run.  The device must still receive the
+    row as it was at the flush: the step that is queued holds the request."""
+    m = manager(num_pages=12)
+    device = deferred(m)
+    a, b = m.admit(), m.admit()
+    assert m.ensure(a, 0, 9) and m.ensure(b, 0, 5)
+    at_flush = {a: list(m.groups[0].tables[a]), b: list(m.groups[0].tables[b])}
+    m.flush()                                   # copies are queued, none has run
+    m.release(a)                                # the host resets a's row (and would hand its pages to others)
+    assert m.ensure(b, 5, 13)                   # b's row grows on the host
+    device.run_until()                          # now the device catches up with the first flush
+    table = m.groups[0].device_table
+    assert table[a, :3].tolist() == at_flush[a], "the queued copy read the live table"
+    assert table[b, :2].tolist() == at_flush[b] and table[b, 2].item() == -1
+    m.flush()
+    device.run_until()
+    assert table[a, :3].tolist() == [-1, -1, -1] and table[b, :4].tolist() == m.groups[0].tables[b]
+    m.check()
+
+
+def test_staging_ring_waits_for_its_own_copies_before_it_is_written_again():
+    m = manager(num_pages=40, page_size=2, max_slots=2)
+    device = deferred(m)
+    s = m.admit()
+    seen = []
+    for step in range(3 * m.groups[0].RING):    # far more flushes than staging buffers, none of them run yet
+        assert m.ensure(s, 2 * step, 2 * step + 2)
+        seen.append(list(m.groups[0].tables[s]))
+        m.flush()
+    device.run_until()
+    assert m.groups[0].device_table[s, :len(seen[-1])].tolist() == seen[-1]
+    m.check()

@@ -31,7 +31,7 @@ def test_config_reads_every_key_and_derives_scales():
 @pytest.mark.parametrize("change, message", [
     ({"hidden_act": "gelu"}, "hidden_act"), ({"attention_bias": True}, "attention_bias"),
     ({"rope_scaling": {"type": "linear"}}, "rope_scaling"), ({"quantization_config": {"bits": 4}}, "quantized"),
-    ({"num_key_value_heads": 3}, "multiple"), ({"head_dim": 24}, "multiple of 16"),
+    ({"num_key_value_heads": 3}, "multiple"), ({"head_dim": 7}, "even"),
     ({"rms_norm_eps": 0}, "rms_norm_eps"), ({"rope_theta": -1}, "rope_theta"), ({"vocab_size": None}, "vocab_size"),
     ({"layer_types": ["sliding_attention", "full_attention"]}, "sliding_window"),
     ({"layer_types": ["full_attention"]}, "layer_types"), ({"scale_depth": float("inf")}, "scale_depth"),
@@ -39,6 +39,18 @@ def test_config_reads_every_key_and_derives_scales():
 def test_config_refusals(change, message):
     with pytest.raises(ConfigError, match=message):
         LlamaConfig.from_dict({**BASE, **change})
+
+
+def test_sizes_the_kernels_cannot_take_are_refused_when_the_model_is_described():
+    """The configuration class knows the architecture, not the kernels: a head size that the attention kernels do
+    not take passes `LlamaConfig` and is refused by the attention part when the model's description is put
+    together (on the CPU, before any tensor is read), with the kernels' reason."""
+    for head_dim in (24, 272):
+        config = LlamaConfig.from_dict({**BASE, "head_dim": head_dim})
+        with pytest.raises(ValueError, match="multiple of 16 of at most 256"):
+            resolve_architecture(config.to_dict()).build(config)
+    config = LlamaConfig.from_dict({**BASE, "head_dim": 48})
+    assert len(resolve_architecture(config.to_dict()).build(config).layers) == config.num_hidden_layers
 
 
 def test_registry():

@@ -184,7 +184,8 @@ def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
     whole = replay.step([("b", tokens, range(4))], end=["a", "b"])
     helpers.assert_close(whole, reference, dtype, f"{name} first tokens whole")
     # a step that wants nothing still writes the cache
-    assert replay.step([("c", tokens[:2], [])]) is None or True
+    nothing = replay.step([("c", tokens[:2], [])])
+    assert nothing is not None and nothing.shape == (0, model["config"]["vocab_size"])
     tail = replay.step([("c", tokens[2:], [0, 1])], end=["c"])
     helpers.assert_close(tail, reference[2:], dtype, f"{name} after a step that wanted nothing")
 
@@ -214,33 +215,133 @@ def test_trace_run_program(tiny_models, tmp_path, dtype):
     helpers.assert_close(read(0), ref_a[[0, 9]], dtype, "trace step 0")
     helpers.assert_close(read(1), ref_b[[7]], dtype, "trace step 1")
     helpers.assert_close(read(2), torch.cat([ref_b[[8]], ref_a[[20]]]), dtype, "trace step 2")
+    with open(tmp_path / "index.json") as f:
+        index = json.load(f)
+    assert index["vocab_size"] == vocab
+    assert index["rows"] == {"0": [["a", 0], ["a", 9]], "1": [["b", 7]], "2": [["b", 8], ["a", 20]]}
+
+
+def test_replay_function_more_than_four_live_and_a_page_size_that_does_not_divide_64(tiny_models):
+    """`replay(model, steps)`: the trace program as a Python call.  Six requests live at once, pages of 12
+    tokens, a pool that the requests' rounded counts just fill, so that the second wave reuses pages."""
+    from lia_rs_b200 import replay
+    model = tiny_models["tiny-D"]
+    vocab = model["config"]["vocab_size"]
+    requests = {f"r{i}": helpers.random_tokens(vocab, 20 + 9 * i, 40 + i) for i in range(6)}
+    later = {f"s{i}": helpers.random_tokens(vocab, 50 + i, 60 + i) for i in range(6)}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": v[:11], "want": [10]} for k, v in requests.items()], "end": []},
+             {"step": 1, "entries": [{"id": k, "tokens": v[11:], "want": [len(v) - 12]} for k, v in requests.items()],
+              "end": list(requests)},
+             {"step": 2, "entries": [{"id": k, "tokens": v, "want": [0, len(v) - 1]} for k, v in later.items()],
+              "end": list(later)}]
+    logits, index = replay(model["dir"], steps, dtype="float32", max_tokens=6 * 128, max_live=6, page_size=12)
+    assert index[1] == [[k, len(v) - 1] for k, v in requests.items()]
+    for row, (k, v) in enumerate(requests.items()):
+        reference = helpers.plain_logits(model, v, "float32")
+        helpers.assert_close(logits[0][row:row + 1], reference[[10]], "float32", f"replay {k} step 0")
+        helpers.assert_close(logits[1][row:row + 1], reference[[len(v) - 1]], "float32", f"replay {k} step 1")
+    for row, (k, v) in enumerate(later.items()):
+        reference = helpers.plain_logits(model, v, "float32")
+        helpers.assert_close(logits[2][2 * row:2 * row + 2], reference[[0, len(v) - 1]], "float32", f"replay {k}")
 
 
 @pytest.mark.parametrize("name", ["tiny-D", "tiny-E"])
 @pytest.mark.parametrize("batch", [1, 3, 8, 11, 16])
-def test_persistent_decode_kernel_against_parts(tiny_models, name, batch):
+def test_decode_batches_with_varied_contexts(tiny_models, name, batch):
     """Decode steps of 1 to 16 requests with contexts from a few tokens to hundreds (several ranges of
-    keys per token, the window's edge, pages used in scrambled order), through the persistent kernel
-    over all layers and through the part-by-part kernels: the same logits beyond rounding, and both
-    close to the plain implementation."""
+    keys per token, the window's edge, pages used in scrambled order) against the plain implementation."""
     from lia_rs_b200.engine import Engine
     model = tiny_models[name]
     vocab = model["config"]["vocab_size"]
     lengths = [3 + (37 * i) % 290 for i in range(batch)]
     prompts = [helpers.random_tokens(vocab, n + 6, 100 + i) for i, n in enumerate(lengths)]
-    results = {}
-    for stack in (True, False):
-        engine = Engine(model["dir"], dtype="bfloat16", page_size=model["page_size"], max_tokens=16 * 320, max_seqs=16,
-                        max_batch_tokens=512, decode_stack=stack)
-        replay = helpers.Replayer(engine)
-        for i, (tokens, n) in enumerate(zip(prompts, lengths)):
-            replay.step([(f"r{i}", tokens[:n], [])])
-        rows = []
-        for k in range(6):
-            rows.append(replay.step([(f"r{i}", [tokens[n + k]], [0]) for i, (tokens, n) in enumerate(zip(prompts, lengths))]))
-        results[stack] = np.stack(rows)                               # [6, batch, vocab]
-        assert (engine.model.stack_steps > 0) == stack
+    engine = Engine(model["dir"], dtype="bfloat16", page_size=model["page_size"], max_tokens=16 * 320, max_seqs=16,
+                    max_batch_tokens=512)
+    replay = helpers.Replayer(engine)
+    for i, (tokens, n) in enumerate(zip(prompts, lengths)):
+        replay.step([(f"r{i}", tokens[:n], [])])
+    rows = []
+    for k in range(6):
+        rows.append(replay.step([(f"r{i}", [tokens[n + k]], [0]) for i, (tokens, n) in enumerate(zip(prompts, lengths))]))
+    result = np.stack(rows)                               # [6, batch, vocab]
     for i, (tokens, n) in enumerate(zip(prompts, lengths)):
         reference = helpers.plain_logits(model, tokens, "bfloat16")[n:n + 6]
-        helpers.assert_close(results[True][:, i], reference, "bfloat16", f"{name} request {i} through the persistent kernel")
-        helpers.assert_close(results[False][:, i], reference, "bfloat16", f"{name} request {i} part by part")
+        helpers.assert_close(result[:, i], reference, "bfloat16", f"{name} request {i}")
+
+
+@pytest.mark.parametrize("name", MODELS)
+def test_float32_logits_are_bit_identical_under_every_way_of_cutting(tiny_models, name):
+    """The 32-bit kernels sum every product's K in ascending order per output element and walk a token's keys in an
+    order that depends on its position alone, so a position's logits are the same bits whole, one by one, in
+    portions, and mixed with other requests on pages that were used before."""
+    model = tiny_models[name]
+    vocab = model["config"]["vocab_size"]
+    a, b = helpers.random_tokens(vocab, 70, 201), helpers.random_tokens(vocab, 45, 202)
+    engine = make_engine(model, "float32", 160)
+    replay = helpers.Replayer(engine)
+    whole_a = replay.step([("a", a, range(70))], end=["a"])
+    whole_b = replay.step([("b", b, range(45))], end=["b"])
+    # most in one step, the last 32 one by one
+    rows = [replay.step([("a", a[:38], range(38))])]
+    rows += [replay.step([("a", [a[i]], [0])], end=["a"] if i == 69 else []) for i in range(38, 70)]
+    assert np.array_equal(np.concatenate(rows), whole_a), "prompt + last 32 one by one"
+    # portions of changing size
+    rows, at, k = [], 0, 0
+    sizes = [5, 2, 7, 3, 2, 11, 4, 2, 9, 6]
+    while at < 70:
+        n = min(sizes[k % len(sizes)], 70 - at)
+        k += 1
+        rows.append(replay.step([("a", a[at:at + n], range(n))], end=["a"] if at + n == 70 else []))
+        at += n
+    assert np.array_equal(np.concatenate(rows), whole_a), "portions"
+    # mixed: portions of one beside single tokens of the other, in both orders within the batch
+    got_a, got_b = [], [replay.step([("b", b[:20], range(20))])]
+    both = replay.step([("a", a[:33], range(33)), ("b", [b[20]], [0])])
+    got_a.append(both[:33]); got_b.append(both[33:])
+    both = replay.step([("b", b[21:30], range(9)), ("a", [a[33]], [0])])
+    got_b.append(both[:9]); got_a.append(both[9:])
+    both = replay.step([("a", a[34:], range(36)), ("b", b[30:], range(15))], end=["a", "b"])
+    got_a.append(both[:36]); got_b.append(both[36:])
+    assert np.array_equal(np.concatenate(got_a), whole_a), "mixed, first request"
+    assert np.array_equal(np.concatenate(got_b), whole_b), "mixed, second request"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny-A", "tiny-C", "tiny-E"])
+def test_last_layer_runs_only_the_wanted_rows(tiny_models, name, dtype):
+    """A step that wants fewer rows than it brings runs the last layer's output projection, second norm and
+    feed-forward for the wanted rows alone (the reference prunes the same way, src/inference/llama_fusion.rs:45-60):
+    the logits do not change, the cache is written for every token, and the products shrink."""
+    from lia_rs_b200.engine import Engine
+    model = tiny_models[name]
+    cfg = model["config"]
+    tokens = helpers.random_tokens(cfg["vocab_size"], 60, 211)
+    reference = helpers.plain_logits(model, tokens, dtype)
+    engine = Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=256, max_seqs=4,
+                    max_batch_tokens=128, profile=True)
+    replay = helpers.Replayer(engine)
+    # rows {0, last} of one request and no row of another, in one step
+    other = helpers.random_tokens(cfg["vocab_size"], 17, 212)
+    logits = replay.step([("a", tokens[:40], [0, 39]), ("b", other[:9], [])])
+    helpers.assert_close(logits, reference[[0, 39]], dtype, f"{name} rows 0 and last")
+    summary = engine.profile_summary()
+    layers, hidden, inter = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"]
+    down = sum(v["flops"] for k, v in summary.items() if k.endswith(":down"))
+    assert down == 2 * hidden * inter * ((layers - 1) * 49 + 2), "the last layer's down product ran more than two rows"
+    out = sum(v["flops"] for k, v in summary.items() if k.endswith(":o"))
+    width = cfg["num_attention_heads"] * cfg["head_dim"]
+    assert out == 2 * hidden * width * ((layers - 1) * 49 + 2)
+    # a step that wants nothing: the last layer only appends to the cache
+    nothing = replay.step([("a", tokens[40:50], []), ("b", other[9:], [])])
+    assert nothing.shape == (0, cfg["vocab_size"])
+    summary = engine.profile_summary()
+    assert sum(v["flops"] for k, v in summary.items() if k.endswith(":down")) == 2 * hidden * inter * (layers - 1) * 18
+    assert not any(k.endswith(":head") for k in summary)
+    # what those steps wrote is what later rows read
+    rest = replay.step([("a", tokens[50:], range(10)), ("b", [other[0]], [])], end=["a"])
+    helpers.assert_close(rest, reference[50:], dtype, f"{name} after pruned steps")
+    # few wanted rows among many tokens: only they attend in the last layer (a different kernel serves them)
+    engine.profile = False
+    long_tokens = helpers.random_tokens(cfg["vocab_size"], 100, 213)
+    logits = replay.step([("c", long_tokens, [3, 57, 99])], end=["c", "b"])
+    helpers.assert_close(logits, helpers.plain_logits(model, long_tokens, dtype)[[3, 57, 99]], dtype, f"{name} three of 100 rows")

@@ -325,43 +325,6 @@ def test_gemm_tc_many_tokens_tile_widths(M, N, K):
     assert flag.item() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2048), (1999, 2700, 520), (4096, 1280, 1024), (2048, 6144, 2048), (777, 12288, 256),
-                                   (256, 256, 64), (300, 3000, 200), (2048, 2048, 6144)])
-def test_gemm_pair_all_epilogues_against_64_bit(M, N, K):
-    """The product on pairs of SMs (cta_group::2): tiles of 256 weight rows x 256 tokens, partial last tiles
-    of tokens and of rows, one tile and thousands, K shorter than the ring and longer."""
-    o = ops()
-    torch.manual_seed(M + N + K)
-    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
-    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
-    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    exact = a.double() @ w.double().T
-    scale = max(1.0, float(exact.abs().max()))
-    out = torch.full((M, N), 7.0, device=DEV)
-    assert o.gemm_pair_accepts(o.GEMM_STORE, a, w[:N], out)
-    o.gemm_pair(o.GEMM_STORE, a, w[:N], out, 0.25, flag)
-    assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(K / 64)
-    half = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    if o.gemm_pair_accepts(o.GEMM_STORE, a, w[:N], half):          # rows of N bfloat16 must be a multiple of 16 bytes
-        o.gemm_pair(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
-        assert float((half.double() - exact[:, :N]).abs().max()) <= 2.0 ** -8 * scale
-    else:
-        with pytest.raises(o.KernelError, match="aligned"):
-            o.gemm_pair(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
-    base = torch.randn(M, N, device=DEV)
-    acc = base.clone()
-    o.gemm_pair(o.GEMM_ACCUM, a, w[:N], acc, 1.5, flag)
-    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(K / 64)
-    act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    if o.gemm_pair_accepts(o.GEMM_SWIGLU, a, w, act):
-        o.gemm_pair(o.GEMM_SWIGLU, a, w, act, 1.0, flag)
-        gate, up = exact[:, :N], exact[:, N:]
-        want = up * gate / (1 + torch.exp(-gate))
-        assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
-    torch.cuda.synchronize()
-    assert flag.item() == 0
-
-
 @pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("N,K", [(40, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (77, 16384), (301, 7000)])
 def test_gemm_skinny_all_epilogues_against_64_bit(M, N, K):

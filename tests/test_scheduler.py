@@ -271,3 +271,17 @@ def test_a_request_ended_by_its_token_has_one_step_computed_for_nobody():
         assert a.generated == expected(prompt, 3) and a.stopped
     assert b.generated == expected([5, 6, 7], 6)
     assert engine.cache.available_pages() == 32
+
+
+def test_live_requests_without_a_row_to_run_raise_instead_of_spinning():
+    """src/server/paged/schedule.rs:123-125: a step in which requests are live and none can be scheduled is an
+    error, not a loop.  The stand-in's cache is made to refuse every page after admission while claiming that
+    none is needed, which the real manager cannot do."""
+    engine = StandInEngine(num_pages=8)
+    s = Scheduler(engine, max_batch_tokens=8, pipeline=False)
+    s.add("a", [1, 2, 3, 4, 5, 6, 7, 8, 9], max_tokens=4)
+    s.admit()
+    engine.cache.ensure = lambda slot, start, end: False
+    engine.cache.pages_for = lambda slot, start, end: 0
+    with pytest.raises(SchedulerError, match="made no progress"):
+        s.step()

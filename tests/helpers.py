@@ -212,6 +212,24 @@ def assert_close(actual, reference, dtype: str, what: str, k: int = None):
         raise AssertionError(f"{what}: max abs error {worst:.3e} > {limit:.3e} (first at wanted row {row})")
 
 
+def assert_as_accurate_as_rounding(actual, exact, rounded, what: str, margin: float = 1.25):
+    """For a deep model in bfloat16.  After tens of layers two computations that round to 16 bits at the same
+    places but add in different orders no longer agree element by element: each is the exact model plus rounding
+    noise of its own (measured on the 40-layer model: the plain implementation with rounding is off the exact one
+    by 4 % of a logit's size, and so is the engine).  So the engine is held to being no farther from the EXACT
+    model than the plain implementation with rounding is, in the root mean square and at the worst logit, with a
+    quarter of margin; a fault (a wrong key, a missing layer, a wrong scale) is far outside that."""
+    actual = torch.as_tensor(np.asarray(actual), dtype=torch.float64)
+    exact, rounded = exact.to(torch.float64), rounded.to(torch.float64)
+    assert actual.shape == exact.shape == rounded.shape, f"{what}: shapes differ"
+    assert torch.isfinite(actual).all(), f"{what}: non-finite logits"
+    rms = lambda x: float(x.pow(2).mean().sqrt())
+    ours, theirs = actual - exact, rounded - exact
+    assert rms(ours) <= margin * rms(theirs), f"{what}: rms error {rms(ours):.3e} > {margin} x {rms(theirs):.3e}"
+    worst, allowed = float(ours.abs().max()), margin * float(theirs.abs().max())
+    assert worst <= allowed, f"{what}: max abs error {worst:.3e} > {allowed:.3e}"
+
+
 class Replayer:
     """Drives an Engine the way bin/trace_run does, in process: requests by name, their positions,
     reservation of pages, release at `end`."""

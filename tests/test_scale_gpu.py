@@ -70,15 +70,15 @@ def test_long_context_in_portions_then_decoding(long_models, name, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["tiny-D", "tiny-E"])
 def test_64_live_requests(tiny_models, name, dtype):
-    """64 requests with contexts of 3 to 600 tokens: 8 decode steps of all of them (a product of 64 tokens in every
+    """64 requests with contexts of 3 to 500 tokens: 8 decode steps of all of them (a product of 64 tokens in every
     layer), then one mixed step of 48 single tokens beside two prompt portions."""
     from lia_rs_b200.engine import Engine
     model = tiny_models[name]
     vocab = model["config"]["vocab_size"]
-    lengths = [3 + (97 * i) % 598 for i in range(64)]
+    lengths = [3 + (97 * i) % 490 for i in range(64)]
     requests = [helpers.random_tokens(vocab, n + 9, 500 + i) for i, n in enumerate(lengths)]
     late = [helpers.random_tokens(vocab, 150, 700), helpers.random_tokens(vocab, 61, 701)]
-    engine = Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=64 * 640, max_seqs=64,
+    engine = Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=64 * 512, max_seqs=64,
                     max_batch_tokens=2048)
     replay = helpers.Replayer(engine)
     batch, count = [], 0
@@ -119,24 +119,36 @@ def whole_model(tmp_path_factory):
 def test_whole_2b_class_model_under_the_four_ways_of_cutting(whole_model, dtype):
     """All 40 layers and the 73,448-token vocabulary, a 64-token and a 33-token request: each whole; most of one
     in a step and its last 32 tokens one by one; portions of changing size; both mixed in a pool so small that
-    pages are used again.  (The plain implementation takes the 2 G parameters through 64-bit products on the CPU:
-    this is the slowest test of the suite.)"""
+    pages are used again.  32-bit: against the plain implementation, within the bound of the arithmetic.
+    bfloat16: no farther from the exact model than the plain implementation that rounds where the serving path
+    does (`helpers.assert_as_accurate_as_rounding` says why element-wise agreement ends at this depth).
+    (The plain implementation takes the 2 G parameters through 64-bit products on the CPU: this is the slowest
+    test of the suite.)"""
     from lia_rs_b200.engine import Engine
     model = whole_model
     vocab = model["config"]["vocab_size"]
     a, b = helpers.random_tokens(vocab, 64, 41), helpers.random_tokens(vocab, 33, 42)
-    ref_a, ref_b = helpers.plain_logits(model, a, dtype), helpers.plain_logits(model, b, dtype)
+    exact = {"a": helpers.plain_logits(model, a, "float32"), "b": helpers.plain_logits(model, b, "float32")}
+    rounded = {"a": helpers.plain_logits(model, a, dtype), "b": helpers.plain_logits(model, b, dtype)}
+    k = helpers.longest_sum(model["config"])
+
+    def check(logits, request, rows, what):
+        rows = list(rows)
+        if dtype == "float32":
+            helpers.assert_close(logits, exact[request][rows], dtype, what, k)
+        else:
+            helpers.assert_as_accurate_as_rounding(logits, exact[request][rows], rounded[request][rows], what)
+
     engine = Engine(model["dir"], dtype=dtype, page_size=16, max_tokens=128, max_seqs=4, max_batch_tokens=128)
     replay = helpers.Replayer(engine)
-    k = helpers.longest_sum(model["config"])
     # whole
-    helpers.assert_close(replay.step([("a", a, range(64))], end=["a"]), ref_a, dtype, "2B whole, 64 tokens", k)
-    helpers.assert_close(replay.step([("b", b, range(33))], end=["b"]), ref_b, dtype, "2B whole, 33 tokens", k)
+    check(replay.step([("a", a, range(64))], end=["a"]), "a", range(64), "2B whole, 64 tokens")
+    check(replay.step([("b", b, range(33))], end=["b"]), "b", range(33), "2B whole, 33 tokens")
     # most in one step, the last 32 one by one
     rows = [replay.step([("a", a[:32], [31])])]
     for i in range(32, 64):
         rows.append(replay.step([("a", [a[i]], [0])], end=["a"] if i == 63 else []))
-    helpers.assert_close(np.concatenate(rows), ref_a[31:], dtype, "2B last 32 one by one", k)
+    check(np.concatenate(rows), "a", range(31, 64), "2B last 32 one by one")
     # portions of changing size
     rows, at = [], 0
     for n in [5, 2, 7, 3, 2, 11, 4, 2, 9, 6, 13]:
@@ -144,7 +156,7 @@ def test_whole_2b_class_model_under_the_four_ways_of_cutting(whole_model, dtype)
         rows.append(replay.step([("a", a[at:at + n], range(n))], end=["a"] if at + n == 64 else []))
         at += n
     assert at == 64
-    helpers.assert_close(np.concatenate(rows), ref_a, dtype, "2B portions", k)
+    check(np.concatenate(rows), "a", range(64), "2B portions")
     # mixed: b decodes while a is filled; the pool (128 tokens) held a before and holds both now
     got_a, got_b = [], []
     got_b.append(replay.step([("b", b[:20], range(20))]))
@@ -156,8 +168,8 @@ def test_whole_2b_class_model_under_the_four_ways_of_cutting(whole_model, dtype)
         both = replay.step([("a", [a[57 + i]], [0]), ("b", [b[22 + i]], [0])])
         got_a.append(both[:1]); got_b.append(both[1:])
     got_b.append(replay.step([("b", b[29:], range(4))], end=["a", "b"]))
-    helpers.assert_close(np.concatenate(got_a), ref_a, dtype, "2B mixed, first request", k)
-    helpers.assert_close(np.concatenate(got_b), ref_b, dtype, "2B mixed, second request", k)
+    check(np.concatenate(got_a), "a", range(64), "2B mixed, first request")
+    check(np.concatenate(got_b), "b", range(33), "2B mixed, second request")
     for group in engine.cache.groups:
         assert group.pool.in_use() == 0
     del engine

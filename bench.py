@@ -15,9 +15,17 @@ printed:
   prefill    one step of a single 2,048-token prompt: tokens/s, ms, and flops / time / peak
   roofline   the decode step's bytes (every weight once + the live requests' cache) / time / peak
   points     decode tokens/s at batch 1 and 64
+  kernels    for the decode step and the prefill step, each kernel class's share of the step's device time
+             (CUDA events around every launch of a step run launch by launch, `Engine(profile=True)`) and the
+             fraction of its own roofline: weight or cache bytes / time / HBM peak for the decode step,
+             flops / time / bf16 peak for the prefill step
+  checked    outside the timed region, the benchmarked engine runs a 64-token prompt whole and again as 48
+             tokens and 16 single tokens; both are compared with the true 32-bit path over the same weights
 
-Weights (4.1 GB) and cache are far larger than the 126 MB L2, so no L2 flush is needed between
-timed steps.  Peaks come from MEASURED_PEAKS.json beside this file when it exists.
+Every point is timed for at least half a second of device time: the loop of K steps is repeated and the
+median loop is reported (`repeats` says how many).  Weights (4.1 GB) and cache are far larger than the
+126 MB L2, so no L2 flush is needed between timed steps.  Peaks come from MEASURED_PEAKS.json beside this
+file when it exists.
 """
 import argparse
 import json
@@ -124,72 +132,102 @@ def fill(engine, batch, prompt_tokens, rng_seed):
     return slots
 
 
+MIN_TIMED_MS = 500.0          # device time every point is measured over, at least
+MAX_DECODE_STEPS = 512        # steps a point may take in all (its requests' pages are reserved for them)
+
+
 def time_decode(engine, slots, start, steps, warmup):
-    """Device time of `steps` decode steps after `warmup` untimed ones; tokens are fixed beforehand."""
+    """Device time per step of the median loop of `steps` decode steps, after `warmup` untimed steps; the loop is
+    repeated until MIN_TIMED_MS of device time have been measured (within MAX_DECODE_STEPS).  Tokens are fixed
+    beforehand.  Returns (ms per step, kernels per step, repeats, steps run in all)."""
     import numpy as np
     import torch
     from lia_rs_b200.engine import StepEntry
     from lia_rs_b200.kernels import ops
     rng = np.random.default_rng(1)
     vocab = engine.spec.vocab_size
-    total = steps + warmup
-    feed = rng.integers(0, vocab, size=(total, len(slots)))
+    most = max(warmup + steps, MAX_DECODE_STEPS)
+    feed = rng.integers(0, vocab, size=(most, len(slots)))
     for slot in slots:
-        assert engine.reserve(slot, start, start + total)
+        assert engine.reserve(slot, start, start + most)
     picked = torch.empty(len(slots), dtype=torch.int32, device=engine.device)
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches = 0
-    for k in range(total):
-        if k == warmup:
-            torch.cuda.synchronize()
-            launches = engine.stats["kernels"]
-            begin.record()
-        entries = [StepEntry(slot, [int(feed[k, j])], start + k, [0]) for j, slot in enumerate(slots)]
-        logits = engine.step(entries)
-        ops.select_tokens(logits, picked)
-    end.record()
-    torch.cuda.synchronize()
-    engine.synchronize()
-    # kernels of the model's step (counted at the launch sites; a graph replay adds its kernel nodes) + selection
-    return begin.elapsed_time(end) / steps, (engine.stats["kernels"] - launches) // steps + 1
+    done = 0
+
+    def run(count):
+        nonlocal done
+        for _ in range(count):
+            entries = [StepEntry(slot, [int(feed[done, j])], start + done, [0]) for j, slot in enumerate(slots)]
+            logits = engine.step(entries)
+            ops.select_tokens(logits, picked)
+            done += 1
+
+    run(warmup)
+    loops, launches, measured = [], 0, 0.0
+    while True:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        before = engine.stats["kernels"]
+        begin.record()
+        run(steps)
+        end.record()
+        torch.cuda.synchronize()
+        engine.synchronize()
+        loops.append(begin.elapsed_time(end))
+        measured += loops[-1]
+        # kernels of the model's step (counted at the launch sites; a graph replay adds its kernel nodes) + selection
+        launches = (engine.stats["kernels"] - before) // steps + 1
+        if measured >= MIN_TIMED_MS or done + steps > most:
+            break
+    return statistics.median(loops) / steps, launches, len(loops), done
 
 
 def time_e2e(engine, batch, steps, warmup):
-    """Wall time per decode step through the scheduler: host token ids in, host token ids out."""
+    """Wall time per decode step through the scheduler: host token ids in, host token ids out.  The loop of
+    `steps` steps is repeated as `time_decode` repeats its loop; the median loop is reported."""
     import numpy as np
     import torch
     from lia_rs_b200.engine.scheduler import Scheduler
     rng = np.random.default_rng(2)
     vocab = engine.spec.vocab_size
     scheduler = Scheduler(engine, max_batch_tokens=engine.max_batch_tokens)
+    most = max(warmup + steps, MAX_DECODE_STEPS)
     for i in range(batch):
-        scheduler.add(i, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], max_tokens=steps + warmup + batch + 4)
+        scheduler.add(i, [int(t) for t in rng.integers(0, vocab, size=PROMPT)], max_tokens=most + batch + 4)
     while any(not r.generated for r in scheduler.live()) or scheduler.queue:
         scheduler.step()
     for _ in range(warmup):
         scheduler.step()
-    torch.cuda.synchronize()
+    loops, done, measured = [], warmup, 0.0
     h2d = d2h = 0
-    started = time.perf_counter()
-    for _ in range(steps):
-        scheduler.step()
-        h2d += engine.runtime_step.h2d_bytes
-        d2h += 4 * batch
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - started
+    while True:
+        torch.cuda.synchronize()
+        h2d = d2h = 0
+        started = time.perf_counter()
+        for _ in range(steps):
+            scheduler.step()
+            h2d += engine.runtime_step.h2d_bytes
+            d2h += 4 * batch
+        torch.cuda.synchronize()
+        loops.append(time.perf_counter() - started)
+        measured += loops[-1] * 1e3
+        done += steps
+        if measured >= MIN_TIMED_MS or done + steps > most:
+            break
     for request in scheduler.live():
         engine.release(request.slot)
-    return seconds / steps, h2d // steps, d2h // steps
+    return statistics.median(loops) / steps, h2d // steps, d2h // steps
 
 
-def time_prefill(engine, warmup=2, repeats=3):
+def time_prefill(engine, warmup=3, repeats=25):
     import numpy as np
     import torch
     from lia_rs_b200.engine import StepEntry
     rng = np.random.default_rng(3)
     tokens = [int(t) for t in rng.integers(0, engine.spec.vocab_size, size=PROMPT)]
-    best = None
-    for k in range(warmup + repeats):
+    times = []
+    k = -1
+    while k + 1 < warmup + repeats or sum(times) < MIN_TIMED_MS:
+        k += 1
         slot = engine.admit()
         assert engine.reserve(slot, 0, PROMPT)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -201,9 +239,8 @@ def time_prefill(engine, warmup=2, repeats=3):
         engine.synchronize()
         engine.release(slot)
         if k >= warmup:
-            ms = begin.elapsed_time(end)
-            best = ms if best is None else min(best, ms)
-    return best
+            times.append(begin.elapsed_time(end))
+    return statistics.median(times)
 
 
 # The family's other sizes and the workloads they are quoted on (--workload): not the contract's line, one line each.
@@ -242,13 +279,13 @@ def other_workload(name, steps, warmup) -> int:
         cfg, batch, prompt = CONFIG_8B, 64, 8192
         layers = cfg["num_hidden_layers"]
         if name == "8b-decode":
-            pool = batch * (prompt + 256)
+            pool = batch * (prompt + MAX_DECODE_STEPS + 64)
             engine = Engine.random(LlamaConfig.from_dict(cfg), seed=5, dtype="bfloat16", page_size=PAGE, max_tokens=pool,
                                    max_seqs=batch, max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
             slots = fill_in_portions(engine, batch, prompt, PROMPT, 7)
-            ms, launches = time_decode(engine, slots, prompt, steps, warmup)
+            ms, launches, _, ran = time_decode(engine, slots, prompt, steps, warmup)
             weight_bytes, cache_bytes_per_token = model_bytes(cfg, layers)       # (untied: of the table only a few rows are read)
-            step_bytes = weight_bytes + batch * (prompt + warmup + steps // 2) * cache_bytes_per_token
+            step_bytes = weight_bytes + batch * (prompt + (warmup + ran) // 2) * cache_bytes_per_token
             achieved = step_bytes / (ms * 1e-3) / 1e9
             print(json.dumps({"workload": name, "metric": "decode tokens/s (8B-class, batch 64, 8,192-token prompts, bf16)",
                               "value": round(batch * 1000.0 / ms, 1), "ms_per_step": round(ms, 3), "steps": steps,
@@ -324,6 +361,7 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
     parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
+    parser.add_argument("--no-check", action="store_true", help="skip the comparison with the 32-bit path")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode steps kernel by kernel instead of replaying CUDA graphs (for profilers)")
     args = parser.parse_args()
@@ -343,31 +381,32 @@ def main() -> int:
     import torch
     from lia_rs_b200 import LlamaConfig
     from lia_rs_b200.engine import Engine
+    from lia_rs_b200.weights import random_weights
 
     cfg = dict(CONFIG_2B, num_hidden_layers=args.layers)
     config = LlamaConfig.from_dict(cfg)
     peak = peaks()
+    sampler = ClockSampler()
+    sampler.start()                                  # clocks over the whole run
     largest = args.batch if args.no_points else max(args.batch, 64)
-    total_steps = args.steps + args.warmup
-    pool = largest * ((PROMPT + total_steps + 8 + 63) // 64 * 64) + PROMPT
-    engine = Engine.random(config, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=largest,
-                           max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"],
-                           cuda_graphs=not args.no_graphs)
+    most_steps = max(args.steps + args.warmup, MAX_DECODE_STEPS)
+    pool = largest * ((PROMPT + most_steps + 8 + 63) // 64 * 64) + PROMPT
+    tensors = random_weights(config, seed=0)         # one set of weights for the benchmarked engine and for its check
+    engine = Engine.from_tensors(config, tensors, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=largest,
+                                 max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"],
+                                 cuda_graphs=not args.no_graphs)
     weight_bytes, cache_bytes_per_token = model_bytes(cfg, args.layers)
 
     def decode_point(batch, steps, warmup):
         slots = fill(engine, batch, PROMPT, 10 + batch)
-        ms, launches = time_decode(engine, slots, PROMPT, steps, warmup)
+        result = time_decode(engine, slots, PROMPT, steps, warmup)
         for slot in slots:
             engine.release(slot)
-        return ms, launches
+        return result
 
-    sampler = ClockSampler()
-    sampler.start()
-    ms, launches = decode_point(args.batch, args.steps, args.warmup)
-    clocks = sampler.stop()
+    ms, launches, repeats, ran = decode_point(args.batch, args.steps, args.warmup)
     value = args.batch * 1000.0 / ms
-    context = PROMPT + args.warmup + args.steps // 2
+    context = PROMPT + (args.warmup + ran) // 2
     step_bytes = weight_bytes + args.batch * context * cache_bytes_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
@@ -377,13 +416,16 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for batch in (1, 64):
-            point_ms, _ = decode_point(batch, max(8, args.steps // 2), args.warmup)
+            point_ms, _, _, _ = decode_point(batch, args.steps, args.warmup)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
+    kernels = kernel_shares(engine, args.batch, peak)
+    checked = None if args.no_check else check_against_32_bit(engine, config, tensors, cfg)
+    clocks = sampler.stop()
 
     line = {
         "metric": "decode tokens/s (2B-class MiniCPM5 Llama, batch %d, 2,048-token prompts, bf16, one B200)" % args.batch,
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms, 4), "repeats": repeats, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
         "config": {"model": "MiniCPM5-Llama-2B-class", "layers": args.layers, "layers_of_config": 40,
@@ -402,10 +444,95 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm"], 4)},
         "points": points,
+        "kernels": kernels,
+        "checked": checked,
         "clocks": clocks,
     }
     print(json.dumps(line))
     return 0
+
+
+def kernel_shares(engine, batch, peak):
+    """Per kernel class, for a decode step of `batch` requests and for the 2,048-token prefill step: its share of
+    the step's device time and the fraction of its own roofline.  The steps run launch by launch with CUDA
+    events around every launch (`engine.profile`), outside every timed region."""
+    import numpy as np
+    from lia_rs_b200.engine import StepEntry
+    rng = np.random.default_rng(5)
+    vocab = engine.spec.vocab_size
+    slots = fill(engine, batch, PROMPT, 30)
+    for slot in slots:
+        assert engine.reserve(slot, PROMPT, PROMPT + 8)
+    engine.profile = True
+    out = {}
+    try:
+        for k in range(8):
+            engine.step([StepEntry(slot, [int(rng.integers(0, vocab))], PROMPT + k, [0]) for slot in slots])
+            if k == 2:
+                engine.profile_summary()                  # the first steps allocate: not counted
+        summary = engine.profile_summary()
+        total = sum(v["ms"] for v in summary.values())
+        out["decode"] = {name: {"share": round(v["ms"] / total, 4),
+                                "frac": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peak["hbm"], 4) if v["bytes"] else None}
+                         for name, v in sorted(summary.items())}
+        for slot in slots:
+            engine.release(slot)
+        tokens = [int(t) for t in rng.integers(0, vocab, size=PROMPT)]
+        for k in range(3):
+            slot = engine.admit()
+            assert engine.reserve(slot, 0, PROMPT)
+            engine.step([StepEntry(slot, tokens, 0, [PROMPT - 1])])
+            engine.synchronize()
+            engine.release(slot)
+            if k == 0:
+                engine.profile_summary()
+        summary = engine.profile_summary()
+        total = sum(v["ms"] for v in summary.values())
+        out["prefill"] = {name: {"share": round(v["ms"] / total, 4),
+                                 "frac": round(v["flops"] / (v["ms"] * 1e-3) / 1e12 / peak["tflops"], 4) if v["flops"] else None}
+                          for name, v in sorted(summary.items())}
+    finally:
+        engine.profile = False
+    return out
+
+
+def check_against_32_bit(engine, config, tensors, cfg):
+    """A tripwire, not parity (the tests hold that): the benchmarked bfloat16 engine and the true 32-bit path over
+    the same weights, a 64-token prompt whole and again as 48 tokens and 16 single tokens.  The limit is what 16-bit
+    rounding at six places a layer adds up to over the layers, at the size of the largest logit."""
+    import math
+    import numpy as np
+    import torch
+    from lia_rs_b200.engine import Engine, StepEntry
+    rng = np.random.default_rng(6)
+    tokens = [int(t) for t in rng.integers(0, cfg["vocab_size"], size=64)]
+
+    def both_ways(e):
+        slot = e.admit()
+        assert e.reserve(slot, 0, 64)
+        whole = e.step([StepEntry(slot, tokens, 0, list(range(64)))]).float().cpu()
+        e.synchronize()
+        e.release(slot)
+        slot = e.admit()
+        assert e.reserve(slot, 0, 64)
+        rows = [e.step([StepEntry(slot, tokens[:48], 0, list(range(48)))]).float().cpu()]
+        for i in range(48, 64):
+            rows.append(e.step([StepEntry(slot, [tokens[i]], i, [0])]).float().cpu())
+        e.synchronize()
+        e.release(slot)
+        return whole, torch.cat(rows)
+
+    whole, cut = both_ways(engine)
+    exact_engine = Engine.from_tensors(config, tensors, dtype="float32", page_size=PAGE, max_tokens=128, max_seqs=2,
+                                       max_batch_tokens=64, max_context=cfg["max_position_embeddings"])
+    exact, exact_cut = both_ways(exact_engine)
+    del exact_engine
+    torch.cuda.empty_cache()
+    largest = float(exact.abs().max())
+    limit = 2.0 ** -8 * math.sqrt(6 * cfg["num_hidden_layers"]) * largest
+    worst = max(float((whole - exact).abs().max()), float((cut - exact).abs().max()))
+    return {"max_abs_err": round(worst, 5), "limit": round(limit, 5), "largest_logit": round(largest, 4),
+            "whole_vs_cut_32_bit": float((exact - exact_cut).abs().max()), "ok": bool(worst <= limit)}
 
 
 if __name__ == "__main__":

@@ -18,7 +18,7 @@ from ..config import read_config_json, resolve_architecture
 from ..kernels import ops
 from ..models import DecoderModel
 from ..parts import Runtime
-from ..weights import adopt_tensors, load_weights, random_tensors
+from ..weights import adopt_tensors, load_weights, random_weights
 from .step import StepRuntime
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -40,7 +40,7 @@ class PendingTokens:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_tokens: int = 8192, max_seqs: int = 8, max_batch_tokens: int = 2048,
-                 max_context: int = None, cuda_graphs: bool = True, profile: bool = False, _random=None):
+                 max_context: int = None, cuda_graphs: bool = True, profile: bool = False, _tensors=None):
         """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
         `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
         `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
@@ -55,17 +55,16 @@ class Engine:
         if not torch.cuda.is_available():
             raise RuntimeError("lia_rs_b200 needs a CUDA device: there is no CPU execution path")
         ops.lib()                                            # build/load the kernels now, loudly
-        raw = _random[0].to_dict() if _random else read_config_json(model_dir)
+        raw = _tensors[0].to_dict() if _tensors else read_config_json(model_dir)
         self.architecture = resolve_architecture(raw)
-        self.config = _random[0] if _random else self.architecture.config_class.from_dict(raw)
+        self.config = _tensors[0] if _tensors else self.architecture.config_class.from_dict(raw)
         self.spec = self.architecture.build(self.config)
         self.dtype_name = "bfloat16" if _DTYPES[dtype] == torch.bfloat16 else "float32"
         self.runtime = Runtime(device, _DTYPES[dtype])
         self.device = self.runtime.device
         torch.cuda.set_device(self.device)
-        if _random:
-            std = float(getattr(self.config, "initializer_range", 0.02))
-            tensors = adopt_tensors(random_tensors(self.spec.tensor_specs(), _random[1], std), self.spec.tensor_specs())
+        if _tensors:
+            tensors = adopt_tensors(_tensors[1], self.spec.tensor_specs())
         else:
             tensors = load_weights(model_dir, self.spec.tensor_specs())
         self.model = DecoderModel(self.spec, tensors, self.runtime)
@@ -90,11 +89,17 @@ class Engine:
         self._graphs = {}
 
     @classmethod
+    def from_tensors(cls, config, tensors: dict, **options) -> "Engine":
+        """An engine over tensors that are already in memory, by checkpoint name (they pass the loader's checks:
+        missing, unexpected, wrong shapes, non-finite values), for a typed configuration."""
+        return cls(None, _tensors=(config, tensors), **options)
+
+    @classmethod
     def random(cls, config, seed: int = 0, **options) -> "Engine":
         """An engine with the weights that `weights.write_random_model(config, folder, seed)` would write (the
         same generator, the same values, through the loader's checks), without the folder: for sizes whose
         file would take long to write and read back."""
-        return cls(None, _random=(config, seed), **options)
+        return cls.from_tensors(config, random_weights(config, seed), **options)
 
     # ---- requests and pages (thin faces of the cache manager) ----
     def admit(self) -> int:

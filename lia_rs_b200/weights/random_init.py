@@ -34,17 +34,20 @@ def random_tensors(specs, seed: int, std: float) -> dict:
     return out
 
 
+def random_weights(config, seed: int = 0) -> dict:
+    """The tensors of the model that `config` (a typed configuration of a registered architecture) describes,
+    by checkpoint name: the one source of random weights, whether they are written to a folder or not."""
+    from ..config import resolve_architecture
+
+    model_spec = resolve_architecture(config.to_dict()).build(config)
+    return random_tensors(model_spec.tensor_specs(), seed, float(getattr(config, "initializer_range", 0.02)))
+
+
 def write_random_model(config, model_dir: str, seed: int = 0) -> str:
     """`config` is a typed configuration (any class registered with the architecture
     registry).  Returns the folder."""
-    from ..config import resolve_architecture
-
-    raw = config.to_dict()
-    arch = resolve_architecture(raw)
-    model_spec = arch.build(config)
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
-        json.dump(raw, f, indent=1)
-    tensors = random_tensors(model_spec.tensor_specs(), seed, float(getattr(config, "initializer_range", 0.02)))
-    write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors)
+        json.dump(config.to_dict(), f, indent=1)
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), random_weights(config, seed))
     return model_dir

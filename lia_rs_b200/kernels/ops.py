@@ -59,6 +59,9 @@ class _Signatures:
     lia_gemm_cluster_splits = [c_int, c_int, c_int, c_int, c_int]
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
+    lia_gemm_stream = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                       c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p]
+    lia_gemm_stream_stages = [c_int, c_int, c_int, c_int, c_int, c_int]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -360,6 +363,48 @@ def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None
     with _timed("gemm_skinny", label, work=lambda: _gemm_work(a, w, out)):
         _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                      out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
+
+
+STREAM_MAX_TOKENS = 16
+STREAM_NORM_MAX_K = 4096
+
+
+def gemm_stream_accepts(mode, a, w, out, norm=False) -> bool:
+    """Whether the persistent few-token kernel takes this product: bfloat16 weights, at most 16 tokens whose rows
+    fit in shared memory beside a ring of two stages, K and the row strides multiples of 8 elements, 16-byte
+    aligned bases.  `norm`: `a` is the 32-bit rows that the kernel norms itself (K at most 4,096)."""
+    if w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    if a.dtype != (torch.float32 if norm else torch.bfloat16):
+        return False
+    M, K = a.shape
+    if not (M <= STREAM_MAX_TOKENS and K % 64 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return False
+    _, sms = _device_scratch(a.device)
+    return lib().lia_gemm_stream_stages(mode, M, out.shape[1], K, 1 if norm else 0, sms) > 0
+
+
+def gemm_stream(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, norm_weight=None, eps: float = 0.0,
+                stages_cap: int = 0, early_stages: int = 0):
+    """out[M, N] (op)= alpha * x[M, K] @ w[N, K]^T for M <= 16 tokens, one persistent CTA per SM with the
+    tokens' rows resident in shared memory; see csrc/gemm_stream.cu.  Without `norm_weight`, x = a (bfloat16);
+    with it, a is 32-bit and x = RMSNorm(a; norm_weight, eps) rounded to bfloat16, computed inside the kernel."""
+    M, K = a.shape
+    N = out.shape[1]
+    if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _, sms = _device_scratch(a.device)
+    if norm_weight is None:
+        x, ldx, src, ld_src, nw, nw_code = _p(a), a.stride(0), None, 0, None, 0
+    else:
+        if a.dtype != torch.float32 or norm_weight.numel() != K or not norm_weight.is_contiguous():
+            raise KernelError("gemm_stream with a norm takes 32-bit rows and a weight of K elements")
+        x, ldx, src, ld_src, nw, nw_code = None, 0, _p(a), a.stride(0), _p(norm_weight), dtype_code(norm_weight.dtype)
+    with _timed("gemm_stream", label, work=lambda: _gemm_work(a, w, out)):
+        _check(lib().lia_gemm_stream(mode, x, ldx, _p(w), w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0),
+                                     M, N, K, alpha, src, ld_src, nw, nw_code, eps, sms, stages_cap, early_stages, _p(error_flag),
+                                     _stream()), "gemm_stream")
 
 
 ATTENTION_HEAD_DIM_STEP, ATTENTION_HEAD_DIM_MAX = 16, 256      # what csrc/attention_generic.cu takes

@@ -25,6 +25,7 @@ from .paged_attention import PagedAttention
 class GQAttention(Mixer):
     graph_safe = True
     supports_rows = True
+    takes_deferred_norm = True
 
     @staticmethod
     def check_params(params):

@@ -95,6 +95,31 @@ class Norm(Part):
         """out[r] = norm(x[rows_index[r]] or x[r]) * out_scale; x 32-bit, out compute type."""
         raise NotImplementedError
 
+    def rms_record(self):
+        """`(weight, eps)` if this norm is exactly y = x / sqrt(mean(x^2) + eps) * weight (a product kernel
+        can then norm its input rows itself, see `DeferredNorm`), else None."""
+        return None
+
+
+class DeferredNorm:
+    """A normalised input that has not been computed yet: `norm` applied to the 32-bit rows `source`.  An
+    arrangement hands it, in place of the tensor, to a mixer or feed-forward that says `takes_deferred_norm`;
+    such a part gives it to `parts.linear.linear` as the product's input, which either lets the product's
+    kernel norm the rows as it reads them (a norm with an `rms_record`, few tokens) or calls `tensor()`.
+    `tensor()` runs the norm's own kernel once and returns the rows in the compute element type."""
+
+    def __init__(self, ctx, norm: Norm, source: torch.Tensor, buffer_name: str = "block.x"):
+        self.ctx, self.norm, self.source, self.buffer_name = ctx, norm, source, buffer_name
+        self.shape = source.shape
+        self._tensor = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            out = self.ctx.buffer(self.buffer_name, tuple(self.source.shape), self.norm.runtime.compute_dtype)
+            self.norm.forward(self.ctx, self.source, out)
+            self._tensor = out
+        return self._tensor
+
 
 class PositionEncoding(Part):
     """Owned by a mixer.  Encodes q and k in place of the mixer and appends k, v to the cache."""
@@ -116,6 +141,8 @@ class Mixer(Part):
     # alone; cache and state are still updated for every token).  False: the arrangement runs the mixer for every
     # token and picks the rows afterwards.
     supports_rows = False
+    # True: `x` may be a `DeferredNorm` (the part only ever gives it to `linear`, or calls its `tensor()`).
+    takes_deferred_norm = False
 
     @staticmethod
     def cache_request(params: dict) -> Optional[KVCacheRequest]:
@@ -132,6 +159,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_deferred_norm = False      # as for Mixer
+
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, scale: float):
         """residual += scale * feed_forward(x)."""
         raise NotImplementedError

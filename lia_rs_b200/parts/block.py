@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Arrangement, PartSpec, lookup,
+from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Arrangement, DeferredNorm, PartSpec, lookup,
                    register_arrangement)
 
 
@@ -62,13 +62,16 @@ class PreNormBlock(Arrangement):
             cls(params, tensors, prefix + place, runtime) for (cls, params), place in zip(self._classes(spec), places))
         self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
+    def _normed(self, ctx, norm, part, source):
+        """The input of `part`: `norm(source)`, left to the part's first product where the part can take that."""
+        deferred = DeferredNorm(ctx, norm, source)
+        return deferred if part.takes_deferred_norm else deferred.tensor()
+
     def forward(self, ctx, residual, kv=None, state=None, rows=None, n_rows=None):
-        x = ctx.buffer("block.x", tuple(residual.shape), self.runtime.compute_dtype)
-        self.norm1.forward(ctx, residual, x)
+        x = self._normed(ctx, self.norm1, self.mixer, residual)
         if rows is None:
             self.mixer.forward(ctx, x, residual, self.scale, kv=kv, state=state)
-            self.norm2.forward(ctx, residual, x)
-            self.feed_forward.forward(ctx, x, residual, self.scale)
+            self.feed_forward.forward(ctx, self._normed(ctx, self.norm2, self.feed_forward, residual), residual, self.scale)
             return None
         # Only `rows` matter after this layer (the reference prunes the last layer the same way:
         # src/inference/llama_fusion.rs:45-60): the mixer brings the cache up to date for every token; the output
@@ -83,9 +86,7 @@ class PreNormBlock(Arrangement):
             if n_rows:
                 self.runtime.ops.gather_rows(residual, rows, picked)
         if n_rows:
-            x = x[:n_rows]
-            self.norm2.forward(ctx, picked, x)
-            self.feed_forward.forward(ctx, x, picked, self.scale)
+            self.feed_forward.forward(ctx, self._normed(ctx, self.norm2, self.feed_forward, picked), picked, self.scale)
         return picked
 
 

@@ -15,6 +15,7 @@ from .linear import ACCUM, SWIGLU, linear, prepare_weight
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     graph_safe = True
+    takes_deferred_norm = True
 
     @staticmethod
     def tensor_specs(params, prefix):

@@ -5,8 +5,11 @@
 * a product whose output tiles alone occupy the SMs (the output head, a wide gate/up matrix) goes to the
   persistent tcgen05 kernel (csrc/gemm_tc.cu) at every number of tokens: 73,448 x 2,048 at 8 tokens 59 us
   against 68 us for the few-token kernel, at 24 tokens 60 against 169;
-* otherwise up to 16 tokens the kernel that streams the weights once with no meeting of CTAs
-  (csrc/gemm_skinny.cu); beyond that, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
+* otherwise up to 16 tokens the persistent kernel that keeps the tokens' rows on the SM and streams the
+  weights through a ring (csrc/gemm_stream.cu; a 2B-class layer's four products at 8 tokens: 23.7 us against
+  30.0 for the kernel below), which can also norm its input rows itself (`a` a `DeferredNorm`: no norm
+  kernel runs then); where it does not take the sizes, the kernel that streams the weights once with one
+  CTA per 16 rows (csrc/gemm_skinny.cu); beyond 16 tokens, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
   while it applies (16 tokens of a 2B-class layer: 58 us with the few-token kernel, 63 us with the cluster
   kernel; 24 tokens: 82 against 66; 32 tokens: 91 against 70: every CTA of the few-token kernel reads all the
   tokens' rows from L2); then the persistent tcgen05 kernel, which cuts K through scratch memory up to 128
@@ -18,6 +21,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .base import DeferredNorm
 
 STORE, ACCUM, SWIGLU = ops.GEMM_STORE, ops.GEMM_ACCUM, ops.GEMM_SWIGLU
 
@@ -29,7 +33,7 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 SKINNY_BEST_TOKENS = 16
 
 
-_TC, _SKINNY, _CLUSTER, _SIMT = range(4)
+_TC, _SKINNY, _CLUSTER, _SIMT, _STREAM = range(5)
 _choices = {}          # what decides the choice -> the kernel chosen (the checks cost more than the lookup)
 
 
@@ -38,6 +42,8 @@ def _choose(mode, a, w, out) -> int:
     few = ops.gemm_skinny_accepts(mode, a, w, out)
     if tensor_cores and ops.gemm_tc_tiles_fill_the_sms(a, out):
         return _TC
+    if a.shape[0] <= ops.STREAM_MAX_TOKENS and ops.gemm_stream_accepts(mode, a, w, out):
+        return _STREAM
     if few and a.shape[0] <= SKINNY_BEST_TOKENS:
         return _SKINNY
     if tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
@@ -52,6 +58,23 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     """`name`: what the product is to its caller ("qkv", "down", ...), for the per-kernel-class profile.
     `error_flag` (int32[1] on the device, a step's `ctx.error_flag`): a tensor-core kernel that gives up on one
     of its bounded waits raises it to 3, and the step's caller then learns that the result is not to be used."""
+    if isinstance(a, DeferredNorm):
+        # few tokens of a norm that a product kernel can apply itself: the norm's own kernel does not run
+        record = a.norm.rms_record() if a.source.shape[0] <= ops.STREAM_MAX_TOKENS and w.dtype == torch.bfloat16 else None
+        if record is not None:
+            source, (norm_weight, eps) = a.source, record
+            key = ("norm", mode, source.shape, source.stride(), source.data_ptr() & 15, w.shape, w.stride(), w.data_ptr() & 15,
+                   out.shape[1], out.stride(), out.dtype, norm_weight.dtype, norm_weight.data_ptr() & 15, source.device.index)
+            fused = _choices.get(key)
+            if fused is None:
+                fused = _choices[key] = (norm_weight.is_contiguous() and norm_weight.data_ptr() % 16 == 0
+                                         and norm_weight.dtype in (torch.bfloat16, torch.float32)
+                                         and not ops.gemm_tc_tiles_fill_the_sms(source, out)
+                                         and ops.gemm_stream_accepts(mode, source, w, out, norm=True))
+            if fused:
+                ops.gemm_stream(mode, source, w, out, alpha, error_flag, label=name, norm_weight=norm_weight, eps=eps)
+                return
+        a = a.tensor()
     if a.dtype != torch.bfloat16:
         ops.gemm_simt(mode, a, w, out, alpha, label=name)
         return
@@ -63,6 +86,8 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
         choice = _choices[key] = _choose(mode, a, w, out)
     if choice == _TC:
         ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name)
+    elif choice == _STREAM:
+        ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _SKINNY:
         ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _CLUSTER:

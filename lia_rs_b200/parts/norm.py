@@ -22,3 +22,6 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, out, rows_index=None, out_scale=1.0):
         self.runtime.ops.rmsnorm(x, self.weight, out, self.eps, out_scale, rows_index)
+
+    def rms_record(self):
+        return self.weight, self.eps

@@ -363,6 +363,75 @@ def test_gemm_skinny_all_epilogues_against_64_bit(M, N, K):
         o.gemm_skinny(o.GEMM_STORE, torch.zeros(33, K, device=DEV, dtype=torch.bfloat16), w[:N], torch.empty(33, N, device=DEV))
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 13, 16])
+@pytest.mark.parametrize("N,K", [(40, 64), (200, 192), (2560, 2048), (1000, 6144), (384, 1024), (520, 4096), (77, 8192), (301, 7040),
+                                 (6144, 2048), (24, 2112)])
+def test_gemm_stream_all_epilogues_against_64_bit(M, N, K):
+    """The persistent few-token product: widths that are no multiple of its 16 rows, the forms that keep the
+    tokens' rows in registers (K 1,024, 2,048, 4,096, 6,144) and the one that keeps them in shared memory, K
+    in one chunk and in several, more blocks than SMs so that the ring is used again; and the same product with
+    the RMSNorm of its input rows done inside the kernel."""
+    o = ops()
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if not o.gemm_stream_accepts(o.GEMM_STORE, a, w[:N], torch.empty(M, N, device=DEV)):
+        assert K > 4096                      # the rows of a long K that has no register form leave no room for a ring
+        with pytest.raises(o.KernelError, match="refuses"):
+            o.gemm_stream(o.GEMM_STORE, a, w[:N], torch.empty(M, N, device=DEV), 0.25, flag)
+        return
+    exact = a.double() @ w.double().T
+    scale = max(1.0, float(exact.abs().max()))
+    out = torch.full((M, N), 7.0, device=DEV)
+    o.gemm_stream(o.GEMM_STORE, a, w[:N], out, 0.25, flag)
+    assert float((out.double() - 0.25 * exact[:, :N]).abs().max()) < 2e-5 * scale * math.sqrt(K / 64)
+    half = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_stream(o.GEMM_STORE, a, w[:N], half, 1.0, flag)
+    assert float((half.double() - exact[:, :N]).abs().max()) <= 2.0 ** -8 * scale
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    o.gemm_stream(o.GEMM_ACCUM, a, w[:N], acc, 1.5, flag)
+    assert float((acc.double() - (base.double() + 1.5 * exact[:, :N])).abs().max()) < 5e-5 * scale * math.sqrt(K / 64)
+    act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o.gemm_stream(o.GEMM_SWIGLU, a, w, act, 1.0, flag)
+    gate, up = exact[:, :N], exact[:, N:]
+    want = up * gate / (1 + torch.exp(-gate))
+    assert float((act.double() - want).abs().max()) <= 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    # a view with a row stride of its own, and a shorter ring
+    wide = torch.full((M, N + 3), 7.0, device=DEV)
+    o.gemm_stream(o.GEMM_STORE, a, w[:N], wide[:, 1:N + 1], 0.25, flag, stages_cap=2, early_stages=2)
+    assert torch.equal(wide[:, 1:N + 1], out) and float(wide[:, 0].min()) == 7.0 and float(wide[:, N + 1:].min()) == 7.0
+    # a token's result does not depend on how many other tokens are in the batch
+    alone = torch.empty(1, N, device=DEV)
+    o.gemm_stream(o.GEMM_STORE, a[M - 1:M].contiguous(), w[:N], alone, 0.25, flag)
+    assert torch.equal(alone[0], out[M - 1])
+    # the norm inside the kernel against the norm's own kernel followed by the product
+    rows = torch.randn(M, K, device=DEV) * 3.0
+    for weight in ((1 + 0.2 * torch.randn(K, device=DEV)).to(torch.bfloat16), 1 + 0.2 * torch.randn(K, device=DEV)):
+        if not o.gemm_stream_accepts(o.GEMM_STORE, rows, w[:N], torch.empty(M, N, device=DEV), norm=True):
+            assert K > 4096 or (M > 8 and K > 2048) or K % 1024
+            continue
+        normed = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+        o.rmsnorm(rows, weight, normed, 1e-5)
+        plain = torch.empty(M, N, device=DEV)
+        o.gemm_stream(o.GEMM_STORE, normed, w[:N], plain, 1.0, flag)
+        fused = torch.empty(M, N, device=DEV)
+        o.gemm_stream(o.GEMM_STORE, rows, w[:N], fused, 1.0, flag, norm_weight=weight, eps=1e-5)
+        # the sum of squares is taken in another order than in the norm's kernel: a row may differ in the last
+        # bit of some bfloat16 elements, which moves a sum of K products of size ~1/sqrt(K) by ~2^-9 at most
+        assert float((fused - plain).abs().max()) < 2.0 ** -7 * scale
+        want_rows = rows.double() / torch.sqrt((rows.double() ** 2).mean(dim=1, keepdim=True) + 1e-5) * weight.double()
+        assert float((fused.double() - want_rows @ w[:N].double().T).abs().max()) < 2.0 ** -6 * scale * max(1.0, float(want_rows.abs().max()))
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+    with pytest.raises(o.KernelError, match="refuses"):
+        o.gemm_stream(o.GEMM_STORE, torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w[:N], torch.empty(17, N, device=DEV))
+    with pytest.raises(o.KernelError, match="refuses"):
+        o.gemm_stream(o.GEMM_STORE, torch.zeros(M, 72, device=DEV, dtype=torch.bfloat16),
+                      torch.zeros(N, 72, device=DEV, dtype=torch.bfloat16), torch.empty(M, N, device=DEV))      # K no multiple of 64
+
+
 @pytest.mark.parametrize("M", [1, 16, 33, 40, 64, 100, 128, 200, 300])
 @pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (2560, 2048), (1000, 6144), (384, 96), (2048, 2048), (6144, 2048)])
 def test_gemm_cluster_all_epilogues_against_64_bit(M, N, K):

@@ -60,7 +60,7 @@ def peaks():
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self):
         self.proc = None
@@ -82,21 +82,26 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, top, reasons = [], None, set()
+        # the clocks of an idle GPU say nothing about the timed kernels: only samples taken under load count
+        # (utilisation of at least half; the host-side phases of the run between the timed loops are idle)
+        sm, top, reasons, every = [], None, set(), 0
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
             try:
-                sm.append(float(f[1]))
-                top = float(f[2])
+                clock, top, busy = float(f[1]), float(f[2]), float(f[9])
             except ValueError:
                 continue
+            every += 1
+            if busy < 50.0:
+                continue
+            sm.append(clock)
             for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if value.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": top, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "samples_idle": every - len(sm)}
 
 
 def model_bytes(cfg, layers):

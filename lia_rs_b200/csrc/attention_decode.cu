@@ -12,6 +12,13 @@
 // token to finish (or `attention_merge_kernel`) combines.  Ranges are `split_len` keys long, counted from the
 // first visible key, so how a token's keys are cut depends on its own position, the window and split_len only.
 //
+// Where the ranges of a token are few enough (2, 4, 8 or 16) and all clusters fit on the device at once, the CTAs of
+// a token's ranges form a thread-block cluster and the ranges meet in DISTRIBUTED SHARED MEMORY instead: every CTA
+// leaves its normalised partial output and log-sum-exp in its own shared memory, the cluster synchronises, and
+// CTA r combines every S-th piece of the output over all ranges in ascending order and writes it.  That replaces
+// three dependent trips (partials to global memory, an atomic, the last CTA reading all partials back: 4-5 us
+// of a 13 us kernel at batch 8) by one cluster barrier.
+//
 // The work of this kernel is streaming the cache: 2 * kv_heads * head_dim * 2 bytes per key and token.
 #include "attention_tc.cuh"
 
@@ -38,6 +45,7 @@ struct Params {
     __nv_bfloat16* k_write;          // the pages again, writable
     __nv_bfloat16* v_write;
     int rotary_dim, write_kv, num_pages;
+    int cluster;                     // the CTAs of a token's ranges are one cluster (gridDim.z of them) and merge in shared memory
     int* error_flag;
 };
 
@@ -68,6 +76,81 @@ __device__ __forceinline__ uint32_t transpose_8x8(uint32_t pair) {       // movm
     return out;
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 / 4 bytes of the shared memory of the cluster's CTA `rank`, at the offset that `addr` has in this CTA's.
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_cluster_f(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+constexpr int MAX_CLUSTER = 16;
+// Where a CTA leaves its range's result for the cluster: [16 heads][D] normalised outputs, then [16] log2-sum-exps
+// (minus infinity: the range has no keys), behind the buffers of the four warps' merge.
+template <int D> __device__ __forceinline__ float* exchange_of(uint8_t* smem) {
+    return reinterpret_cast<float*>(smem) + WARPS * 16 * (D + 4 + 3);
+}
+
+// The cluster's CTAs combine their ranges: piece i (four elements of a head) is written by CTA i mod S, which adds
+// the ranges in ascending order, so the result does not depend on which CTA finishes when.  Every thread of every
+// CTA of the cluster calls this once.
+template <int D>
+__device__ __forceinline__ void cluster_merge(const Params& p, uint8_t* smem, int t, int h0, int heads) {
+    cluster_sync_all();                               // every CTA's result is in its exchange buffer
+    const uint32_t rank = cluster_rank();
+    const int S = gridDim.z;
+    const uint32_t base = smem_u32(exchange_of<D>(smem));
+    for (int item = (int)rank + (int)threadIdx.x * S; item < heads * (D / 4); item += S * WARPS * 32) {
+        const int r = item / (D / 4), c4 = item % (D / 4);
+        float l[MAX_CLUSTER];
+        float4 v[MAX_CLUSTER];
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c) {
+            if (c < S) {
+                l[c] = ld_cluster_f(base + (uint32_t)((16 * D + r) * 4), (uint32_t)c);
+                v[c] = ld_cluster_f4(base + (uint32_t)((r * D + c4 * 4) * 4), (uint32_t)c);
+            }
+        }
+        float top = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c)
+            if (c < S) top = fmaxf(top, l[c]);
+        float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < MAX_CLUSTER; ++c) {
+            if (c < S && l[c] > -INFINITY) {            // a range without keys left nothing to read
+                const float w = exp2f(l[c] - top);
+                total += w;
+                acc[0] += w * v[c].x; acc[1] += w * v[c].y; acc[2] += w * v[c].z; acc[3] += w * v[c].w;
+            }
+        }
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+        packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(p.out + ((size_t)t * p.nq + h0 + r) * D + c4 * 4) = packed;
+    }
+    cluster_sync_all();                               // nobody leaves while a neighbour may still read its shared memory
+}
+
 // NH: groups of 8 query heads per kv head that the CTA serves (1 or 2)
 template <int D, int NH>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -96,7 +179,13 @@ attention_decode_kernel(Params p) {
     const int split_len = range_length(p, pos + 1 - first);
     const int key_begin = first + blockIdx.z * split_len;
     const int key_end = min(pos + 1, key_begin + split_len);
-    if (key_begin >= key_end) return;
+    if (key_begin >= key_end) {
+        if (!p.cluster) return;
+        float* exchange = exchange_of<D>(smem);       // a range without keys: it says so and stays for the cluster's merge
+        if (tid < 16) exchange[16 * D + tid] = -INFINITY;
+        cluster_merge<D>(p, smem, t, h0, heads);
+        return;
+    }
     const int* table = p.block_table + (size_t)slot * p.table_stride;
 
     // ---- loading a tile: CHUNKS lanes share a key row; lane j of them looks up the row of pass j ----
@@ -422,7 +511,8 @@ attention_decode_kernel(Params p) {
         const float inv = 1.0f / total;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) merge_f[w * 16 + r] = f[w] * inv;
-        if (p.n_splits > 1)
+        if (p.cluster) exchange_of<D>(smem)[16 * D + r] = top + log2f(total);
+        else if (p.n_splits > 1)
             p.partial[(size_t)p.n_tokens * p.nq * p.n_splits * D + ((size_t)t * p.nq + h0 + r) * p.n_splits + blockIdx.z] =
                 top + log2f(total);
     }
@@ -442,7 +532,9 @@ attention_decode_kernel(Params p) {
                 value.x += share * part.x; value.y += share * part.y; value.z += share * part.z; value.w += share * part.w;
             }
             const int h = h0 + r;
-            if (p.n_splits == 1) {
+            if (p.cluster) {
+                *reinterpret_cast<float4*>(exchange_of<D>(smem) + r * D + c4 * 4) = value;
+            } else if (p.n_splits == 1) {
                 uint2 packed;
                 packed.x = pack_bf16(value.x, value.y);
                 packed.y = pack_bf16(value.z, value.w);
@@ -452,6 +544,10 @@ attention_decode_kernel(Params p) {
                 *reinterpret_cast<float4*>(p.partial + at * D + c4 * 4) = value;
             }
         }
+    }
+    if (p.cluster) {
+        cluster_merge<D>(p, smem, t, h0, heads);
+        return;
     }
     if (p.n_splits == 1 || !p.counters) return;
 
@@ -578,27 +674,115 @@ __global__ void attention_merge_kernel(Params p) {
     }
 }
 
+template <int D>
+size_t decode_smem_bytes() {
+    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4 + 18 * D * 4;   // the tiles, the rotated queries, the angles' cosines and sines, the step's 32-bit rows
+    const size_t merge = (size_t)WARPS * 16 * (D + 4 + 3) * sizeof(float) + (size_t)(16 * D + 16) * sizeof(float);   // the warps' merge, then the cluster's exchange
+    const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
+    return ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
+}
+
+template <int D, int NH>
+int configure_decode() {
+    static int state = 0;                  // 1: done, -1: failed
+    if (state == 0) {
+        state = 1;
+        if (cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes<D>()) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+            cudaGetLastError();
+            state = -1;
+        }
+    }
+    return state == 1 ? LIA_OK : LIA_ERR_LAUNCH;
+}
+
+// Clusters of `size` CTAs of the kernel that the device holds at once (asked of the driver once per size; 0: none).
+template <int D, int NH>
+int max_active_clusters(int size) {
+    static int cached[MAX_CLUSTER + 1] = {};
+    if (size < 2 || size > MAX_CLUSTER) return 0;
+    if (cached[size] == 0) {
+        cached[size] = -1;
+        if (configure_decode<D, NH>() == LIA_OK) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(1, 1, (unsigned)size);
+            config.blockDim = dim3(WARPS * 32);
+            config.dynamicSmemBytes = decode_smem_bytes<D>();
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeClusterDimension;
+            attribute[0].val.clusterDim.x = 1;
+            attribute[0].val.clusterDim.y = 1;
+            attribute[0].val.clusterDim.z = (unsigned)size;
+            config.attrs = attribute;
+            config.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<D, NH>, &config) == cudaSuccess && clusters > 0)
+                cached[size] = clusters;
+            else
+                cudaGetLastError();
+        }
+    }
+    return cached[size] > 0 ? cached[size] : 0;
+}
+
 template <int D, int NH>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
-    const size_t ring = (size_t)STAGES * 2 * Tile<D>::BYTES + 16 * D * 2 + D * 4 + 18 * D * 4;   // the tiles, the rotated queries, the angles' cosines and sines, the step's 32-bit rows
-    const size_t merge = (size_t)WARPS * 16 * (D + 4 + 3) * sizeof(float);
-    const size_t weights = (size_t)16 * (MAX_FUSED_SPLITS + 1) * sizeof(float);
-    const size_t smem = ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return LIA_ERR_LAUNCH;
-        configured = true;
-    }
+    int rc = configure_decode<D, NH>();
+    if (rc != LIA_OK) return rc;
+    const size_t smem = decode_smem_bytes<D>();
     const int group = p.nq / p.nkv;
     dim3 grid(n_rows, p.nkv * ((group + 15) / 16), p.n_splits);
-    int rc = lia_launch(attention_decode_kernel<D, NH>, grid, dim3(WARPS * 32), smem, stream, p);
+    if (p.cluster) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = dim3(WARPS * 32);
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = 1;
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = (unsigned)p.n_splits;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes;
+        config.numAttrs = lia_pdl_enabled.load(std::memory_order_relaxed) ? 2 : 1;
+        lia_launch_counter.fetch_add(1, std::memory_order_relaxed);
+        if (cudaLaunchKernelEx(&config, attention_decode_kernel<D, NH>, p) != cudaSuccess) {
+            cudaGetLastError();
+            return LIA_ERR_LAUNCH;
+        }
+        return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
+    }
+    rc = lia_launch(attention_decode_kernel<D, NH>, grid, dim3(WARPS * 32), smem, stream, p);
     if (rc != LIA_OK) return rc;
     if (p.n_splits > 1 && !p.counters)
         rc = lia_launch(attention_merge_kernel<D>, dim3(n_rows, p.nq), dim3(D < 128 ? D : 128), 0, stream, p);
     return rc;
 }
+
+template <int D>
+int cluster_splits_for(bool wide, int clusters, int wanted) {
+    for (int size = MAX_CLUSTER; size >= 2; size /= 2) {
+        if (size > wanted) continue;
+        const int fit = wide ? max_active_clusters<D, 2>(size) : max_active_clusters<D, 1>(size);
+        if (clusters <= fit) return size;
+    }
+    return 1;
+}
 }  // namespace
+
+// Into how many ranges (2, 4, 8 or 16, at most `wanted`) the kernel can cut the keys of `clusters` (token, head group)
+// pairs with the ranges of a pair as one thread-block cluster, all clusters on the device at once; 1: none, the
+// ranges then meet through scratch memory (or there is one range).
+LIA_EXPORT int lia_attention_decode_cluster_splits(int d, int heads_per_kv_head, int clusters, int wanted) {
+    if (clusters <= 0 || wanted < 2) return 1;
+    const bool wide = heads_per_kv_head > 8;
+    if (d == 128) return cluster_splits_for<128>(wide, clusters, wanted);
+    if (d == 64) return cluster_splits_for<64>(wide, clusters, wanted);
+    if (d == 32) return cluster_splits_for<32>(wide, clusters, wanted);
+    return 1;
+}
 
 // Floats of scratch that n_rows tokens with n_splits ranges need.
 LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, int d, int n_splits) {
@@ -610,6 +794,7 @@ LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, i
 // range rotates the token's key and appends key and value to the page of its position before reading them.
 // Decode attention for the tokens listed in `rows` (indices into the step's batch), bfloat16 only,
 // head_dim 32, 64 or 128 (other sizes: LIA_ERR_SIZE; the caller falls back to the generic kernel).
+// `cluster` non-zero: `n_splits` is what lia_attention_decode_cluster_splits gave; `partial` and `counters` are not used.
 // `n_splits` ranges of `split_len` keys each must cover the longest visible span among the rows;
 // split_len 0 lets every row cut its own span into n_splits ranges (see range_length).
 LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* rows,
@@ -617,14 +802,15 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, const float* qkv, const float* inv_freq, int rotary_dim,
-                                    int write_kv, int num_pages, int* error_flag, cudaStream_t stream) {
+                                    int write_kv, int num_pages, int cluster, int* error_flag, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
         return LIA_ERR_SIZE;
-    if (n_splits > 1 && (!partial || partial_floats < lia_attention_decode_scratch_floats(n_tokens, nq, d, n_splits)))
+    if (cluster && (n_splits < 2 || n_splits > MAX_CLUSTER || (n_splits & (n_splits - 1)))) return LIA_ERR_SIZE;
+    if (!cluster && n_splits > 1 && (!partial || partial_floats < lia_attention_decode_scratch_floats(n_tokens, nq, d, n_splits)))
         return LIA_ERR_SIZE;
-    if (n_splits > 1 && ((uintptr_t)partial & 15u)) return LIA_ERR_ALIGN;
+    if (!cluster && n_splits > 1 && ((uintptr_t)partial & 15u)) return LIA_ERR_ALIGN;
     Params p;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.rows = rows; p.positions = positions; p.slots = slots; p.block_table = block_table;
@@ -635,6 +821,7 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
     p.qkv = qkv; p.inv_freq = inv_freq; p.rotary_dim = rotary_dim; p.write_kv = write_kv; p.num_pages = num_pages;
     p.k_write = (__nv_bfloat16*)const_cast<void*>(k_pages); p.v_write = (__nv_bfloat16*)const_cast<void*>(v_pages);
     p.error_flag = error_flag;
+    p.cluster = cluster ? 1 : 0;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

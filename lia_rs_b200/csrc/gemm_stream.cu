@@ -107,16 +107,6 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
 // The MMA warps and the epilogue warp meet here; the producer does not.
 __device__ __forceinline__ void fill_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(FILL_THREADS) : "memory"); }
 
-#ifdef LIA_STAMPS
-__device__ unsigned long long g_stamps[1 << 16][8];
-__device__ unsigned int g_stamp_slot;
-__device__ long long g_detail[1 << 16][16];
-#define DETAIL(i) do { if (stamp_slot >= 0 && warp == 0 && (i) < 16) g_detail[stamp_slot][i] = clock64(); } while (0)
-#define STAMP(i) do { if (stamp_slot >= 0) g_stamps[stamp_slot][i] = global_timer_ns(); } while (0)
-#else
-#define STAMP(i) do { } while (0)
-#define DETAIL(i) do { } while (0)
-#endif
 
 struct Args {
     const __nv_bfloat16* W;
@@ -267,14 +257,6 @@ gemm_stream_kernel(Args a) {
     constexpr int X_ROWS = NT * 8;
     constexpr int ASKED = XG > 0 ? (MMA_WARPS + 1) * 32 : THREADS;      // the MMA warps (and the epilogue warp) and the producer warp
     constexpr bool NORM_IN_REGISTERS = XG > 0 && XG * NT <= 16;
-#ifdef LIA_STAMPS
-    __shared__ int stamp_slot_s;
-    if (threadIdx.x == 0) {
-        stamp_slot_s = (int)(atomicAdd(&g_stamp_slot, 1u) & 0xffffu);
-        g_stamps[stamp_slot_s][0] = global_timer_ns();
-        g_stamps[stamp_slot_s][7] = ((unsigned long long)MODE << 32) | blockIdx.x;
-    }
-#endif
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < a.stages; ++i) {
@@ -291,10 +273,6 @@ gemm_stream_kernel(Args a) {
     __syncthreads();
     pdl_launch_dependents();
     const int grid = gridDim.x;
-#ifdef LIA_STAMPS
-    long long stamp_clock = 0;
-    const int stamp_slot = (lane == 0 && (warp == 0 || warp == EPILOGUE_WARP || warp == PRODUCER_WARP)) ? stamp_slot_s : -1;
-#endif
 
     if (warp == PRODUCER_WARP) {
         // ---- producer: lane 0 asks; the weights depend on no earlier kernel.  Memory serves requests in order, so
@@ -400,7 +378,6 @@ gemm_stream_kernel(Args a) {
             if (lane == 0) mbar_arrive(smem_u32(&sums_empty[buf]));
         }
         if (!ok && lane == 0 && a.error_flag) atomicExch(a.error_flag, 3);
-        STAMP(5);
     } else {
         // ---- eight MMA warps: each takes every eighth group of 32 k ----
         const int g = lane >> 2, t = lane & 3;
@@ -430,7 +407,6 @@ gemm_stream_kernel(Args a) {
                 }
             }
             pdl_wait();                               // the tokens' rows come from the kernel ahead
-            if (warp == 0) STAMP(1);
             if (!(NORM_IN_REGISTERS && normed)) {
 #pragma unroll
                 for (int r = 0; r < XR; ++r) {
@@ -515,12 +491,10 @@ gemm_stream_kernel(Args a) {
             }
         } else {
             pdl_wait();
-            if (warp == 0) STAMP(1);
             asked_arrive<ASKED>();
             fill_rows<X_ROWS>(a, x_s, (int)threadIdx.x, lane);
             fill_barrier();
         }
-        if (warp == 0) STAMP(2);
         const uint8_t* x_base = x_s + (size_t)g * a.x_pitch + t * 16;       // XG == 0: token g's part for this lane
         (void)x_base;
 
@@ -541,10 +515,6 @@ gemm_stream_kernel(Args a) {
                 for (int c = 0; c < (CHUNKS > 0 ? CHUNKS : 1); ++c) {
                     const int st = it % a.stages;
                     if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / a.stages) & 1u)) { ok = false; break; }
-#ifdef LIA_STAMPS
-                    if (warp == 0 && it == 0) { STAMP(3); stamp_clock = clock64(); }
-#endif
-                    DETAIL(it * 3);
                     const uint8_t* stage = smem + (size_t)st * a.stage_bytes + w_offset + warp * 64;
 #pragma unroll
                     for (int i0 = 0; i0 < PWR; i0 += 4) {
@@ -567,7 +537,6 @@ gemm_stream_kernel(Args a) {
                             }
                         }
                     }
-                    DETAIL(it * 3 + 1);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&empty_bar[st]));
                     ++it;
@@ -578,9 +547,6 @@ gemm_stream_kernel(Args a) {
                     const int k0 = c * a.ck;
                     const int groups = min(groups_per_chunk, (a.K - k0) >> 5);      // K is a multiple of 64: whole groups
                     if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / a.stages) & 1u)) { ok = false; break; }
-#ifdef LIA_STAMPS
-                    if (warp == 0 && it == 0) { STAMP(3); stamp_clock = clock64(); }
-#endif
                     const uint8_t* stage = smem + (size_t)st * a.stage_bytes + w_offset;
                     const uint8_t* xk = x_base + (size_t)k0 * 2;
                     for (int base = warp; base < groups; base += 4 * MMA_WARPS) {
@@ -633,12 +599,8 @@ gemm_stream_kernel(Args a) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sums_full[buf]));
-            DETAIL((it - 1) * 3 + 2);
         }
         if (!ok && lane == 0 && a.error_flag) atomicExch(a.error_flag, 3);
-#ifdef LIA_STAMPS
-        if (warp == 0) { STAMP(4); if (stamp_slot >= 0) g_stamps[stamp_slot][6] = (unsigned long long)(clock64() - stamp_clock); }
-#endif
     }
     // Nobody leaves while a copy may still be in flight into this CTA's shared memory: in a run without a
     // failed wait every stage asked for has been waited for by the MMA warps; after a failure thread 0 waits,
@@ -735,20 +697,6 @@ void plan(int mode, int M, int N, int K, bool with_norm, int sms, int* stages, i
 }
 }  // namespace
 
-#ifdef LIA_STAMPS
-LIA_EXPORT int lia_stamps_read(unsigned long long* host, int slots) {
-    unsigned int n = 0;
-    cudaMemcpyFromSymbol(&n, g_stamp_slot, sizeof(n));
-    cudaMemcpyFromSymbol(host, g_stamps, sizeof(unsigned long long) * 8 * slots);
-    unsigned int zero = 0;
-    cudaMemcpyToSymbol(g_stamp_slot, &zero, sizeof(zero));
-    return (int)n;
-}
-LIA_EXPORT int lia_detail_read(long long* host, int slots) {
-    cudaMemcpyFromSymbol(host, g_detail, sizeof(long long) * 16 * slots);
-    return 0;
-}
-#endif
 
 // Whether (and with how many stages) the kernel takes M tokens of K elements on a device of `sms` SMs for a
 // product of N features: 0 when K is not a multiple of 64, when the tokens' rows leave no room for a ring of two
@@ -765,7 +713,7 @@ LIA_EXPORT int lia_gemm_stream_stages(int mode, int M, int N, int K, int with_no
 // (row stride ldo).  Refuses K that is not a multiple of 64, ldw or ldx that are not multiples of 8 elements,
 // pointers that are not 16-byte aligned (bulk copies and 16-byte loads need both), and sizes whose rows do not
 // fit in shared memory beside a ring (ask lia_gemm_stream_stages first).  `stages_cap` > 0 limits the ring;
-// `early_stages` > 0 sets how many stages the producer asks for before the tokens' rows have been asked for (default 1).
+// `early_stages` > 0 sets how many stages the producer asks for before the tokens' rows have been asked for (default 2).
 LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                int ldo, int M, int N, int K, float alpha, const float* norm_src, int ld_norm,
                                const void* norm_weight, int norm_weight_dtype, float eps, int sms, int stages_cap,
@@ -802,7 +750,7 @@ LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, 
     plan(mode, M, N, K, norm_src != nullptr, sms, &a.stages, &form_chunks, &form_pw);
     if (a.stages <= 0) return LIA_ERR_SIZE;
     if (stages_cap > 0 && a.stages > stages_cap) a.stages = stages_cap;
-    a.early = early_stages > 0 ? early_stages : 1;
+    a.early = early_stages > 0 ? early_stages : 2;
     if (mode == GEMM_STORE) return launch_form<GEMM_STORE>(a, form_chunks, form_pw, ctas, stream);
     if (mode == GEMM_ACCUM) return launch_form<GEMM_ACCUM>(a, form_chunks, form_pw, ctas, stream);
     return launch_form<GEMM_SWIGLU>(a, form_chunks, form_pw, ctas, stream);

@@ -51,7 +51,8 @@ class _Signatures:
     lia_wait_probe = [c_int, c_void_p, c_void_p, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lia_attention_decode_cluster_splits = [c_int, c_int, c_int, c_int]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
     lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -432,7 +433,7 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
-                     error_flag=None, label=None, work_bytes=0):
+                     error_flag=None, label=None, work_bytes=0, cluster=False):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
@@ -441,7 +442,9 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
     128 ranges) a second kernel does.  With `qkv` (32-bit q|k|v rows of the step, at most 16 query heads per
     kv head) `q` may be None: the kernel takes the queries from `qkv`, applies the rotary encoding
     (`inv_freq`, `rotary_dim`; 0: none) and, if `write_kv`, appends each token's key and value to the cache
-    itself, so no separate position-encoding kernel runs."""
+    itself, so no separate position-encoding kernel runs.  `cluster`: `n_splits` came from
+    `attention_decode_cluster_splits`; the ranges of a token then meet in distributed shared memory and neither
+    `partial` nor `counters` is used."""
     _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters, qkv, inv_freq, error_flag)
     if qkv is not None:
         if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
@@ -457,8 +460,15 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
                                           _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
                                           0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
                                           k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
-                                          int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], _p(error_flag), _stream()),
+                                          int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], 1 if cluster else 0, _p(error_flag),
+                                          _stream()),
                "attention_decode")
+
+
+def attention_decode_cluster_splits(d: int, group: int, clusters: int, wanted: int) -> int:
+    """Ranges per token (2, 4, 8 or 16, at most `wanted`) with which `attention_decode(..., cluster=True)` can
+    serve `clusters` (token, head group) pairs at once; 1: it cannot (one range, or too many clusters for the device)."""
+    return int(lib().lia_attention_decode_cluster_splits(d, group, clusters, wanted))
 
 
 def attention_prefill_tokens_per_tile(group: int) -> int:

@@ -52,6 +52,7 @@ class PagedAttention:
                   f"{ops.DECODE_HEAD_DIMS}", file=sys.stderr, flush=True)
         self.rotate_half = rotate_half if (self.variant == "tensor" and self.group <= 16) else None
         self._prefill = None          # (kernel, tokens per tile), asked of the library at the first prompt portion
+        self._decode_plans = {}       # (rows, wanted ranges) -> (ranges, as clusters)
 
     # ---- how a decode row's keys are cut ----
     def decode_splits(self, ctx, rows: int) -> int:
@@ -64,6 +65,18 @@ class PagedAttention:
         ctas = max(1, rows * groups)
         wanted = (2 * ctx.runtime.sm_count) // ctas
         return max(1, min(wanted, 32, ctx.context_bucket // 256))
+
+    def decode_plan(self, ctx, rows: int):
+        """(ranges per token, whether a token's ranges form a thread-block cluster).  As clusters (2, 4, 8 or 16
+        ranges, all clusters on the device at once) the ranges meet in distributed shared memory; otherwise
+        through scratch memory, the CTA that finishes a token last combining them."""
+        wanted = self.decode_splits(ctx, rows)
+        plan = self._decode_plans.get((rows, wanted))
+        if plan is None:
+            groups = self.nkv * ((self.group + 15) // 16)
+            clustered = ops.attention_decode_cluster_splits(self.d, self.group, rows * groups, wanted) if wanted >= 2 else 1
+            plan = self._decode_plans[(rows, wanted)] = (clustered, True) if clustered >= 2 else (wanted, False)
+        return plan
 
     def _decode_scratch(self, ctx, rows: int, n_splits: int):
         if n_splits <= 1:
@@ -121,11 +134,11 @@ class PagedAttention:
                                       d, self.window, self.scale, rows=ctx.prefill_rows, error_flag=ctx.error_flag)
 
     def _decode(self, ctx, q, kv, out, rows, n_rows, work_bytes=0):
-        n_splits = self.decode_splits(ctx, n_rows)
-        partial, counters = self._decode_scratch(ctx, n_rows, n_splits)
+        n_splits, clustered = self.decode_plan(ctx, n_rows)
+        partial, counters = (None, None) if clustered else self._decode_scratch(ctx, n_rows, n_splits)
         ops.attention_decode(q, kv.k_pages, kv.v_pages, rows, ctx.positions, ctx.slots, kv.block_table, out, partial,
                              self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
-                             error_flag=ctx.error_flag, work_bytes=work_bytes)
+                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered)
 
     def forward_fused(self, ctx, qkv, kv, out) -> bool:
         """For a step of single decoded tokens and a rotate-half (or no) position encoding: encoding of q and k,
@@ -134,10 +147,10 @@ class PagedAttention:
         if self.rotate_half is None or not ctx.decode_only or kv.k_pages.dtype != torch.bfloat16:
             return False
         rotary_dim, inv_freq = self.rotate_half
-        n_splits = self.decode_splits(ctx, ctx.n_tokens)
-        partial, counters = self._decode_scratch(ctx, ctx.n_tokens, n_splits)
+        n_splits, clustered = self.decode_plan(ctx, ctx.n_tokens)
+        partial, counters = (None, None) if clustered else self._decode_scratch(ctx, ctx.n_tokens, n_splits)
         ops.attention_decode(None, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table,
                              out, partial, self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
                              qkv=qkv, inv_freq=inv_freq, rotary_dim=rotary_dim, write_kv=kv.writes,
-                             error_flag=ctx.error_flag, label="fused", work_bytes=self._work(ctx, 2)[0])
+                             error_flag=ctx.error_flag, label="fused", work_bytes=self._work(ctx, 2)[0], cluster=clustered)
         return True

@@ -486,7 +486,8 @@ def test_gemm_tc_refuses_what_tma_cannot_address():
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,split_len", [
     (128, 16, 2, 16, None, 128), (128, 16, 2, 16, None, 4096), (64, 16, 2, 4, None, 64), (32, 3, 1, 16, 100, 64),
-    (64, 40, 2, 8, None, 192), (128, 32, 2, 32, 700, 256), (32, 8, 8, 16, None, 64), (64, 6, 3, 12, None, 128)])
+    (64, 40, 2, 8, None, 192), (128, 32, 2, 32, 700, 256), (32, 8, 8, 16, None, 64), (64, 6, 3, 12, None, 128),
+    (128, 16, 2, 16, None, 384), (128, 16, 2, 16, None, 768), (64, 6, 3, 12, 500, 128)])
 @pytest.mark.parametrize("fused", [True, False])
 def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len, fused):
     """Tensor-core decode attention: groups of up to 16 query heads per kv head, ranges of keys merged,
@@ -535,6 +536,19 @@ def test_attention_decode_split_keys(d, nq, nkv, page_size, window, split_len, f
     assert error <= 1.6e-2 * max(1.0, float(want.abs().max())), error
     assert float((out[4].float() - 7.0).abs().max()) == 0
     assert float((got[-1, 0] - v[far, 0].double()).abs().max()) < 0.05
+    # the same ranges as thread-block clusters, meeting in distributed shared memory: the ranges are normalised and
+    # added in the same order as through scratch memory, so the bits are the same
+    if n_splits in (2, 4, 8, 16) and fused:
+        fit = ops().attention_decode_cluster_splits(d, nq // nkv, n * nkv * ((nq // nkv + 15) // 16), n_splits)
+        assert fit in (1, 2, 4, 8, 16) and fit <= n_splits
+        if fit == n_splits:
+            clustered = torch.full((n, nq * d), 7.0, device=DEV, dtype=torch.bfloat16)
+            ops().attention_decode(q.view(n, nq * d), kp, vp, rows, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                                   torch.ones(n, dtype=torch.int32, device=DEV), bt.to(DEV), clustered, None, nq, nkv, d, window,
+                                   scale, split_len, n_splits, None, cluster=True)
+            assert float((clustered[4].float() - 7.0).abs().max()) == 0
+            difference = float((clustered[keep].float() - out[keep].float()).abs().max())
+            assert difference <= 2.0 ** -7 * max(1.0, float(want.abs().max())), difference
 
 
 @pytest.mark.parametrize("kernel", ["mma.sync", "tcgen05"])
@@ -604,7 +618,8 @@ def test_attention_prefill_portions(d, nq, nkv, page_size, window, kernel):
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,rotary_dim,n_splits", [
     (128, 16, 2, 16, None, 128, 5), (64, 12, 3, 8, None, 64, 1), (32, 3, 1, 16, 50, 16, 3), (128, 4, 4, 32, 300, 0, 2),
-    (64, 32, 2, 4, None, 32, 7)])
+    (64, 32, 2, 4, None, 32, 7), (128, 16, 2, 16, None, 128, 16), (128, 16, 2, 16, None, 128, 8), (64, 32, 2, 4, None, 32, 4),
+    (32, 3, 1, 16, 50, 16, 2), (64, 8, 2, 8, 100, 64, 4)])
 def test_attention_decode_with_rotary_and_append(d, nq, nkv, page_size, window, rotary_dim, n_splits):
     """The decode attention kernel that also encodes positions and appends the token's key and value,
     against the two separate kernels: the same pages afterwards, the same output (each token at another
@@ -660,3 +675,13 @@ def test_attention_decode_with_rotary_and_append(d, nq, nkv, page_size, window, 
     assert flag.item() == 0
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
     assert torch.equal(out1, out2)
+    # and with the ranges of a token as a cluster (ranges beyond a short context have no keys and still take part)
+    if n_splits in (2, 4, 8, 16) and o.attention_decode_cluster_splits(d, nq // nkv, n * nkv, n_splits) == n_splits:
+        k3, v3 = kp.clone(), vp.clone()
+        out3 = torch.empty(n, nq * d, device=DEV, dtype=torch.bfloat16)
+        o.attention_decode(None, k3, v3, rows, pos, slots, bt, out3, None, nq, nkv, d, window, scale, 0, n_splits, None,
+                           qkv=qkv, inv_freq=inv, rotary_dim=rotary_dim, write_kv=True, error_flag=flag, cluster=True)
+        torch.cuda.synchronize()
+        assert flag.item() == 0
+        assert torch.equal(k1, k3) and torch.equal(v1, v3)
+        assert float((out3.float() - out1.float()).abs().max()) <= 2.0 ** -7 * max(1.0, float(out1.float().abs().max()))

@@ -19,17 +19,21 @@ pages per kind of need, and slots of fixed-size per-request state.
   reference uploads the whole table before each step and waits (src/inference/paging.rs:224-237).
   A table entry of -1 means "no page" (never allocated, or passed by the window).
 
-The manager is pure bookkeeping plus tensors; it runs on the CPU device too, which is how its
-tests exercise it without a GPU.
+The bookkeeping (pools, the tables of every slot, what an `ensure` has to allocate and give back, which table
+rows changed) is native: csrc/host/cache_host.cpp, one object for all groups of a manager; the classes here are
+its faces and own the tensors.  The manager runs on the CPU device too, which is how its tests exercise it
+without a GPU.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Optional
 
+import ctypes
+
 import torch
 
-from .pages import PageError, PagePool
+from .pages import PageError, host_library, raise_last
 
 
 @dataclass
@@ -54,110 +58,106 @@ class _NoFence:
         pass
 
 
+class _PoolFace:
+    """What `group.pool` answers: the pool of one group of the native cache."""
+
+    def __init__(self, group):
+        self._group = group
+        self.num_pages = group.num_pages
+
+    def available(self) -> int:
+        return self._group._lib.lia_cache_available(self._group._native(), self._group.index)
+
+    def in_use(self) -> int:
+        return self.num_pages - self.available()
+
+
+class _Tables:
+    """`group.tables[slot]`: the page of each logical block of the slot (a list; -1: given back)."""
+
+    def __init__(self, group):
+        self._group = group
+
+    def __getitem__(self, slot):
+        group = self._group
+        out = (ctypes.c_int * group.max_blocks)()
+        n = group._lib.lia_cache_table(group._native(), group.index, int(slot), out, group.max_blocks)
+        if n < 0:
+            raise_last()
+        return list(out[:n])
+
+    def __len__(self):
+        return self._group.max_slots
+
+    def __iter__(self):
+        return (self[slot] for slot in range(self._group.max_slots))
+
+
+class _FirstBlocks:
+    def __init__(self, group):
+        self._group = group
+
+    def __getitem__(self, slot):
+        return self._group._lib.lia_cache_first_block(self._group._native(), self._group.index, int(slot))
+
+
 class CacheGroup:
     RING = 3          # staging snapshots in flight: one per step the host may run ahead of the device, and one to spare
 
     def __init__(self, index, request, cache_ids, num_pages, page_size, max_slots, max_blocks, dtype, device):
         self.index, self.request, self.cache_ids = index, request, list(cache_ids)
         self.page_size, self.window = page_size, request.window
-        self.pool = PagePool(num_pages)
-        self.tables = [[] for _ in range(max_slots)]       # per slot: page of each logical block, or -1
-        self.first_block = [0] * max_slots                 # blocks before this were given back
+        self.num_pages, self.max_slots, self.max_blocks = num_pages, max_slots, max_blocks
+        self._lib = host_library()
+        self._owner = None                                 # the manager, which holds the native cache of all its groups
+        self.pool = _PoolFace(self)
+        self.tables = _Tables(self)                        # per slot: page of each logical block, or -1
+        self.first_block = _FirstBlocks(self)              # blocks before this were given back
         shape = (num_pages, page_size, request.kv_heads, request.head_dim)
         self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
         self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
         pin = torch.device(device).type == "cuda"
-        self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32)      # the live table
-        self.host_view = self.host_table.numpy()           # the same memory: single entries are written through this
+        # the live table: the native cache writes the entries it changes straight into this memory
+        self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, pin_memory=pin)
+        self.host_view = self.host_table.numpy()
         self.device_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, device=device)
-        self.dirty = {}                                    # slot -> (lo, hi) block range to copy
+        self._dirty = (ctypes.c_int * (3 * max_slots))()
         # what the asynchronous copies read: snapshots of the dirty ranges, taken at flush()
         self._staging = [torch.empty(max_slots * max_blocks, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
         self._staging_views = [t.numpy() for t in self._staging]
         self._fences = [torch.cuda.Event() if pin else _NoFence() for _ in range(self.RING)]
         self._turn = 0
 
-    def _mark(self, slot, block):
-        lo, hi = self.dirty.get(slot, (block, block + 1))
-        self.dirty[slot] = (min(lo, block), max(hi, block + 1))
-
-    def pages_needed(self, slot, start, end):
-        """(blocks to allocate, blocks to give back, first block kept) for positions [start, end).
-        The blocks of a slot's table from `first_block` on are all present (blocks are only ever given
-        back from the front, and allocated without gaps), so only the table's ends are looked at: a
-        decode step costs the same whatever the context length."""
-        ps = self.page_size
-        table = self.tables[slot]
-        n, first = len(table), self.first_block[slot]
-        keep_from = 0
-        if self.window is not None:
-            keep_from = max(0, start - self.window + 1) // ps
-        give_back = [b for b in range(first, min(keep_from, n)) if table[b] >= 0]
-        last = (end - 1) // ps
-        allocate = [b for b in range(keep_from, min(first, last + 1))]        # given back earlier, wanted again
-        allocate += [b for b in range(max(keep_from, n), last + 1)]           # beyond the table's end
-        return allocate, give_back, keep_from
-
-    def pages_needed_by_scan(self, slot, start, end):
-        """The same by looking at every block (what `check` compares `pages_needed` with)."""
-        ps = self.page_size
-        table = self.tables[slot]
-        keep_from = 0
-        if self.window is not None:
-            keep_from = max(0, start - self.window + 1) // ps
-        give_back = [b for b in range(self.first_block[slot], min(keep_from, len(table))) if table[b] >= 0]
-        last = (end - 1) // ps
-        allocate = [b for b in range(max(keep_from, 0), last + 1) if b >= len(table) or table[b] < 0]
-        return allocate, give_back, keep_from
-
-    def apply(self, slot, allocate, give_back, keep_from):
-        table = self.tables[slot]
-        for b in give_back:
-            self.pool.release(table[b])
-            table[b] = -1
-            self.host_view[slot, b] = -1
-            self._mark(slot, b)
-        self.first_block[slot] = max(self.first_block[slot], min(keep_from, len(table)))
-        for b in allocate:
-            while len(table) <= b:
-                table.append(-1)
-            page = self.pool.allocate()
-            table[b] = page
-            self.host_view[slot, b] = page
-            self._mark(slot, b)
-
-    def release_slot(self, slot):
-        table = self.tables[slot]
-        for b, page in enumerate(table):
-            if page >= 0:
-                self.pool.release(page)
-        if table:
-            self.host_view[slot, :len(table)] = -1
-            self.dirty[slot] = (0, max(len(table), self.dirty.get(slot, (0, 0))[1]))
-        self.tables[slot] = []
-        self.first_block[slot] = 0
+    def _native(self):
+        return self._owner._handle
 
     def held_pages(self):
         return [p for table in self.tables for p in table if p >= 0]
+
+    def held_by(self, slot) -> int:
+        """Pages that the slot holds in this group."""
+        return self._lib.lia_cache_held(self._native(), self.index, int(slot))
 
     @staticmethod
     def _copy(destination, source):
         destination.copy_(source, non_blocking=True)
 
     def flush(self):
-        if not self.dirty:
+        n = self._lib.lia_cache_take_dirty(self._native(), self.index, self._dirty, self.max_slots)
+        if n <= 0:
             return
         self._turn = (self._turn + 1) % self.RING
         staging, view, fence = self._staging[self._turn], self._staging_views[self._turn], self._fences[self._turn]
         fence.synchronize()                                # the copies that read this buffer last have run
         at = 0
-        for slot, (lo, hi) in self.dirty.items():
+        dirty = self._dirty
+        for i in range(n):
+            slot, lo, hi = dirty[3 * i], dirty[3 * i + 1], dirty[3 * i + 2]
             count = hi - lo
             view[at:at + count] = self.host_view[slot, lo:hi]
             self._copy(self.device_table[slot, lo:hi], staging[at:at + count])
             at += count
         fence.record()
-        self.dirty = {}
 
 
 class CacheManager:
@@ -176,12 +176,28 @@ class CacheManager:
             by_need.setdefault(request, []).append(cache_id)
         self.groups = [CacheGroup(i, request, ids, num_pages, page_size, max_slots, self.max_blocks, dtype, device)
                        for i, (request, ids) in enumerate(by_need.items())]
+        self._lib = host_library()
+        n = len(self.groups)
+        IntArray, PointerArray = ctypes.c_int * max(1, n), ctypes.c_void_p * max(1, n)
+        self._handle = ctypes.c_void_p(self._lib.lia_cache_create(
+            n, IntArray(*[num_pages] * n), IntArray(*[page_size] * n),
+            IntArray(*[-1 if g.window is None else int(g.window) for g in self.groups]), max_slots, self.max_blocks,
+            PointerArray(*[g.host_table.data_ptr() for g in self.groups])))
+        if not self._handle:
+            raise_last()
+        for group in self.groups:
+            group._owner = self
         self.group_of = {c: g for g in self.groups for c in g.cache_ids}
         self.states = {sid: torch.zeros((max_slots, *req.shape), dtype=req.dtype, device=device)
                        for sid, req in state_requests.items()}
         self._free_slots = list(range(max_slots - 1, -1, -1))
         self._live = set()
         self.length = [0] * max_slots          # positions [0, length) have been ensured
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.lia_cache_destroy(handle)
 
     # ---- slots ----
     def free_slots(self) -> int:
@@ -204,8 +220,8 @@ class CacheManager:
     def release(self, slot: int) -> None:
         if slot not in self._live:
             raise PageError(f"slot {slot} released twice or never admitted")
-        for group in self.groups:
-            group.release_slot(slot)
+        if self._lib.lia_cache_release_slot(self._handle, int(slot)) < 0:
+            raise_last()
         self._live.remove(slot)
         self._free_slots.append(slot)
         self.length[slot] = 0
@@ -218,12 +234,9 @@ class CacheManager:
     def pages_for(self, slot: int, start: int, end: int) -> int:
         """How many free pages `ensure(slot, start, end)` would need in the tightest group,
         counting the pages it would first give back."""
-        if all(group.window is None and (end - 1) // group.page_size < len(group.tables[slot]) for group in self.groups):
-            return 0                                              # every position already has its page
-        worst = 0
-        for group in self.groups:
-            allocate, give_back, _ = group.pages_needed(slot, start, end)
-            worst = max(worst, len(allocate) - len(give_back))
+        worst = self._lib.lia_cache_pages_for(self._handle, int(slot), int(start), int(end))
+        if worst < 0:
+            raise_last()
         return worst
 
     def ensure(self, slot: int, start: int, end: int) -> bool:
@@ -233,19 +246,12 @@ class CacheManager:
             raise PageError(f"slot {slot} is not live")
         if not 0 <= start < end or end > self.max_context:
             raise PageError(f"positions [{start}, {end}) are outside the context of {self.max_context}")
-        if all(group.window is None and (end - 1) // group.page_size < len(group.tables[slot]) for group in self.groups):
-            self.length[slot] = max(self.length[slot], end)      # every position already has its page (most decode steps)
-            return True
-        plans = []
-        for group in self.groups:
-            allocate, give_back, keep_from = group.pages_needed(slot, start, end)
-            if len(allocate) - len(give_back) > group.pool.available():
-                return False
-            plans.append((group, allocate, give_back, keep_from))
-        for group, allocate, give_back, keep_from in plans:
-            group.apply(slot, allocate, give_back, keep_from)
-        self.length[slot] = max(self.length[slot], end)
-        return True
+        done = self._lib.lia_cache_ensure(self._handle, int(slot), int(start), int(end))
+        if done < 0:
+            raise_last()
+        if done:
+            self.length[slot] = max(self.length[slot], end)
+        return bool(done)
 
     def flush(self) -> None:
         """Copy changed block-table rows to the device (asynchronous from pinned memory)."""
@@ -262,19 +268,17 @@ class CacheManager:
 
     def check(self) -> None:
         """Assert the invariants: no page lost, none held twice, none both free and held."""
+        live = sorted(self._live)
+        Array = ctypes.c_int * max(1, len(live))
         for group in self.groups:
-            held = group.held_pages()
-            if len(set(held)) != len(held):
-                raise PageError(f"group {group.index}: a page is held twice")
-            group.pool.check(held)
-            for slot in self._live:                          # the table's shape that pages_needed relies on
-                table, first = group.tables[slot], group.first_block[slot]
-                if any(p >= 0 for p in table[:first]) or any(p < 0 for p in table[first:]):
-                    raise PageError(f"group {group.index}, slot {slot}: the block table has a gap")
-                probe = (self.length[slot], self.length[slot] + 1)
-                if self.length[slot] < self.max_context and \
-                        group.pages_needed(slot, *probe) != group.pages_needed_by_scan(slot, *probe):
-                    raise PageError(f"group {group.index}, slot {slot}: pages_needed disagrees with a scan of the table")
+            if self._lib.lia_cache_check(self._handle, group.index, Array(*live), Array(*[self.length[s] for s in live]),
+                                         len(live), self.max_context) < 0:
+                raise_last()
+            # the host table (what goes to the device) says what the tables say
+            for slot in live:
+                table = group.tables[slot]
+                if group.host_view[slot, :len(table)].tolist() != table:
+                    raise PageError(f"group {group.index}, slot {slot}: the host table differs from the slot's table")
         if len(set(self._free_slots)) != len(self._free_slots) or set(self._free_slots) & self._live:
             raise PageError("a slot is both free and live, or free twice")
         if len(self._free_slots) + len(self._live) != self.max_slots:

@@ -159,7 +159,7 @@ class Scheduler:
             self._preempt(victim)
 
     def _pages_held(self, request: Request) -> int:
-        return max(sum(1 for p in group.tables[request.slot] if p >= 0) for group in self.cache.groups) \
+        return max(group.held_by(request.slot) for group in self.cache.groups) \
             if self.cache.groups else 0
 
     def _preempt(self, request: Request) -> None:

@@ -1,4 +1,5 @@
-"""Compile the CUDA sources under csrc/ for sm_100a into one shared library and load it.
+"""Compile the CUDA sources under csrc/ for sm_100a into one shared library and load it; and the host-only C++
+sources under csrc/host/ (the cache's bookkeeping) into a second one that needs no CUDA.
 
 The library is plain CUDA with C entry points (no Python or torch headers), so a build takes
 seconds per file.  It is built at the first call that needs it, in `_build/` inside the package
@@ -135,3 +136,66 @@ def load() -> ctypes.CDLL:
         except OSError as error:
             raise KernelBuildError(f"cannot load {path}: {error}") from error
     return _LIBRARY
+
+
+# ---- the host-only library (csrc/host/*.cpp): plain C++, no CUDA, so it also serves the CPU-only tests ----
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+_HOST_LIBRARY = None
+
+
+def _host_compiler() -> str:
+    for candidate in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if candidate and (os.path.exists(candidate) or shutil.which(candidate)):
+            return candidate
+    raise KernelBuildError("no C++ compiler found (set CXX); the cache's host library cannot be built")
+
+
+def host_sources() -> list:
+    return sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
+
+
+def host_library_path() -> str:
+    h = hashlib.sha256()
+    for path in host_sources() + sorted(glob.glob(os.path.join(HOST_DIR, "*.h"))):
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return os.path.join(_build_dir(), f"liblia_host_{h.hexdigest()[:16]}.so")
+
+
+def build_host(verbose: bool = True) -> str:
+    target = host_library_path()
+    if os.path.exists(target):
+        return target
+    partial = target + f".tmp{os.getpid()}"
+    if verbose:
+        print(f"[lia_rs_b200] compiling the host library into {os.path.dirname(target)} (first call only)", file=sys.stderr, flush=True)
+    done = subprocess.run([_host_compiler(), *HOST_FLAGS, "-o", partial, *host_sources()],
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if done.returncode != 0:
+        raise KernelBuildError("the host library failed to compile:\n" + done.stdout)
+    os.replace(partial, target)
+    for stale in glob.glob(os.path.join(os.path.dirname(target), "liblia_host_*.so")):
+        if stale != target:
+            try:
+                os.remove(stale)
+            except OSError:
+                pass
+    return target
+
+
+def load_host() -> ctypes.CDLL:
+    """The loaded host library (the cache's native bookkeeping); builds it first if needed."""
+    global _HOST_LIBRARY
+    if _HOST_LIBRARY is None:
+        path = build_host()
+        try:
+            _HOST_LIBRARY = ctypes.CDLL(path)
+        except OSError as error:
+            raise KernelBuildError(f"cannot load {path}: {error}") from error
+        _HOST_LIBRARY.lia_host_error.restype = ctypes.c_char_p
+        for name in ("lia_pool_create", "lia_cache_create"):
+            getattr(_HOST_LIBRARY, name).restype = ctypes.c_void_p
+    return _HOST_LIBRARY

@@ -2,14 +2,16 @@
 
 `prepare_weight` brings a checkpoint matrix to the compute element type once, at load.
 `linear` chooses the kernel for a bfloat16 product (measured on a B200, in TB/s of weights streamed):
-* a product whose output tiles alone occupy the SMs (the output head, a wide gate/up matrix) goes to the
-  persistent tcgen05 kernel (csrc/gemm_tc.cu) at every number of tokens: 73,448 x 2,048 at 8 tokens 59 us
-  against 68 us for the few-token kernel, at 24 tokens 60 against 169;
-* otherwise up to 16 tokens the persistent kernel that keeps the tokens' rows on the SM and streams the
-  weights through a ring (csrc/gemm_stream.cu; a 2B-class layer's four products at 8 tokens: 23.7 us against
-  30.0 for the kernel below), which can also norm its input rows itself (`a` a `DeferredNorm`: no norm
-  kernel runs then); where it does not take the sizes, the kernel that streams the weights once with one
-  CTA per 16 rows (csrc/gemm_skinny.cu); beyond 16 tokens, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
+* up to 16 tokens the persistent kernel that keeps the tokens' rows on the SM and streams the weights
+  through a ring (csrc/gemm_stream.cu; a 2B-class layer's four products at 8 tokens: 23.7 us against 30.0 for
+  the one-CTA-per-16-rows kernel below; the output head, 73,448 x 2,048, at 8 tokens: 47.6 us = 6.3 TB/s against
+  60.3 us for the tcgen05 kernel), which can also norm its input rows itself (`a` a `DeferredNorm`: no norm
+  kernel runs then);
+* beyond that, a product whose output tiles alone occupy the SMs (the output head, a wide gate/up matrix) goes
+  to the persistent tcgen05 kernel (csrc/gemm_tc.cu) at every number of tokens (the head at 24 tokens: 60 us
+  against 169 for the few-token kernel);
+* otherwise, where the persistent few-token kernel does not take the sizes, up to 16 tokens the kernel that
+  streams the weights once with one CTA per 16 rows (csrc/gemm_skinny.cu); beyond 16 tokens, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
   while it applies (16 tokens of a 2B-class layer: 58 us with the few-token kernel, 63 us with the cluster
   kernel; 24 tokens: 82 against 66; 32 tokens: 91 against 70: every CTA of the few-token kernel reads all the
   tokens' rows from L2); then the persistent tcgen05 kernel, which cuts K through scratch memory up to 128
@@ -40,10 +42,10 @@ _choices = {}          # what decides the choice -> the kernel chosen (the check
 def _choose(mode, a, w, out) -> int:
     tensor_cores = ops.gemm_tc_accepts(mode, a, w, out)
     few = ops.gemm_skinny_accepts(mode, a, w, out)
-    if tensor_cores and ops.gemm_tc_tiles_fill_the_sms(a, out):
-        return _TC
     if a.shape[0] <= ops.STREAM_MAX_TOKENS and ops.gemm_stream_accepts(mode, a, w, out):
         return _STREAM
+    if tensor_cores and ops.gemm_tc_tiles_fill_the_sms(a, out):
+        return _TC
     if few and a.shape[0] <= SKINNY_BEST_TOKENS:
         return _SKINNY
     if tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
@@ -69,7 +71,6 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
             if fused is None:
                 fused = _choices[key] = (norm_weight.is_contiguous() and norm_weight.data_ptr() % 16 == 0
                                          and norm_weight.dtype in (torch.bfloat16, torch.float32)
-                                         and not ops.gemm_tc_tiles_fill_the_sms(source, out)
                                          and ops.gemm_stream_accepts(mode, source, w, out, norm=True))
             if fused:
                 ops.gemm_stream(mode, source, w, out, alpha, error_flag, label=name, norm_weight=norm_weight, eps=eps)

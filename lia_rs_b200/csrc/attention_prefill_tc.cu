@@ -12,7 +12,10 @@
 // 5..8 bring Q once and then K and V tiles from their pages with cp.async into 128-byte-swizzled shared
 // memory (two stages).  The roles meet only through mbarriers, every wait on one is bounded.  The first product
 // of tile j + 1 is issued before the softmax of tile j is awaited (two score buffers in TMEM), and the softmax of
-// tile j + 1 runs while the second product of tile j does: the tensor cores and the exponentials overlap.
+// tile j + 1 runs while the second product of tile j does (two buffers of probabilities in shared memory, so the
+// softmax never waits for the product that reads the other): the tensor cores and the exponentials overlap.
+// What bounds a tile is the softmax warps' special-function pipe: 128 ex2 and 64 conversions to bf16 pairs per row
+// are 1,280 cycles of it (the conversion shares the pipe), against 1,024 cycles of the two products.
 //
 // Rows are (token, head) pairs: row r is token r / g, head r % g of the CTA's tokens, so the keys of a kv
 // head are read once for all its query heads.  Head sizes 64 and 128, g a divisor of 128; the caller uses
@@ -29,6 +32,7 @@ constexpr int THREADS = (SOFTMAX_WARPS + 1 + LOAD_WARPS) * 32;
 constexpr int LOADERS = LOAD_WARPS * 32;
 constexpr int STAGES = 2;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LAZY = 8.f;              // see the softmax
 
 struct Params {
     const __nv_bfloat16* q;          // [tokens, nq, D]
@@ -103,14 +107,14 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], p_ready, pv_done;
+    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], p_ready, p_free[2];
     __shared__ uint32_t tmem_base_slot;
     constexpr int PIECES = D / 8;                      // 16-byte pieces per row
     constexpr uint32_t Q_BYTES = ROWS * D * 2, KV_BYTES = KT * D * 2, P_BYTES = ROWS * KT * 2;
     constexpr int TMEM_COLS = 512;                     // two score buffers of 128 columns, then the output's head_dim columns
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = smem_base, p_s = q_s + Q_BYTES, kv_s = p_s + P_BYTES;       // kv_s: [stage][K, V]
+    const uint32_t q_s = smem_base, p_s = q_s + Q_BYTES, kv_s = p_s + 2 * P_BYTES;   // p_s: two buffers of probabilities; kv_s: [stage][K, V]
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
     // ---- which portion, which tokens, which kv head (later tiles first: they have the most keys) ----
@@ -144,7 +148,8 @@ attention_prefill_tc_kernel(Params p) {
         mbar_init(smem_u32(&s_full[0]), 1);
         mbar_init(smem_u32(&s_full[1]), 1);
         mbar_init(smem_u32(&p_ready), SOFTMAX_WARPS * 32);
-        mbar_init(smem_u32(&pv_done), 1);
+        mbar_init(smem_u32(&p_free[0]), 1);
+        mbar_init(smem_u32(&p_free[1]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
@@ -254,12 +259,12 @@ attention_prefill_tc_kernel(Params p) {
             tc_fence_after();
 #pragma unroll
             for (int ks16 = 0; ks16 < KT / 16; ++ks16) {
-                const uint32_t a = p_s + (uint32_t)((ks16 >> 2) * (ROWS * 128) + (ks16 & 3) * 32);
+                const uint32_t a = p_s + (uint32_t)((j & 1) * P_BYTES) + (uint32_t)((ks16 >> 2) * (ROWS * 128) + (ks16 & 3) * 32);
                 const uint32_t b = vs + (uint32_t)(ks16 * 2048);              // 16 keys = two groups of 8 rows
                 tc_mma(tmem_o, smem_desc(a), smem_desc_mn(b, KT * 128, 1024), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&v_empty[st]));
-            tc_commit(smem_u32(&pv_done));
+            tc_commit(smem_u32(&p_free[j & 1]));       // this tile's buffer of probabilities is free again, and O holds the tile
         }
         if (!ok && p.error_flag) atomicExch(p.error_flag, 3);
     } else if (warp < SOFTMAX_WARPS && n_tiles > 0) {
@@ -298,7 +303,11 @@ attention_prefill_tc_kernel(Params p) {
                 tile_max = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
             }
             // whole-number reference point: see attention_decode.cu
-            const float new_max = fmaxf(row_max, ceilf(tile_max * p.scale_log2));
+            // ... and it moves only when the tile's maximum lies more than LAZY whole numbers above it: the
+            // probabilities then reach 2^LAZY at most, which bf16 and the 32-bit sums hold, and O is rescaled once
+            // or twice in a row's walk instead of at most of its first tiles (686 cycles each time)
+            const float tile_ref = ceilf(tile_max * p.scale_log2);
+            const float new_max = (row_max == -INFINITY || tile_ref > row_max + LAZY) ? fmaxf(row_max, tile_ref) : row_max;
             const float safe_max = new_max == -INFINITY ? 0.f : new_max;        // a row that has seen no key yet
             const float correction = exp2_whole(row_max - safe_max);
             row_max = new_max;
@@ -314,10 +323,14 @@ attention_prefill_tc_kernel(Params p) {
                 raw[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             row_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-            // the second product of the tile before must be done: it reads P, and O is about to be rescaled
-            if (j > 0 && !mbar_wait(smem_u32(&pv_done), (uint32_t)(j - 1) & 1u)) { ok = false; break; }
+            // This tile's buffer of probabilities (one of two) is free once the second product of two tiles ago is done;
+            // O may be rescaled only when the second product of the tile before is done.  (p_free[b] completes once
+            // per tile of parity b; the wait for the buffer keeps every later wait's parity unambiguous.)
+            if (j >= 2 && !mbar_wait(smem_u32(&p_free[j & 1]), (uint32_t)((j >> 1) - 1) & 1u)) { ok = false; break; }
+            const bool rescale = __any_sync(0xffffffffu, correction != 1.f) && j > 0;
+            if (rescale && !mbar_wait(smem_u32(&p_free[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
-            if (__any_sync(0xffffffffu, correction != 1.f) && j > 0) {
+            if (rescale) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 16) {
                     float o[16];
@@ -330,14 +343,14 @@ attention_prefill_tc_kernel(Params p) {
             }
 #pragma unroll
             for (int piece = 0; piece < KT / 8; ++piece)
-                *reinterpret_cast<uint4*>(smem + Q_BYTES + tile_offset<ROWS>(r, piece)) =
+                *reinterpret_cast<uint4*>(smem + Q_BYTES + (j & 1) * P_BYTES + tile_offset<ROWS>(r, piece)) =
                     make_uint4(raw[piece * 4], raw[piece * 4 + 1], raw[piece * 4 + 2], raw[piece * 4 + 3]);
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(smem_u32(&p_ready));
         }
         // ---- the row's output ----
-        if (ok && !mbar_wait(smem_u32(&pv_done), (uint32_t)(n_tiles - 1) & 1u)) ok = false;
+        if (ok && !mbar_wait(smem_u32(&p_free[(n_tiles - 1) & 1]), (uint32_t)((n_tiles - 1) >> 1) & 1u)) ok = false;
         tc_fence_after();
         if (ok) {
             const float inv = 1.0f / row_sum;
@@ -371,7 +384,7 @@ attention_prefill_tc_kernel(Params p) {
 
 template <int D>
 int launch(const Params& p, int n_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)ROWS * D * 2 + (size_t)ROWS * KT * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
+    const size_t smem = (size_t)ROWS * D * 2 + 2 * (size_t)ROWS * KT * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -3,19 +3,23 @@
 // A CTA owns 128 query rows = (128 / g) consecutive tokens x the g query heads of one kv head, and walks
 // the keys its rows can see, 128 at a time:
 //     S = Q K^T     tcgen05.mma, M 128 (rows), N 128 (keys), K head_dim, accumulator in TMEM
-//     softmax       one thread per row reads its 128 scores with tcgen05.ld (no shuffles: a row lives in one
-//                   TMEM lane), running maximum (a whole number of base-2 logarithms, so rescaling is exact and
-//                   rare) and sum in 32-bit, probabilities to shared memory as bf16
+//     softmax       two threads per row, each with 64 of its 128 scores from tcgen05.ld (no shuffles: a row lives in
+//                   one TMEM lane, which the warps w and w + 4 can both read); the two meet through shared memory
+//                   for the row's maximum (a whole number of base-2 logarithms, so rescaling is exact and rare);
+//                   each makes the exponentials of its 64 keys and keeps their sum, in 32-bit; probabilities to
+//                   shared memory as bf16, rounded on the integer pipe
 //     O += P V      tcgen05.mma, M 128, N head_dim, K 128 keys, V taken as it lies in its pages ([key][dim],
 //                   an MN-major operand), accumulator in TMEM for the whole walk
-// Roles: warps 0..3 softmax (thread = row), warp 4 allocates TMEM and one of its lanes issues the MMAs, warps
-// 5..8 bring Q once and then K and V tiles from their pages with cp.async into 128-byte-swizzled shared
+// Roles: warps 0..7 softmax, warp 8 allocates TMEM and one of its lanes issues the MMAs, warps
+// 9..12 bring Q once and then K and V tiles from their pages with cp.async into 128-byte-swizzled shared
 // memory (two stages).  The roles meet only through mbarriers, every wait on one is bounded.  The first product
 // of tile j + 1 is issued before the softmax of tile j is awaited (two score buffers in TMEM), and the softmax of
 // tile j + 1 runs while the second product of tile j does (two buffers of probabilities in shared memory, so the
 // softmax never waits for the product that reads the other): the tensor cores and the exponentials overlap.
-// What bounds a tile is the softmax warps' special-function pipe: 128 ex2 and 64 conversions to bf16 pairs per row
-// are 1,280 cycles of it (the conversion shares the pipe), against 1,024 cycles of the two products.
+// What bounds a tile is the softmax warps' special-function pipe: a row's 128 ex2 are 1,024 cycles of it, as long
+// as the tile's two products; the conversion instruction to bf16 pairs runs on the same pipe (256 cycles more), so
+// the rounding is done with an integer add instead, and two warps per scheduler hide the pipe's latency where one
+// thread with 128 scores in registers could keep only two exponentials in flight.
 //
 // Rows are (token, head) pairs: row r is token r / g, head r % g of the CTA's tokens, so the keys of a kv
 // head are read once for all its query heads.  Head sizes 64 and 128, g a divisor of 128; the caller uses
@@ -27,7 +31,7 @@ using namespace tc5;
 namespace {
 constexpr int ROWS = 128;                // query rows per CTA: the MMA's M
 constexpr int KT = 128;                  // keys per tile: N of the first product, K of the second
-constexpr int SOFTMAX_WARPS = 4, LOAD_WARPS = 4;
+constexpr int SOFTMAX_WARPS = 8, LOAD_WARPS = 4;
 constexpr int THREADS = (SOFTMAX_WARPS + 1 + LOAD_WARPS) * 32;
 constexpr int LOADERS = LOAD_WARPS * 32;
 constexpr int STAGES = 2;
@@ -109,6 +113,7 @@ attention_prefill_tc_kernel(Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], p_ready, p_free[2];
     __shared__ uint32_t tmem_base_slot;
+    __shared__ short pair_ref[2][2][ROWS];         // what the two threads of a row tell each other (16 bits: shared memory is full)
     constexpr int PIECES = D / 8;                      // 16-byte pieces per row
     constexpr uint32_t Q_BYTES = ROWS * D * 2, KV_BYTES = KT * D * 2, P_BYTES = ROWS * KT * 2;
     constexpr int TMEM_COLS = 512;                     // two score buffers of 128 columns, then the output's head_dim columns
@@ -268,45 +273,54 @@ attention_prefill_tc_kernel(Params p) {
         }
         if (!ok && p.error_flag) atomicExch(p.error_flag, 3);
     } else if (warp < SOFTMAX_WARPS && n_tiles > 0) {
-        // ---- softmax: thread = row (TMEM lane) ----
-        const int r = threadIdx.x;                                          // 0..127
+        // ---- softmax: warp w and warp w + 4 share the rows of TMEM lanes 32 (w % 4) ..; each takes half the keys of
+        //      a tile and half the output's columns ----
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;                                  // 0..127
         const int tok = r / group, head = r % group;
         const bool row_ok = tok < tok_count;
         const int pos = row_ok ? pos_first + tok : 0x3fffffff;              // a row beyond the portion sees every key and is never written
-        const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
-        float row_max = -INFINITY, row_sum = 0.f;
+        const uint32_t lane_base = ((uint32_t)(quarter * 32) << 16);
+        constexpr int HALF = KT / 2;
+        float row_max = -INFINITY, row_sum = 0.f;                           // the sum: of this thread's keys only
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int key0 = key_begin + j * KT;
+            const int key0 = key_begin + j * KT + half * HALF;              // this thread's first key of the tile
             if (!mbar_wait(smem_u32(&s_full[j & 1]), ((uint32_t)j >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
-            const bool masked = key0 + KT - 1 > pos_first || (p.window > 0 && key0 <= pos_last - p.window);
-            // the row's 128 scores, in two loads that are both in flight before the wait
-            uint32_t raw[KT];
-            tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT) + lane_base, raw);
-            tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT) + lane_base + 64u, raw + 64);
+            const bool masked = key_begin + j * KT + KT - 1 > pos_first || (p.window > 0 && key_begin + j * KT <= pos_last - p.window);
+            uint32_t raw[HALF];
+            tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT + half * HALF) + lane_base, raw);
             tmem_load_wait();
-            float tile_max = -INFINITY;
             if (masked) {
 #pragma unroll
-                for (int c = 0; c < KT; ++c) {
+                for (int c = 0; c < HALF; ++c) {
                     const int key = key0 + c;
                     bool visible = key <= pos;
                     if (p.window > 0) visible = visible && key > pos - p.window;
                     if (!visible) raw[c] = 0xff800000u;                         // -infinity
                 }
             }
-            {   // four chains: a single one would be 128 instructions that wait for one another
+            float tile_max;
+            {   // four chains: a single one would be 64 instructions that wait for one another
                 float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < KT; ++c) part[c & 3] = fmaxf(part[c & 3], __uint_as_float(raw[c]));
+                for (int c = 0; c < HALF; ++c) part[c & 3] = fmaxf(part[c & 3], __uint_as_float(raw[c]));
                 tile_max = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
             }
-            // whole-number reference point: see attention_decode.cu
+            // the row's maximum: the two threads tell each other theirs (two buffers: the partner may still read
+            // the tile before's while this thread writes; the barrier of a tile orders the tile before's reads)
+            // Whole-number reference point: see attention_decode.cu.  What the two threads exchange is that whole number
+            // (the ceiling of the larger maximum is the larger ceiling), as 16 bits: beyond +-126 a 32-bit exponential
+            // is 0 or infinite anyway, so the clamp to +-30,000 changes nothing; -32,768 stands for minus infinity.
+            const float own_ref = ceilf(tile_max * p.scale_log2);
+            pair_ref[j & 1][half][r] = own_ref == -INFINITY ? (short)-32768 : (short)fminf(fmaxf(own_ref, -30000.f), 30000.f);
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const short both = max(pair_ref[j & 1][0][r], pair_ref[j & 1][1][r]);
             // ... and it moves only when the tile's maximum lies more than LAZY whole numbers above it: the
             // probabilities then reach 2^LAZY at most, which bf16 and the 32-bit sums hold, and O is rescaled once
             // or twice in a row's walk instead of at most of its first tiles (686 cycles each time)
-            const float tile_ref = ceilf(tile_max * p.scale_log2);
+            const float tile_ref = both == -32768 ? -INFINITY : (float)both;
             const float new_max = (row_max == -INFINITY || tile_ref > row_max + LAZY) ? fmaxf(row_max, tile_ref) : row_max;
             const float safe_max = new_max == -INFINITY ? 0.f : new_max;        // a row that has seen no key yet
             const float correction = exp2_whole(row_max - safe_max);
@@ -315,12 +329,13 @@ attention_prefill_tc_kernel(Params p) {
             // probabilities, as bf16 pairs (the scores' registers are reused)
             float sums[4] = {0.f, 0.f, 0.f, 0.f};                     // four chains again, met in a fixed order
 #pragma unroll
-            for (int c = 0; c < KT; c += 2) {
+            for (int c = 0; c < HALF; c += 2) {
                 const float e0 = ex2_approx(fmaf(__uint_as_float(raw[c]), p.scale_log2, -safe_max));
                 const float e1 = ex2_approx(fmaf(__uint_as_float(raw[c + 1]), p.scale_log2, -safe_max));
                 sums[(c >> 1) & 3] += e0 + e1;
-                __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
-                raw[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                // to bf16 with an integer add (round half up: the values are finite and not negative) and a byte
+                // permute that keeps the two upper halves: the conversion instruction would share ex2's pipe
+                raw[c >> 1] = __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632);
             }
             row_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             // This tile's buffer of probabilities (one of two) is free once the second product of two tiles ago is done;
@@ -332,7 +347,7 @@ attention_prefill_tc_kernel(Params p) {
             tc_fence_after();
             if (rescale) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 16) {
+                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
                     float o[16];
                     tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);
 #pragma unroll
@@ -342,21 +357,24 @@ attention_prefill_tc_kernel(Params p) {
                 tmem_store_wait();
             }
 #pragma unroll
-            for (int piece = 0; piece < KT / 8; ++piece)
-                *reinterpret_cast<uint4*>(smem + Q_BYTES + (j & 1) * P_BYTES + tile_offset<ROWS>(r, piece)) =
-                    make_uint4(raw[piece * 4], raw[piece * 4 + 1], raw[piece * 4 + 2], raw[piece * 4 + 3]);
+            for (int i = 0; i < HALF / 8; ++i)
+                *reinterpret_cast<uint4*>(smem + Q_BYTES + (j & 1) * P_BYTES + tile_offset<ROWS>(r, half * (HALF / 8) + i)) =
+                    make_uint4(raw[i * 4], raw[i * 4 + 1], raw[i * 4 + 2], raw[i * 4 + 3]);
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(smem_u32(&p_ready));
         }
-        // ---- the row's output ----
+        // ---- the row's output: the two threads' sums meet, each writes half the columns ----
         if (ok && !mbar_wait(smem_u32(&p_free[(n_tiles - 1) & 1]), (uint32_t)((n_tiles - 1) >> 1) & 1u)) ok = false;
         tc_fence_after();
+        float* pair_sum = reinterpret_cast<float*>(smem);                   // [2][ROWS], where Q was: every product is done
+        pair_sum[half * ROWS + r] = row_sum;
+        asm volatile("bar.sync 5, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
         if (ok) {
-            const float inv = 1.0f / row_sum;
+            const float inv = 1.0f / (pair_sum[r] + pair_sum[ROWS + r]);
             __nv_bfloat16* dst = p.out + ((size_t)(q_offset + tok0 + (row_ok ? tok : 0)) * p.nq + kvh * group + head) * D;
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 16) {
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
                 float o[16];
                 tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);           // every lane takes part in the load
                 if (row_ok) {

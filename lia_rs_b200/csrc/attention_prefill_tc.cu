@@ -6,20 +6,24 @@
 //     softmax       two threads per row, each with 64 of its 128 scores from tcgen05.ld (no shuffles: a row lives in
 //                   one TMEM lane, which the warps w and w + 4 can both read); the two meet through shared memory
 //                   for the row's maximum (a whole number of base-2 logarithms, so rescaling is exact and rare);
-//                   each makes the exponentials of its 64 keys and keeps their sum, in 32-bit; probabilities to
-//                   shared memory as bf16, rounded on the integer pipe
-//     O += P V      tcgen05.mma, M 128, N head_dim, K 128 keys, V taken as it lies in its pages ([key][dim],
-//                   an MN-major operand), accumulator in TMEM for the whole walk
+//                   each makes the exponentials of its 64 keys and keeps their sum, in 32-bit; probabilities back
+//                   to TMEM as bf16 pairs (tcgen05.st), rounded on the integer pipe
+//     O += P V      tcgen05.mma with P as the operand from TMEM, M 128, N head_dim, K 128 keys, V taken as it lies
+//                   in its pages ([key][dim], an MN-major operand), accumulator in TMEM for the whole walk
 // Roles: warps 0..7 softmax, warp 8 allocates TMEM and one of its lanes issues the MMAs, warps
 // 9..12 bring Q once and then K and V tiles from their pages with cp.async into 128-byte-swizzled shared
-// memory (two stages).  The roles meet only through mbarriers, every wait on one is bounded.  The first product
-// of tile j + 1 is issued before the softmax of tile j is awaited (two score buffers in TMEM), and the softmax of
-// tile j + 1 runs while the second product of tile j does (two buffers of probabilities in shared memory, so the
-// softmax never waits for the product that reads the other): the tensor cores and the exponentials overlap.
-// What bounds a tile is the softmax warps' special-function pipe: a row's 128 ex2 are 1,024 cycles of it, as long
-// as the tile's two products; the conversion instruction to bf16 pairs runs on the same pipe (256 cycles more), so
-// the rounding is done with an integer add instead, and two warps per scheduler hide the pipe's latency where one
-// thread with 128 scores in registers could keep only two exponentials in flight.
+// memory (three stages: Q and three tiles of K and V fill it).  The roles meet only through mbarriers, every wait
+// on one is bounded.  The first product of tile j + 1 is issued before the softmax of tile j is awaited (two score
+// buffers in TMEM), and the softmax of tile j + 1 runs while the second product of tile j does (two buffers of
+// probabilities in TMEM, so the softmax never waits for the product that reads the other): the tensor cores and
+// the exponentials overlap.  TMEM holds all of it: 2 x 128 columns of scores, 128 of output, 2 x 64 of
+// probabilities.
+// What bounds a tile: the one thread that issues the MMAs is held at the tensor pipe's pace (a 128 x 128 x 16 MMA
+// takes 64 cycles alone and 70-90 here, where tcgen05.ld and .st of the softmax share the tensor memory's ports), and
+// its waits for keys and probabilities add to that; the loaders' cp.async of a 64 KB tile take ~1,700 cycles of the
+// load/store unit; the special-function pipe needs 1,024 cycles for a tile's 16,384 ex2 (the conversion to bf16
+// pairs would run on the same pipe, 256 cycles more, so the rounding is an integer add).  Two warps per scheduler
+// hide the pipe's latency where one thread with 128 scores in registers could keep only two exponentials in flight.
 //
 // Rows are (token, head) pairs: row r is token r / g, head r % g of the CTA's tokens, so the keys of a kv
 // head are read once for all its query heads.  Head sizes 64 and 128, g a divisor of 128; the caller uses
@@ -34,7 +38,7 @@ constexpr int KT = 128;                  // keys per tile: N of the first produc
 constexpr int SOFTMAX_WARPS = 8, LOAD_WARPS = 4;
 constexpr int THREADS = (SOFTMAX_WARPS + 1 + LOAD_WARPS) * 32;
 constexpr int LOADERS = LOAD_WARPS * 32;
-constexpr int STAGES = 2;
+constexpr int STAGES = 3;                // K and V tiles in flight (the probabilities live in tensor memory, so three fit)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LAZY = 8.f;              // see the softmax
 
@@ -83,6 +87,23 @@ __device__ __forceinline__ void tmem_load64_nowait(uint32_t addr, uint32_t* r) {
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
         : "r"(addr));
 }
+// 32 consecutive columns of this warp's 32 TMEM lanes, written from registers.
+__device__ __forceinline__ void tmem_store32(uint32_t addr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+// D (+)= A B with A from tensor memory (rows = lanes, two 16-bit elements of K per 32-bit column, the lower index in
+// the lower half) and B from shared memory.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // A tile of `rows` rows x D elements as the tensor cores want a K-major operand (and, read with the other
@@ -113,13 +134,15 @@ attention_prefill_tc_kernel(Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], p_ready, p_free[2];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ short pair_ref[2][2][ROWS];         // what the two threads of a row tell each other (16 bits: shared memory is full)
+    __shared__ short pair_ref[2][2][ROWS];         // what the two threads of a row tell each other (16 bits: shared memory is full to the last KB)
     constexpr int PIECES = D / 8;                      // 16-byte pieces per row
-    constexpr uint32_t Q_BYTES = ROWS * D * 2, KV_BYTES = KT * D * 2, P_BYTES = ROWS * KT * 2;
-    constexpr int TMEM_COLS = 512;                     // two score buffers of 128 columns, then the output's head_dim columns
+    constexpr uint32_t Q_BYTES = ROWS * D * 2, KV_BYTES = KT * D * 2;
+    // tensor memory: two score buffers of 128 columns, the output's head_dim columns (128 kept), and two buffers of
+    // probabilities of 64 columns (128 keys as bf16 pairs)
+    constexpr int TMEM_COLS = 512;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = smem_base, p_s = q_s + Q_BYTES, kv_s = p_s + 2 * P_BYTES;   // p_s: two buffers of probabilities; kv_s: [stage][K, V]
+    const uint32_t q_s = smem_base, kv_s = q_s + Q_BYTES;   // kv_s: [stage][K, V]
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
     // ---- which portion, which tokens, which kv head (later tiles first: they have the most keys) ----
@@ -167,7 +190,7 @@ attention_prefill_tc_kernel(Params p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 2 * KT;       // score buffer b at tmem_s + b * KT
+    const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 2 * KT, tmem_p = tmem_o + 128;   // score buffer b at tmem_s + b * KT, probabilities b at tmem_p + b * KT / 2
     pdl_launch_dependents();
     pdl_wait();                                   // q and this step's keys come from the kernel ahead
 
@@ -189,7 +212,7 @@ attention_prefill_tc_kernel(Params p) {
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j % STAGES;
-            // the keys' stage is free as soon as the first product of two tiles ago has read it, the values' stage
+            // the keys' stage is free as soon as the first product of three tiles ago has read it, the values' stage
             // only after the second
             if (j >= STAGES && !mbar_wait(smem_u32(&k_empty[st]), ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { ok = false; break; }
             const uint32_t ks = kv_s + (uint32_t)st * 2 * KV_BYTES, vs = ks + KV_BYTES;
@@ -258,15 +281,14 @@ attention_prefill_tc_kernel(Params p) {
             const uint32_t vs = kv_s + (uint32_t)st * 2 * KV_BYTES + KV_BYTES;
             if (j + 1 < n_tiles) first_product(j + 1);
             if (!ok) break;
-            // O += P V once the values and the probabilities lie in shared memory (and O has been rescaled if it had to be)
+            // O += P V once the values lie in shared memory and the probabilities in TMEM (and O has been rescaled if it had to be)
             if (!mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / STAGES) & 1u)) { ok = false; break; }
             if (!mbar_wait(smem_u32(&p_ready), (uint32_t)j & 1u)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
             for (int ks16 = 0; ks16 < KT / 16; ++ks16) {
-                const uint32_t a = p_s + (uint32_t)((j & 1) * P_BYTES) + (uint32_t)((ks16 >> 2) * (ROWS * 128) + (ks16 & 3) * 32);
                 const uint32_t b = vs + (uint32_t)(ks16 * 2048);              // 16 keys = two groups of 8 rows
-                tc_mma(tmem_o, smem_desc(a), smem_desc_mn(b, KT * 128, 1024), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
+                tc_mma_ts(tmem_o, tmem_p + (uint32_t)((j & 1) * (KT / 2) + ks16 * 8), smem_desc_mn(b, KT * 128, 1024), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&v_empty[st]));
             tc_commit(smem_u32(&p_free[j & 1]));       // this tile's buffer of probabilities is free again, and O holds the tile
@@ -356,11 +378,8 @@ attention_prefill_tc_kernel(Params p) {
                 }
                 tmem_store_wait();
             }
-#pragma unroll
-            for (int i = 0; i < HALF / 8; ++i)
-                *reinterpret_cast<uint4*>(smem + Q_BYTES + (j & 1) * P_BYTES + tile_offset<ROWS>(r, half * (HALF / 8) + i)) =
-                    make_uint4(raw[i * 4], raw[i * 4 + 1], raw[i * 4 + 2], raw[i * 4 + 3]);
-            fence_async_smem();
+            tmem_store32(tmem_p + lane_base + (uint32_t)((j & 1) * (KT / 2) + half * (HALF / 2)), raw);
+            tmem_store_wait();
             tc_fence_before();
             mbar_arrive(smem_u32(&p_ready));
         }
@@ -402,7 +421,7 @@ attention_prefill_tc_kernel(Params p) {
 
 template <int D>
 int launch(const Params& p, int n_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)ROWS * D * 2 + 2 * (size_t)ROWS * KT * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
+    const size_t smem = (size_t)ROWS * D * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -54,6 +54,12 @@ struct Params {
     float scale_log2;
     int num_pages;
     int* error_flag;
+    // With `splits` > 1 the keys of every CTA's rows are cut into that many ranges (blockIdx.z; whole tiles): each
+    // range leaves its output unnormalised and the row's reference point and sum, and the merge kernel puts them together.
+    int splits;
+    float* partial_o;                // [splits][tokens * nq][D]
+    float* partial_ms;               // [splits][tokens * nq][2]: reference point (a whole number, or -infinity), sum
+    long long n_rows_total;          // tokens * nq
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -161,9 +167,15 @@ attention_prefill_tc_kernel(Params p) {
     const int tok0 = tile * p.tokens_per_tile;
     const int tok_count = active ? min(p.tokens_per_tile, seg_count - tok0) : 0;
     const int pos_first = seg_start + tok0, pos_last = pos_first + tok_count - 1;
-    const int key_begin = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
     const int key_end = pos_last + 1;
-    const int n_tiles = active ? (key_end - key_begin + KT - 1) / KT : 0;
+    int key_begin = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
+    int n_tiles = active ? (key_end - key_begin + KT - 1) / KT : 0;
+    if (p.splits > 1) {                             // this CTA's range of the tiles
+        const int per = (n_tiles + p.splits - 1) / p.splits;
+        const int first = min(n_tiles, (int)blockIdx.z * per);
+        n_tiles = min(n_tiles, first + per) - first;
+        key_begin += first * KT;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), LOADERS);
@@ -389,7 +401,25 @@ attention_prefill_tc_kernel(Params p) {
         float* pair_sum = reinterpret_cast<float*>(smem);                   // [2][ROWS], where Q was: every product is done
         pair_sum[half * ROWS + r] = row_sum;
         asm volatile("bar.sync 5, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-        if (ok) {
+        if (ok && p.splits > 1) {
+            // this range's share of the row: O as it stands, the reference point and the sum of the exponentials
+            const size_t row = (size_t)(q_offset + tok0 + (row_ok ? tok : 0)) * p.nq + kvh * group + head;
+            const size_t plane = (size_t)blockIdx.z * p.n_rows_total + row;
+            if (row_ok && half == 0) {
+                p.partial_ms[plane * 2] = row_max;
+                p.partial_ms[plane * 2 + 1] = pair_sum[r] + pair_sum[ROWS + r];
+            }
+            float* dst = p.partial_o + plane * D;
+#pragma unroll 1
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
+                float o[16];
+                tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4) *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                }
+            }
+        } else if (ok) {
             const float inv = 1.0f / (pair_sum[r] + pair_sum[ROWS + r]);
             __nv_bfloat16* dst = p.out + ((size_t)(q_offset + tok0 + (row_ok ? tok : 0)) * p.nq + kvh * group + head) * D;
 #pragma unroll 1
@@ -410,6 +440,15 @@ attention_prefill_tc_kernel(Params p) {
         } else if (lane == 0 && p.error_flag) {
             atomicExch(p.error_flag, 3);
         }
+    } else if (warp < 4 && n_tiles == 0 && p.splits > 1 && active) {
+        // a range without tiles (fewer tiles than ranges): it says so, its output is never read
+        const int r = threadIdx.x, tok = r / group, head = r % group;
+        if (tok < tok_count) {
+            const size_t row = (size_t)(q_offset + tok0 + tok) * p.nq + kvh * group + head;
+            const size_t plane = (size_t)blockIdx.z * p.n_rows_total + row;
+            p.partial_ms[plane * 2] = -INFINITY;
+            p.partial_ms[plane * 2 + 1] = 0.f;
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -417,6 +456,66 @@ attention_prefill_tc_kernel(Params p) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"((uint32_t)TMEM_COLS) : "memory");
     }
+}
+
+// The ranges of a row put together: for every row of a CTA's tokens
+//     out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) s_i,   M = max_i m_i,
+// the ranges in ascending order; the m_i are whole numbers, so the weights are exact powers of two.  Grid as the
+// kernel above, its z counting groups of four rows: a warp per row, lane i holding range i's m and s (at most 32
+// ranges), every lane a few of the row's elements.
+template <int D>
+__global__ void __launch_bounds__(128) attention_prefill_merge_kernel(Params p) {
+    pdl_launch_dependents();
+    const int group = p.nq / p.nkv;
+    const int kvh = blockIdx.y;
+    int tile = gridDim.x - 1 - blockIdx.x, seg = 0, q_offset = 0, seg_count = 0;
+    for (; seg < p.n_segments; ++seg) {
+        q_offset = p.segments[seg * 3];
+        seg_count = p.segments[seg * 3 + 2];
+        const int tiles = (seg_count + p.tokens_per_tile - 1) / p.tokens_per_tile;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    const bool active = seg < p.n_segments && p.slots[q_offset] >= 0;
+    const int tok0 = tile * p.tokens_per_tile;
+    const int tok_count = active ? min(p.tokens_per_tile, seg_count - tok0) : 0;
+    constexpr int E = D / 32;                          // elements per lane: 2 or 4
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.z * 4 + warp, tok = r / group, head = r % group;
+    pdl_wait();
+    if (tok >= tok_count) return;
+    const size_t row = (size_t)(q_offset + tok0 + tok) * p.nq + kvh * group + head;
+    float m = -INFINITY, sum = 0.f;
+    if (lane < p.splits) {
+        const float2 ms = *reinterpret_cast<const float2*>(p.partial_ms + ((size_t)lane * p.n_rows_total + row) * 2);
+        m = ms.x;
+        sum = ms.y;
+    }
+    float top = m;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    const float weight = m == -INFINITY ? 0.f : exp2_whole(m - top);     // 0: a range in which the row saw no key
+    float acc[E], total = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+    const float* o = p.partial_o + row * D + lane * E;
+#pragma unroll 4
+    for (int i = 0; i < p.splits; ++i) {
+        const float w = __shfl_sync(0xffffffffu, weight, i), s_i = __shfl_sync(0xffffffffu, sum, i);
+        if (w == 0.f) continue;                        // its output may never have been written
+        total = fmaf(w, s_i, total);
+        const float* src = o + (size_t)i * p.n_rows_total * D;
+#pragma unroll
+        for (int e = 0; e < E; e += 2) {
+            const float2 v = *reinterpret_cast<const float2*>(src + e);
+            acc[e] = fmaf(w, v.x, acc[e]);
+            acc[e + 1] = fmaf(w, v.y, acc[e + 1]);
+        }
+    }
+    const float inv = 1.0f / total;
+    __nv_bfloat16* dst = p.out + row * D + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; e += 2) *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
 }
 
 template <int D>
@@ -428,7 +527,9 @@ int launch(const Params& p, int n_tiles, cudaStream_t stream) {
             return LIA_ERR_LAUNCH;
         configured = true;
     }
-    return lia_launch(attention_prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(THREADS), smem, stream, p);
+    const int rc = lia_launch(attention_prefill_tc_kernel<D>, dim3(n_tiles, p.nkv, p.splits), dim3(THREADS), smem, stream, p);
+    if (rc != LIA_OK || p.splits <= 1) return rc;
+    return lia_launch(attention_prefill_merge_kernel<D>, dim3(n_tiles, p.nkv, ROWS / 4), dim3(128), 0, stream, p);
 }
 }  // namespace
 
@@ -440,16 +541,23 @@ LIA_EXPORT int lia_attention_prefill_tc_tokens_per_tile(int group, int d) {
 }
 
 // Arguments as lia_attention_prefill; `n_tiles` = sum over portions of ceil(count / tokens_per_tile) with the
-// tokens per tile of this kernel.
+// tokens per tile of this kernel.  With `splits` > 1 every CTA's keys are cut into that many ranges of whole
+// 128-key tiles, each range a CTA of its own, and a second kernel merges them (few tokens over a long context
+// would otherwise leave most SMs idle); `partial` then holds splits * n_tokens * nq * (head size + 2) 32-bit words,
+// `n_tokens` being the tokens of the whole batch that `q` and `out` cover.
 LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                         int n_segments, int n_tiles, const int* slots, const int* block_table,
                                         int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int num_pages, int* error_flag, cudaStream_t stream) {
+                                        float scale, int num_pages, int splits, float* partial, int n_tokens,
+                                        int* error_flag, cudaStream_t stream) {
     if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
+    if (splits < 1 || splits > 32 || (splits > 1 && (!partial || n_tokens <= 0))) return LIA_ERR_SIZE;
     const int per_tile = lia_attention_prefill_tc_tokens_per_tile(nq / nkv, d);
     if (per_tile == 0) return LIA_ERR_SIZE;
-    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)k_pages & 15u) || ((uintptr_t)v_pages & 15u)) return LIA_ERR_ALIGN;
+    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)k_pages & 15u) || ((uintptr_t)v_pages & 15u) ||
+        ((uintptr_t)partial & 15u))
+        return LIA_ERR_ALIGN;
     Params p;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.segments = segments; p.slots = slots; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
@@ -459,6 +567,10 @@ LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, cons
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;
+    p.splits = splits;
+    p.n_rows_total = (long long)n_tokens * nq;
+    p.partial_o = partial;
+    p.partial_ms = partial ? partial + (size_t)splits * p.n_rows_total * d : nullptr;
     if (d == 128) return launch<128>(p, n_tiles, stream);
     return launch<64>(p, n_tiles, stream);
 }

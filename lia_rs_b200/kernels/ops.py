@@ -66,7 +66,8 @@ class _Signatures:
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_void_p]
     lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p]
@@ -497,18 +498,28 @@ def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                         window, scale, error_flag=None, label=None, work_flops=0):
+                         window, scale, error_flag=None, label=None, work_flops=0, splits=1, partial=None):
     """Prompt-portion attention on the tcgen05 tensor cores (bfloat16, head size 64 or 128, heads per kv head a
-    divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`."""
-    _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag)
+    divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`.  `splits` > 1 cuts every
+    CTA's keys into that many ranges that run side by side and are merged by a second kernel; `partial` is their
+    32-bit scratch, `attention_prefill_tc_partial_floats` words long."""
+    _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag, partial)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("attention_prefill_tc is a bfloat16 kernel")
+    splits = int(splits)
+    if splits > 1 and (partial is None or partial.dtype != torch.float32
+                       or partial.numel() < attention_prefill_tc_partial_floats(q.shape[0], nq, d, splits)):
+        raise KernelError("attention_prefill_tc: the ranges need 32-bit scratch of attention_prefill_tc_partial_floats words")
     with _timed("attention_prefill_tc", label, 0, work_flops):
         _check(lib().lia_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
                                               _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
-                                              k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], _p(error_flag),
-                                              _stream()),
+                                              k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], splits,
+                                              _p(partial) if splits > 1 else None, q.shape[0], _p(error_flag), _stream()),
                "attention_prefill_tc")
+
+
+def attention_prefill_tc_partial_floats(n_tokens: int, nq: int, d: int, splits: int) -> int:
+    return int(splits) * int(n_tokens) * int(nq) * (int(d) + 2)
 
 
 _select_scratch = {}

@@ -78,6 +78,15 @@ class PagedAttention:
             plan = self._decode_plans[(rows, wanted)] = (clustered, True) if clustered >= 2 else (wanted, False)
         return plan
 
+    def prefill_splits(self, ctx, tiles: int) -> int:
+        """Into how many ranges the tcgen05 prompt kernel cuts the keys of each of its CTAs: as many as give every
+        SM a CTA, none shorter than 1,024 keys at the step's context bucket (so none before 1,024 tokens), at most 16.  A whole prompt has CTAs
+        enough and is not cut; a short portion late in a long prompt is (the reference cuts a tile's keys into parts
+        of 4,096 and merges them: src/inference/llama_plan.rs:76-99).  It depends on the portions' lengths and the
+        context bucket alone, as a captured step needs."""
+        ctas = max(1, tiles * self.nkv)
+        return max(1, min(ctx.runtime.sm_count // ctas, 16, ctx.context_bucket // 1024))
+
     def _decode_scratch(self, ctx, rows: int, n_splits: int):
         if n_splits <= 1:
             return None, None
@@ -127,8 +136,15 @@ class PagedAttention:
             kernel, per_tile = self._prefill
             if per_tile:
                 tiles = sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1)
+                more = {}
+                if kernel is ops.attention_prefill_tc:
+                    splits = self.prefill_splits(ctx, tiles)
+                    if splits > 1:
+                        words = ops.attention_prefill_tc_partial_floats(ctx.n_tokens, nq, d, splits)
+                        more = dict(splits=splits, partial=ctx.runtime.scratch("attn.prefill_partial", words, torch.float32))
                 kernel(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles, ctx.slots,
-                       kv.block_table, out, nq, nkv, d, self.window, self.scale, ctx.error_flag, work_flops=work_flops)
+                       kv.block_table, out, nq, nkv, d, self.window, self.scale, ctx.error_flag, work_flops=work_flops,
+                       **more)
             else:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, nq, nkv,
                                       d, self.window, self.scale, rows=ctx.prefill_rows, error_flag=ctx.error_flag)

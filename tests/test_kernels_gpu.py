@@ -614,6 +614,23 @@ def test_attention_prefill_portions(d, nq, nkv, page_size, window, kernel):
     assert float((got[:150] - want_b).abs().max()) <= limit
     assert float((got[150:] - want_a).abs().max()) <= limit
     assert float((got[-1, 0] - va[far, 0].double()).abs().max()) < 0.05
+    if tc:
+        # the keys of every CTA cut into ranges that are merged afterwards: 7 is more than the tiles of either request,
+        # so some ranges are empty; the scratch starts as NaN, so a word that is read without having been written shows
+        for splits in (2, 3, 7):
+            partial = torch.full((ops().attention_prefill_tc_partial_floats(n, nq, d, splits),), float("nan"), device=DEV)
+            cut = torch.zeros(n, nq * d, device=DEV, dtype=torch.bfloat16)
+            ops().attention_prefill_tc(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), cut, nq, nkv, d,
+                                       window, scale, flag, splits=splits, partial=partial)
+            torch.cuda.synchronize()
+            assert flag.item() == 0
+            got = cut.view(n, nq, d).double()
+            assert float((got[:150] - want_b).abs().max()) <= limit, splits
+            assert float((got[150:] - want_a).abs().max()) <= limit, splits
+            assert float((got[-1, 0] - va[far, 0].double()).abs().max()) < 0.05
+        with pytest.raises(Exception):
+            ops().attention_prefill_tc(q.view(n, nq * d), kp, vp, segments, 2, tiles, slots, bt.to(DEV), cut, nq, nkv, d,
+                                       window, scale, flag, splits=2, partial=partial[:16])
 
 
 @pytest.mark.parametrize("d,nq,nkv,page_size,window,rotary_dim,n_splits", [

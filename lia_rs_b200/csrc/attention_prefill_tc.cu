@@ -271,18 +271,21 @@ attention_prefill_tc_kernel(Params p) {
         // ---- MMA issuer ----
         const uint32_t idesc_s = instr_desc(ROWS, KT), idesc_o = instr_desc_b_mn(ROWS, D);
         bool ok = mbar_wait(smem_u32(&q_full), 0u);
+        // the operands' descriptors: the tile's first plus an offset in their lowest field (the start address in 16-byte
+        // units; shared memory ends below what the field holds), so that an MMA costs this thread an addition
+        static_assert(ROWS == KT, "Q and K tiles share their offsets");
+        const uint64_t desc_q0 = smem_desc(q_s), desc_kv0 = smem_desc(kv_s), desc_v0 = smem_desc_mn(kv_s + KV_BYTES, KT * 128, 1024);
         // S_j = Q K_j^T into score buffer j & 1: issued one tile ahead, so that it runs while the softmax of the
         // tile before is at work (that buffer's last reader arrived on p_ready two tiles ago)
         auto first_product = [&](int j) {
             const int st = j % STAGES;
-            const uint32_t ks = kv_s + (uint32_t)st * 2 * KV_BYTES;
             if (!mbar_wait(smem_u32(&k_full[st]), (uint32_t)(j / STAGES) & 1u)) { ok = false; return; }
             tc_fence_after();
+            const uint64_t desc_k = desc_kv0 + (uint64_t)((uint32_t)st * (2 * KV_BYTES >> 4));
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t a = q_s + (uint32_t)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
-                const uint32_t b = ks + (uint32_t)((kk >> 2) * (KT * 128) + (kk & 3) * 32);
-                tc_mma(tmem_s + (uint32_t)((j & 1) * KT), smem_desc(a), smem_desc(b), idesc_s, kk > 0 ? 1u : 0u);
+                const uint64_t offset = (uint64_t)(((kk >> 2) * (ROWS * 128) + (kk & 3) * 32) >> 4);      // Q and K tiles are laid out alike
+                tc_mma(tmem_s + (uint32_t)((j & 1) * KT), desc_q0 + offset, desc_k + offset, idesc_s, kk > 0 ? 1u : 0u);
             }
             tc_commit(smem_u32(&s_full[j & 1]));
             tc_commit(smem_u32(&k_empty[st]));
@@ -290,7 +293,7 @@ attention_prefill_tc_kernel(Params p) {
         if (ok) first_product(0);
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j % STAGES;
-            const uint32_t vs = kv_s + (uint32_t)st * 2 * KV_BYTES + KV_BYTES;
+            const uint64_t desc_v = desc_v0 + (uint64_t)((uint32_t)st * (2 * KV_BYTES >> 4));
             if (j + 1 < n_tiles) first_product(j + 1);
             if (!ok) break;
             // O += P V once the values lie in shared memory and the probabilities in TMEM (and O has been rescaled if it had to be)
@@ -299,8 +302,8 @@ attention_prefill_tc_kernel(Params p) {
             tc_fence_after();
 #pragma unroll
             for (int ks16 = 0; ks16 < KT / 16; ++ks16) {
-                const uint32_t b = vs + (uint32_t)(ks16 * 2048);              // 16 keys = two groups of 8 rows
-                tc_mma_ts(tmem_o, tmem_p + (uint32_t)((j & 1) * (KT / 2) + ks16 * 8), smem_desc_mn(b, KT * 128, 1024), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
+                // (16 keys = two groups of 8 rows = 2,048 bytes further in the tile)
+                tc_mma_ts(tmem_o, tmem_p + (uint32_t)((j & 1) * (KT / 2) + ks16 * 8), desc_v + (uint64_t)(ks16 * (2048 >> 4)), idesc_o, (j > 0 || ks16 > 0) ? 1u : 0u);
             }
             tc_commit(smem_u32(&v_empty[st]));
             tc_commit(smem_u32(&p_free[j & 1]));       // this tile's buffer of probabilities is free again, and O holds the tile

@@ -171,22 +171,28 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         bool ok = true;
         int mine = 0;                                         // K blocks this issuer has taken
         if (me < issuers) {
+            // (the stage and its phase are counted along, and the descriptors are the first stage's plus an offset in
+            // their lowest field, the start address in 16-byte units: what this thread does between two MMAs is
+            // what a K block of a narrow tile takes)
+            const uint64_t desc_a0 = smem_desc(smem_base), desc_b0 = smem_desc(smem_base + A_TILES * a_bytes);
+            const uint32_t stage_step = stage_bytes >> 4, a_step = a_bytes >> 4;
+            int st = me % s.stages;
+            uint32_t phase = (uint32_t)(me / s.stages) & 1u;
             for (int it = me; it < nkb; it += issuers, ++mine) {
-                const int st = it % s.stages;
-                if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&full_bar[st]), phase)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
-                const uint32_t b_addr = a_addr + A_TILES * a_bytes;
+                const uint64_t da0 = desc_a0 + (uint64_t)((uint32_t)st * stage_step), db0 = desc_b0 + (uint64_t)((uint32_t)st * stage_step);
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / 16; ++k) {
-                    const uint64_t db = smem_desc(b_addr + k * 32);
                     const int chain = me * own + (k & (own - 1));
                     const uint32_t accumulate = (mine > 0 || k >= own) ? 1u : 0u;
                     const uint32_t acc_addr = tmem_base + (uint32_t)(chain * A_TILES * s.n_tile);
-                    tc_mma(acc_addr, smem_desc(a_addr + k * 32), db, idesc, accumulate);
-                    if (A_TILES == 2) tc_mma(acc_addr + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                    tc_mma(acc_addr, da0 + 2 * k, db0 + 2 * k, idesc, accumulate);
+                    if (A_TILES == 2) tc_mma(acc_addr + (uint32_t)s.n_tile, da0 + a_step + 2 * k, db0 + 2 * k, idesc, accumulate);
                 }
                 tc_commit(smem_u32(&empty_bar[st]));
+                st += issuers;
+                while (st >= s.stages) { st -= s.stages; phase ^= 1u; }
             }
             if (ok) tc_commit(smem_u32(&acc_full));
             else if (s.error_flag) atomicExch(s.error_flag, 3);

@@ -160,15 +160,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             ahead = it;
         }
         pdl_wait();
-        int it = 0;
+        // (the stage and its phase are counted along: a division by the number of stages per K block costs this
+        // thread more than the block's loads)
+        int it = 0, st = 0;
+        uint32_t phase = 0;
         for (int index = first_unit; index < units && ok; index += stride) {
             const Unit u = unit_at(s, index);
-            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-                const int st = it % s.stages;
+            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it, st = (st + 1 == s.stages ? 0 : st + 1), phase ^= (st == 0 ? 1u : 0u)) {
                 const uint32_t full = smem_u32(&full_bar[st]);
                 const uint32_t dst = smem_base + (uint32_t)st * stage_bytes;
                 if (it >= ahead) {
-                    const uint32_t phase = (uint32_t)(it / s.stages) & 1u;
                     if (!mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u)) { ok = false; break; }
                     mbar_expect_tx(full, stage_bytes);
                     tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
@@ -192,7 +193,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int n_first = s.n_tile > 256 ? 256 : s.n_tile, n_rest = s.n_tile - n_first;
         const uint32_t idesc = instr_desc(TILE_F, n_first), idesc_rest = instr_desc(TILE_F, n_rest > 0 ? n_rest : 16);
         bool ok = true;
-        int it = 0, n_unit = 0;
+        int n_unit = 0, st = 0;
+        uint32_t phase = 0;
+        // A narrow tile's K block is four short MMAs, and what this thread does between them sets the block's time:
+        // so the stage and its phase are counted along (no division per block), and the operands' descriptors are
+        // the first stage's plus an offset (the start address is their lowest field, in 16-byte units, and shared
+        // memory ends below what the field holds).
+        const uint64_t desc_a0 = smem_desc(smem_base), desc_b0 = smem_desc(smem_base + A_TILES * a_bytes);
+        const uint64_t stage_step = stage_bytes >> 4, a_step = a_bytes >> 4, rest_step = ((uint32_t)n_first * 128u) >> 4;
+        uint64_t stage_offset = 0;
         for (int index = first_unit; index < units && ok; index += stride, ++n_unit) {
             const Unit u = unit_at(s, index);
             const int buf = s.acc_buffers == 2 ? (n_unit & 1) : 0;
@@ -200,32 +209,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!mbar_wait(smem_u32(&acc_empty[buf]), (use & 1u) ^ 1u)) { ok = false; break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(buf * s.acc_cols);
-            for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-                const int st = it % s.stages;
-                if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / s.stages) & 1u)) { ok = false; break; }
+            for (int kb = u.kb_begin; kb < u.kb_end; ++kb) {
+                if (!mbar_wait(smem_u32(&full_bar[st]), phase)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_base + (uint32_t)st * stage_bytes;
-                const uint32_t b_addr = a_addr + A_TILES * a_bytes;
-                // (the issuing thread sets the pace of a 256-wide tile: the wide tile's second MMA has a loop of its own,
-                // so that the common loop carries nothing for it)
+                const uint64_t da0 = desc_a0 + stage_offset, db0 = desc_b0 + stage_offset;
+                const uint32_t first = kb > u.kb_begin ? 1u : 0u;
+                // (the wide tile's second MMA has a loop of its own, so that the common loop carries nothing for it)
                 if (n_rest == 0) {
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / 16; ++k) {
-                        const uint64_t db = smem_desc(b_addr + k * 32);
-                        const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
-                        tc_mma(acc, smem_desc(a_addr + k * 32), db, idesc, accumulate);
-                        if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, smem_desc(a_addr + a_bytes + k * 32), db, idesc, accumulate);
+                        const uint32_t accumulate = k > 0 ? 1u : first;
+                        tc_mma(acc, da0 + 2 * k, db0 + 2 * k, idesc, accumulate);
+                        if (A_TILES == 2) tc_mma(acc + (uint32_t)s.n_tile, da0 + a_step + 2 * k, db0 + 2 * k, idesc, accumulate);
                     }
                 } else {
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / 16; ++k) {
-                        const uint64_t da = smem_desc(a_addr + k * 32);
-                        const uint32_t accumulate = (kb > u.kb_begin || k > 0) ? 1u : 0u;
-                        tc_mma(acc, da, smem_desc(b_addr + k * 32), idesc, accumulate);
-                        tc_mma(acc + (uint32_t)n_first, da, smem_desc(b_addr + (uint32_t)n_first * 128u + k * 32), idesc_rest, accumulate);
+                        const uint32_t accumulate = k > 0 ? 1u : first;
+                        tc_mma(acc, da0 + 2 * k, db0 + 2 * k, idesc, accumulate);
+                        tc_mma(acc + (uint32_t)n_first, da0 + 2 * k, db0 + rest_step + 2 * k, idesc_rest, accumulate);
                     }
                 }
                 tc_commit(smem_u32(&empty_bar[st]));      // the stage is free when these MMAs have read it
+                if (++st == s.stages) { st = 0; stage_offset = 0; phase ^= 1u; }
+                else stage_offset += stage_step;
             }
             if (ok) tc_commit(smem_u32(&acc_full[buf]));  // the accumulator is complete
         }
@@ -403,15 +410,17 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
         while (p.n_tile < M) p.n_tile *= 2;
     } else {
         // many tokens: the tile width (a multiple of 32, the epilogue's step) that leaves the SMs least idle: rounds of
-        // tiles times the time of one.  Measured on a B200: a tile takes 5.5 us plus, per K block, its MMAs' time (0.43 us
-        // at 256 tokens, in proportion below; twice that for the gated product's two accumulators) but no less than
-        // what its issuing threads need whatever the width (0.36 us: four MMAs and two TMA loads; 0.58 us gated).
-        // Ties go to the wider tile (fewer bytes through shared memory per flop).  Up to 512 tokens wide (all of
-        // TMEM, so one buffer: the epilogue and the next tile take turns), 256 for the gated product, where that saves
-        // a round: 2,048 tokens x 2,560 features are 140 tiles of 320 tokens, one round, against 260 of 160.  Down
-        // to 32 tokens where the tiles would otherwise be too few for the SMs: K is NOT cut for more than 128 tokens
-        // (the CTA that arrives last would add up ranges of hundreds of tokens alone, which costs more than narrow
-        // tiles do).
+        // tiles times the time of one.  Measured on a B200: a tile takes 5.5 us plus, per K block, the longest of
+        // three: its MMAs' time (0.43 us at 256 tokens at the clocks a long product runs at, in proportion below;
+        // twice that for the gated product's two accumulators); the time its SM needs to take the block in (an SM
+        // takes in about 108 GB/s: 16 KB of W, or 32, and 128 bytes per token; this is what a narrow tile waits
+        // for, and why narrower tiles on more SMs beat wide ones on few); and what its producer thread needs to
+        // issue the block's two to four TMA boxes (0.1 us each).  Ties go to the wider tile (fewer bytes through
+        // shared memory per flop).  Up to 512 tokens wide (all of TMEM, so one buffer: the epilogue and the next tile
+        // take turns), 256 for the gated product, where that saves a round: 2,048 tokens x 2,560 features are 140
+        // tiles of 320 tokens, one round, against 260 of 160.  Down to 32 tokens where the tiles would otherwise be
+        // too few for the SMs: K is NOT cut for more than 128 tokens (the CTA that arrives last would add up ranges
+        // of hundreds of tokens alone, which costs more than narrow tiles do).
         const double weights = swiglu ? 2.0 : 1.0;
         const int widest = std::min(swiglu ? 256 : 512, (M + 31) / 32 * 32);
         double best = -1;
@@ -419,8 +428,10 @@ Plan make_plan(int mode, int M, int N, int K, int sm_count, long long scratch_fl
         for (int n = widest; n >= 32; n -= 32) {
             const long long tiles = (long long)p.f_tiles * ((M + n - 1) / n);
             const long long rounds = (tiles + sm_count - 1) / sm_count;
-            const double mma = weights * 0.43 * n / 256.0, issue = swiglu ? 0.58 : 0.36;
-            const double cost = (double)rounds * (5.5 + kblocks * std::max(mma, issue));
+            const double mma = weights * 0.43 * n / 256.0;
+            const double intake = (weights * 16384.0 + n * 128.0) / 108e3;
+            const double issue = 0.1 * (weights + (n > 256 ? 2.0 : 1.0));
+            const double cost = (double)rounds * (5.5 + kblocks * std::max(mma, std::max(intake, issue)));
             if (best < 0 || cost < best) { best = cost; p.n_tile = n; }
         }
     }

@@ -14,8 +14,9 @@
   streams the weights once with one CTA per 16 rows (csrc/gemm_skinny.cu); beyond 16 tokens, the tcgen05 kernel that cuts K over a cluster (csrc/gemm_cluster.cu)
   while it applies (16 tokens of a 2B-class layer: 58 us with the few-token kernel, 63 us with the cluster
   kernel; 24 tokens: 82 against 66; 32 tokens: 91 against 70: every CTA of the few-token kernel reads all the
-  tokens' rows from L2); then the persistent tcgen05 kernel, which cuts K through scratch memory up to 128
-  tokens and beyond that cuts the tokens into tiles as narrow as fills the SMs;
+  tokens' rows from L2) and up to 256 tokens; then the persistent tcgen05 kernel, which cuts K through scratch
+  memory up to 128 tokens and beyond that cuts the tokens into tiles as narrow as fills the SMs (a 2B-class
+  layer's four products at 512 tokens: 90 us, at 256 tokens 70 us with the cluster kernel for three of them);
 * what TMA cannot address goes to the few-token kernel if it can take it, else, and always for the 32-bit
   path, to the product on the 32-bit pipes (csrc/gemm_simt.cu)."""
 from __future__ import annotations
@@ -33,6 +34,7 @@ def prepare_weight(weight: torch.Tensor, runtime) -> torch.Tensor:
 
 
 SKINNY_BEST_TOKENS = 16
+CLUSTER_MAX_TOKENS = 256        # beyond, narrow tiles of the persistent kernel are as fast or faster (2,048 x 2,048 at 512 tokens: 14.9 against 18.2 us)
 
 
 _TC, _SKINNY, _CLUSTER, _SIMT, _STREAM = range(5)
@@ -48,7 +50,7 @@ def _choose(mode, a, w, out) -> int:
         return _TC
     if few and a.shape[0] <= SKINNY_BEST_TOKENS:
         return _SKINNY
-    if tensor_cores and ops.gemm_cluster_accepts(mode, a, w, out):
+    if tensor_cores and a.shape[0] <= CLUSTER_MAX_TOKENS and ops.gemm_cluster_accepts(mode, a, w, out):
         return _CLUSTER
     if tensor_cores:
         return _TC

@@ -280,14 +280,14 @@ gemm_stream_kernel(Args a) {
         //      memory at work until the kernel ahead has finished), the rest when the rows have been asked for.
         //      (The whole warp walks the loop, since a named barrier counts warps.) ----
         bool asked = false, ok = true;
-        int it = 0;
+        int it = 0, st = 0;
+        uint32_t phase = 0;                                           // of the stage's use: counted along, not divided out
         const bool whole_rows = a.chunks == 1 && a.ldw == a.K;       // a half of a stage is one piece of memory
         for (int block = blockIdx.x; block < a.blocks && ok; block += grid) {
-            for (int c = 0; c < a.chunks; ++c, ++it) {
+            for (int c = 0; c < a.chunks; ++c, ++it, st = (st + 1 == a.stages ? 0 : st + 1), phase ^= (st == 0 ? 1u : 0u)) {
                 if (it == a.early && !asked) { __syncwarp(); asked_wait<ASKED>(); asked = true; }
-                const int st = it % a.stages;
                 if (it >= a.stages) {
-                    if (lane == 0) ok = mbar_wait(smem_u32(&empty_bar[st]), ((uint32_t)(it / a.stages) & 1u) ^ 1u);
+                    if (lane == 0) ok = mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                 }
@@ -499,7 +499,8 @@ gemm_stream_kernel(Args a) {
         (void)x_base;
 
         bool ok = true;
-        int it = 0, ui = 0;
+        int it = 0, ui = 0, st = 0;
+        uint32_t phase = 0;                                           // of the stage's use: counted along, not divided out
         for (int block = blockIdx.x; block < a.blocks && ok; block += grid, ++ui) {
             // Eight accumulators per tile of tokens: an mma.sync takes some hundred cycles from issue to result, so a
             // warp keeps eight of them in flight, none waiting for another (four groups of 32 k, two instructions each).
@@ -513,8 +514,7 @@ gemm_stream_kernel(Args a) {
             if (XG > 0) {
 #pragma unroll
                 for (int c = 0; c < (CHUNKS > 0 ? CHUNKS : 1); ++c) {
-                    const int st = it % a.stages;
-                    if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / a.stages) & 1u)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&full_bar[st]), phase)) { ok = false; break; }
                     const uint8_t* stage = smem + (size_t)st * a.stage_bytes + w_offset + warp * 64;
 #pragma unroll
                     for (int i0 = 0; i0 < PWR; i0 += 4) {
@@ -540,13 +540,13 @@ gemm_stream_kernel(Args a) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&empty_bar[st]));
                     ++it;
+                    if (++st == a.stages) { st = 0; phase ^= 1u; }
                 }
             } else {
-                for (int c = 0; c < a.chunks; ++c, ++it) {
-                    const int st = it % a.stages;
+                for (int c = 0; c < a.chunks; ++c, ++it, st = (st + 1 == a.stages ? 0 : st + 1), phase ^= (st == 0 ? 1u : 0u)) {
                     const int k0 = c * a.ck;
                     const int groups = min(groups_per_chunk, (a.K - k0) >> 5);      // K is a multiple of 64: whole groups
-                    if (!mbar_wait(smem_u32(&full_bar[st]), (uint32_t)(it / a.stages) & 1u)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&full_bar[st]), phase)) { ok = false; break; }
                     const uint8_t* stage = smem + (size_t)st * a.stage_bytes + w_offset;
                     const uint8_t* xk = x_base + (size_t)k0 * 2;
                     for (int base = warp; base < groups; base += 4 * MMA_WARPS) {

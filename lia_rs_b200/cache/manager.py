@@ -160,6 +160,19 @@ class CacheGroup:
         fence.record()
 
 
+class _Lengths:
+    """`manager.length[slot]`: up to where the native cache has ensured the slot's positions."""
+
+    def __init__(self, manager):
+        self._manager = manager
+
+    def __getitem__(self, slot: int) -> int:
+        value = int(self._manager._lib.lia_cache_length(self._manager._handle, int(slot)))
+        if value < 0:
+            raise_last()
+        return value
+
+
 class CacheManager:
     """`cache_requests`: cache id -> KVCacheRequest; `state_requests`: state id -> StateRequest.
     `num_pages` pages of `page_size` tokens per group; `max_context` bounds a request's positions."""
@@ -190,41 +203,47 @@ class CacheManager:
         self.group_of = {c: g for g in self.groups for c in g.cache_ids}
         self.states = {sid: torch.zeros((max_slots, *req.shape), dtype=req.dtype, device=device)
                        for sid, req in state_requests.items()}
-        self._free_slots = list(range(max_slots - 1, -1, -1))
-        self._live = set()
-        self.length = [0] * max_slots          # positions [0, length) have been ensured
+        self.length = _Lengths(self)           # positions [0, length[slot]) of a live slot have been ensured
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
         if handle:
             self._lib.lia_cache_destroy(handle)
 
-    # ---- slots ----
+    # ---- slots (kept by the native cache: the scheduler's native policy works on the same state) ----
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return int(self._lib.lia_cache_free_slots(self._handle))
+
+    def is_live(self, slot: int) -> bool:
+        return bool(self._lib.lia_cache_is_live(self._handle, int(slot)))
+
+    def reserved(self, slots) -> list:
+        """For each slot: up to where it has pages, or -1 when it is not live."""
+        n = len(slots)
+        Array = ctypes.c_int * max(1, n)
+        out = Array()
+        self._lib.lia_cache_reserved(self._handle, Array(*slots), n, out)
+        return out[:n]
 
     def live_slots(self):
-        return sorted(self._live)
+        return [slot for slot in range(self.max_slots) if self.is_live(slot)]
 
     def admit(self) -> int:
         """Take a slot for a new request; its state is zeroed.  Raises when none is free."""
-        if not self._free_slots:
-            raise PageError("no free request slot")
-        slot = self._free_slots.pop()
-        self._live.add(slot)
-        self.length[slot] = 0
-        for state in self.states.values():
-            state[slot].zero_()
+        slot = int(self._lib.lia_cache_admit(self._handle))
+        if slot < 0:
+            raise_last()
+        self.admitted(slot)
         return slot
 
+    def admitted(self, slot: int) -> None:
+        """What the face owes a slot that the native side has just handed out: its state zeroed."""
+        for state in self.states.values():
+            state[slot].zero_()
+
     def release(self, slot: int) -> None:
-        if slot not in self._live:
-            raise PageError(f"slot {slot} released twice or never admitted")
         if self._lib.lia_cache_release_slot(self._handle, int(slot)) < 0:
             raise_last()
-        self._live.remove(slot)
-        self._free_slots.append(slot)
-        self.length[slot] = 0
 
     # ---- pages ----
     def available_pages(self) -> int:
@@ -240,17 +259,11 @@ class CacheManager:
         return worst
 
     def ensure(self, slot: int, start: int, end: int) -> bool:
-        """Make pages present for positions [start, end) of `slot` in every group, all or nothing.
+        """Make pages present for positions [start, end) of the live slot `slot` in every group, all or nothing.
         False: some group has too few free pages (nothing was changed)."""
-        if slot not in self._live:
-            raise PageError(f"slot {slot} is not live")
-        if not 0 <= start < end or end > self.max_context:
-            raise PageError(f"positions [{start}, {end}) are outside the context of {self.max_context}")
-        done = self._lib.lia_cache_ensure(self._handle, int(slot), int(start), int(end))
+        done = self._lib.lia_cache_ensure(self._handle, int(slot), int(start), int(end), self.max_context)
         if done < 0:
             raise_last()
-        if done:
-            self.length[slot] = max(self.length[slot], end)
         return bool(done)
 
     def flush(self) -> None:
@@ -268,7 +281,7 @@ class CacheManager:
 
     def check(self) -> None:
         """Assert the invariants: no page lost, none held twice, none both free and held."""
-        live = sorted(self._live)
+        live = self.live_slots()
         Array = ctypes.c_int * max(1, len(live))
         for group in self.groups:
             if self._lib.lia_cache_check(self._handle, group.index, Array(*live), Array(*[self.length[s] for s in live]),
@@ -279,7 +292,9 @@ class CacheManager:
                 table = group.tables[slot]
                 if group.host_view[slot, :len(table)].tolist() != table:
                     raise PageError(f"group {group.index}, slot {slot}: the host table differs from the slot's table")
-        if len(set(self._free_slots)) != len(self._free_slots) or set(self._free_slots) & self._live:
+        free = (ctypes.c_int * self.max_slots)()
+        free = list(free[:self._lib.lia_cache_free_slot_list(self._handle, free)])
+        if len(set(free)) != len(free) or set(free) & set(live):
             raise PageError("a slot is both free and live, or free twice")
-        if len(self._free_slots) + len(self._live) != self.max_slots:
+        if len(free) + len(live) != self.max_slots:
             raise PageError("a slot was lost")

@@ -8,177 +8,22 @@
 // pinned host copy of the table (`host_table`, given at creation) and remembers, per slot, the range of blocks
 // that changed since the last `lia_cache_take_dirty`, so that only those go to the device.
 //
+// The request slots live here too (which are free, which are live, up to where each has pages), so that the
+// scheduler's policy (scheduler_host.cpp) and the Python face `cache.CacheManager` see one state.
+//
 // Every function returns 0 or a count on success and a negative code on a refusal; `lia_host_error` gives the
 // message of the last refusal on this thread.  Nothing here throws across the C boundary.
-#include <stdint.h>
 #include <stdio.h>
 #include <string.h>
 
-#include <algorithm>
 #include <new>
-#include <string>
-#include <vector>
+
+#include "cache_host.h"
 
 #define LIA_HOST_EXPORT extern "C" __attribute__((visibility("default")))
 
-namespace {
-thread_local std::string last_error;
+using namespace lia_host;
 
-int refuse(const std::string& message) {
-    last_error = message;
-    return -1;
-}
-
-struct Pool {
-    int num_pages = 0;
-    std::vector<int> free_list;          // back() is handed out next: a page just given back is used again first
-    std::vector<int> users;
-
-    explicit Pool(int n) : num_pages(n), users((size_t)n, 0) {
-        free_list.reserve((size_t)n);
-        for (int page = n - 1; page >= 0; --page) free_list.push_back(page);     // page 0 first
-    }
-    int available() const { return (int)free_list.size(); }
-    int allocate() {
-        if (free_list.empty()) return refuse("page pool exhausted");
-        const int page = free_list.back();
-        if (users[(size_t)page] != 0) return refuse("page " + std::to_string(page) + " on the free list is held");
-        free_list.pop_back();
-        users[(size_t)page] = 1;
-        return page;
-    }
-    int release(int page) {
-        if (page < 0 || page >= num_pages) return refuse("page " + std::to_string(page) + " is outside the pool");
-        if (users[(size_t)page] <= 0) return refuse("page " + std::to_string(page) + " freed twice");
-        if (--users[(size_t)page] == 0) free_list.push_back(page);
-        return 0;
-    }
-    // Every page is on the free list once or held by exactly the given holders (`held`: the pages the block tables hold).
-    int check(const std::vector<int>& held) const {
-        std::vector<int> on_free((size_t)num_pages, 0), holders((size_t)num_pages, 0);
-        for (int page : free_list) {
-            if (page < 0 || page >= num_pages) return refuse("the free list names page " + std::to_string(page));
-            if (++on_free[(size_t)page] > 1) return refuse("a page is on the free list twice");
-        }
-        for (int page : held) {
-            if (page < 0 || page >= num_pages) return refuse("a block table names page " + std::to_string(page));
-            ++holders[(size_t)page];
-        }
-        for (int page = 0; page < num_pages; ++page) {
-            if (users[(size_t)page] != holders[(size_t)page])
-                return refuse("page " + std::to_string(page) + ": " + std::to_string(users[(size_t)page]) + " users recorded, " +
-                              std::to_string(holders[(size_t)page]) + " holders found");
-            if ((holders[(size_t)page] == 0) != (on_free[(size_t)page] == 1))
-                return refuse("page " + std::to_string(page) + " is lost or both held and free");
-        }
-        return 0;
-    }
-};
-
-struct Plan {
-    std::vector<int> allocate, give_back;
-    int keep_from = 0;
-};
-
-struct Group {
-    Pool pool;
-    int page_size, window, max_slots, max_blocks;      // window < 0: all keys
-    int32_t* host_table;                               // [max_slots, max_blocks], -1: no page
-    std::vector<std::vector<int>> tables;              // per slot: page of each logical block, or -1
-    std::vector<int> first_block;                      // blocks before this were given back
-    std::vector<int> dirty_lo, dirty_hi;               // per slot: the range of blocks to copy (lo < 0: none)
-    std::vector<int> dirty_slots;                      // slots with a range, in the order they became dirty
-
-    Group(int pages, int page_size_, int window_, int slots, int blocks, int32_t* table)
-        : pool(pages), page_size(page_size_), window(window_), max_slots(slots), max_blocks(blocks), host_table(table),
-          tables((size_t)slots), first_block((size_t)slots, 0), dirty_lo((size_t)slots, -1), dirty_hi((size_t)slots, 0) {}
-
-    void mark(int slot, int lo, int hi) {
-        if (dirty_lo[(size_t)slot] < 0) {
-            dirty_lo[(size_t)slot] = lo;
-            dirty_hi[(size_t)slot] = hi;
-            dirty_slots.push_back(slot);
-        } else {
-            dirty_lo[(size_t)slot] = std::min(dirty_lo[(size_t)slot], lo);
-            dirty_hi[(size_t)slot] = std::max(dirty_hi[(size_t)slot], hi);
-        }
-    }
-    // The blocks of a slot's table from first_block on are all present (blocks are only ever given back from the
-    // front, and allocated without gaps), so only the table's ends are looked at: a decode step costs the same
-    // whatever the context length.
-    void needed(int slot, int start, int end, Plan* plan) const {
-        const std::vector<int>& table = tables[(size_t)slot];
-        const int n = (int)table.size(), first = first_block[(size_t)slot];
-        int keep_from = 0;
-        if (window >= 0) keep_from = std::max(0, start - window + 1) / page_size;
-        plan->allocate.clear();
-        plan->give_back.clear();
-        plan->keep_from = keep_from;
-        for (int b = first; b < std::min(keep_from, n); ++b)
-            if (table[(size_t)b] >= 0) plan->give_back.push_back(b);
-        const int last = (end - 1) / page_size;
-        for (int b = keep_from; b < std::min(first, last + 1); ++b) plan->allocate.push_back(b);       // given back earlier, wanted again
-        for (int b = std::max(keep_from, n); b <= last; ++b) plan->allocate.push_back(b);              // beyond the table's end
-    }
-    // The same by looking at every block (what the invariant check compares `needed` with).
-    void needed_by_scan(int slot, int start, int end, Plan* plan) const {
-        const std::vector<int>& table = tables[(size_t)slot];
-        const int n = (int)table.size();
-        int keep_from = 0;
-        if (window >= 0) keep_from = std::max(0, start - window + 1) / page_size;
-        plan->allocate.clear();
-        plan->give_back.clear();
-        plan->keep_from = keep_from;
-        for (int b = first_block[(size_t)slot]; b < std::min(keep_from, n); ++b)
-            if (table[(size_t)b] >= 0) plan->give_back.push_back(b);
-        const int last = (end - 1) / page_size;
-        for (int b = keep_from; b <= last; ++b)
-            if (b >= n || table[(size_t)b] < 0) plan->allocate.push_back(b);
-    }
-    int apply(int slot, const Plan& plan) {
-        std::vector<int>& table = tables[(size_t)slot];
-        int32_t* row = host_table + (size_t)slot * max_blocks;
-        for (int b : plan.give_back) {
-            if (pool.release(table[(size_t)b]) < 0) return -1;
-            table[(size_t)b] = -1;
-            row[b] = -1;
-            mark(slot, b, b + 1);
-        }
-        first_block[(size_t)slot] = std::max(first_block[(size_t)slot], std::min(plan.keep_from, (int)table.size()));
-        for (int b : plan.allocate) {
-            if (b >= max_blocks) return refuse("block " + std::to_string(b) + " is beyond the table's " + std::to_string(max_blocks));
-            while ((int)table.size() <= b) table.push_back(-1);
-            const int page = pool.allocate();
-            if (page < 0) return -1;
-            table[(size_t)b] = page;
-            row[b] = page;
-            mark(slot, b, b + 1);
-        }
-        return 0;
-    }
-    int release_slot(int slot) {
-        std::vector<int>& table = tables[(size_t)slot];
-        for (int page : table)
-            if (page >= 0 && pool.release(page) < 0) return -1;
-        if (!table.empty()) {
-            int32_t* row = host_table + (size_t)slot * max_blocks;
-            for (size_t b = 0; b < table.size(); ++b) row[b] = -1;
-            mark(slot, 0, (int)table.size());
-        }
-        table.clear();
-        first_block[(size_t)slot] = 0;
-        return 0;
-    }
-};
-
-struct Cache {
-    std::vector<Group> groups;
-    int max_slots = 0;
-    std::vector<Plan> plans;             // scratch of ensure
-};
-
-bool bad_slot(const Cache* cache, int slot) { return slot < 0 || slot >= cache->max_slots; }
-}  // namespace
 
 LIA_HOST_EXPORT const char* lia_host_error() { return last_error.c_str(); }
 
@@ -217,71 +62,72 @@ LIA_HOST_EXPORT void* lia_cache_create(int n_groups, const int* num_pages, const
         cache->groups.emplace_back(num_pages[g], page_sizes[g], windows[g], max_slots, max_blocks, host_tables[g]);
     }
     cache->plans.resize((size_t)n_groups);
+    cache->live.assign((size_t)max_slots, 0);
+    cache->length.assign((size_t)max_slots, 0);
+    for (int slot = max_slots - 1; slot >= 0; --slot) cache->free_slots.push_back(slot);      // slot 0 first
     return cache;
 }
 LIA_HOST_EXPORT void lia_cache_destroy(void* cache) { delete static_cast<Cache*>(cache); }
 
 LIA_HOST_EXPORT int lia_cache_available(void* handle, int group) { return static_cast<Cache*>(handle)->groups[(size_t)group].pool.available(); }
 
-// Free pages that ensure(slot, start, end) would need in the tightest group, counting what it would first give back.
-LIA_HOST_EXPORT int lia_cache_pages_for(void* handle, int slot, int start, int end) {
+// ---- request slots ----
+LIA_HOST_EXPORT int lia_cache_free_slots(void* handle) { return (int)static_cast<Cache*>(handle)->free_slots.size(); }
+LIA_HOST_EXPORT int lia_cache_admit(void* handle) { return static_cast<Cache*>(handle)->admit(); }
+LIA_HOST_EXPORT int lia_cache_is_live(void* handle, int slot) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
-    int worst = 0;
-    Plan plan;
-    for (Group& group : cache->groups) {
-        if (group.window < 0 && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size()) continue;
-        group.needed(slot, start, end, &plan);
-        worst = std::max(worst, (int)plan.allocate.size() - (int)plan.give_back.size());
-    }
-    return worst;
+    return !cache->bad_slot(slot) && cache->live[(size_t)slot];
 }
-
-// Pages for positions [start, end) of `slot` in every group, all or nothing: 1 done, 0 some group has too few free
-// pages (nothing was changed), negative a refusal.
-LIA_HOST_EXPORT int lia_cache_ensure(void* handle, int slot, int start, int end) {
+LIA_HOST_EXPORT int lia_cache_length(void* handle, int slot) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
-    bool present = true;
-    for (const Group& group : cache->groups)
-        present = present && group.window < 0 && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size();
-    if (present) return 1;                               // every position already has its page (most decode steps)
-    for (size_t g = 0; g < cache->groups.size(); ++g) {
-        Group& group = cache->groups[g];
-        group.needed(slot, start, end, &cache->plans[g]);
-        if ((int)cache->plans[g].allocate.size() - (int)cache->plans[g].give_back.size() > group.pool.available()) return 0;
-    }
-    for (size_t g = 0; g < cache->groups.size(); ++g)
-        if (cache->groups[g].apply(slot, cache->plans[g]) < 0) return -1;
-    return 1;
+    return cache->bad_slot(slot) ? refuse("slot outside the cache") : cache->length[(size_t)slot];
 }
-
-LIA_HOST_EXPORT int lia_cache_release_slot(void* handle, int slot) {
+// For each of `n` slots: up to where it has pages, or -1 when it is not live (one call for a step's entries).
+LIA_HOST_EXPORT int lia_cache_reserved(void* handle, const int* slots, int n, int* out) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
-    for (Group& group : cache->groups)
-        if (group.release_slot(slot) < 0) return -1;
+    for (int i = 0; i < n; ++i)
+        out[i] = (cache->bad_slot(slots[i]) || !cache->live[(size_t)slots[i]]) ? -1 : cache->length[(size_t)slots[i]];
     return 0;
 }
+// The free slots into `out` (room for max_slots), in the order of the list; returns how many.
+LIA_HOST_EXPORT int lia_cache_free_slot_list(void* handle, int* out) {
+    Cache* cache = static_cast<Cache*>(handle);
+    for (size_t i = 0; i < cache->free_slots.size(); ++i) out[i] = cache->free_slots[i];
+    return (int)cache->free_slots.size();
+}
+
+// Free pages that ensure(slot, start, end) would need in the tightest group, counting what it would first give back.
+LIA_HOST_EXPORT int lia_cache_pages_for(void* handle, int slot, int start, int end) {
+    return static_cast<Cache*>(handle)->pages_for(slot, start, end);
+}
+
+// Pages for positions [start, end) of the live slot `slot` in every group, all or nothing: 1 done, 0 some group has too
+// few free pages (nothing was changed), negative a refusal.
+LIA_HOST_EXPORT int lia_cache_ensure(void* handle, int slot, int start, int end, int max_context) {
+    return static_cast<Cache*>(handle)->ensure(slot, start, end, max_context);
+}
+
+// The slot's pages are given back and the slot is free again.
+LIA_HOST_EXPORT int lia_cache_release_slot(void* handle, int slot) { return static_cast<Cache*>(handle)->release(slot); }
 
 // The table of `slot` in `group` (page per logical block, -1: none) into `out` (up to `capacity` entries); returns
 // its length.
 LIA_HOST_EXPORT int lia_cache_table(void* handle, int group, int slot, int* out, int capacity) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
+    if (cache->bad_slot(slot)) return refuse("slot outside the cache");
     const std::vector<int>& table = cache->groups[(size_t)group].tables[(size_t)slot];
     for (size_t b = 0; b < table.size() && (int)b < capacity; ++b) out[b] = table[b];
     return (int)table.size();
 }
 LIA_HOST_EXPORT int lia_cache_first_block(void* handle, int group, int slot) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
+    if (cache->bad_slot(slot)) return refuse("slot outside the cache");
     return cache->groups[(size_t)group].first_block[(size_t)slot];
 }
 // Pages that the table of `slot` holds in `group`.
 LIA_HOST_EXPORT int lia_cache_held(void* handle, int group, int slot) {
     Cache* cache = static_cast<Cache*>(handle);
-    if (bad_slot(cache, slot)) return refuse("slot outside the cache");
+    if (cache->bad_slot(slot)) return refuse("slot outside the cache");
     int held = 0;
     for (int page : cache->groups[(size_t)group].tables[(size_t)slot]) held += page >= 0;
     return held;
@@ -323,7 +169,7 @@ LIA_HOST_EXPORT int lia_cache_check(void* handle, int group, const int* live_slo
     Plan fast, scan;
     for (int i = 0; i < n_live; ++i) {
         const int slot = live_slots[i];
-        if (bad_slot(cache, slot)) return refuse("slot outside the cache");
+        if (cache->bad_slot(slot)) return refuse("slot outside the cache");
         const std::vector<int>& table = g.tables[(size_t)slot];
         const int first = g.first_block[(size_t)slot];
         for (int b = 0; b < (int)table.size(); ++b)

@@ -34,11 +34,13 @@ takes the plain path above.
 """
 from __future__ import annotations
 
+import ctypes
 import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Optional
 
+from ..cache.pages import host_library
 from ..sampling import RequestSampler, Sampling
 from .step import StepEntry
 
@@ -65,9 +67,14 @@ class Request:
     submitted: float = 0.0
     first_token: Optional[float] = None
     finished: Optional[float] = None
+    number: int = -1                                     # the native core's name for the request
 
 
 class Scheduler:
+    """The face of the native policy (csrc/host/scheduler_host.cpp): it owns the requests' tokens, samplers and
+    times, asks the native core whom to admit, whom to preempt and what a step runs, runs the step and reports
+    what was accepted.  `queue`, `paused`, `active` and a request's `slot`, `computed` and `preemptions` mirror
+    the core's state."""
     NUCLEUS_CANDIDATES = 32                              # candidates asked of the device for a rule without top_k
 
     def __init__(self, engine, max_batch_tokens: int = 512, even_split: bool = False, eos_token_ids=(),
@@ -87,6 +94,24 @@ class Scheduler:
                       "pipelined_steps": 0, "candidate_steps": 0, "whole_row_draws": 0}
         self.pipeline = bool(pipeline) and hasattr(engine, "select_tokens_start")
         self._pending = None                             # (tokens on their way to the host, the requests they belong to)
+        self._lib = host_library()
+        self._lib.lia_sched_create.restype = ctypes.c_void_p
+        self._core = ctypes.c_void_p(self._lib.lia_sched_create(self.cache._handle, self.budget, int(bool(even_split)),
+                                                                self.cache.max_context, self.cache.page_size))
+        if not self._core:
+            raise SchedulerError(self._lib.lia_host_error().decode())
+        self._requests = []                              # by the core's request number
+        self._events = (ctypes.c_int * (3 * (2 * self.cache.max_slots + 2)))()
+        self._plan = (ctypes.c_int * (4 * self.cache.max_slots))()
+        self._retired = (ctypes.c_int * self.cache.max_slots)()
+
+    def __del__(self):
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.lia_sched_destroy(core)
+
+    def _refused(self):
+        raise SchedulerError(self._lib.lia_host_error().decode())
 
     # ---- requests ----
     def add(self, rid, prompt, sampling: Sampling = None, max_tokens: int = 8192) -> Request:
@@ -104,8 +129,20 @@ class Scheduler:
             request.error, request.done = "completion token limit must be positive", True
             self.finished.append(request)
             return request
+        request.number = self._lib.lia_sched_add(self._core, len(prompt), request.max_tokens)
+        if request.number < 0:
+            self._refused()
+        self._requests.append(request)
         self.queue.append(request)
         return request
+
+    def core_state(self, request: Request) -> dict:
+        """What the native core holds of a request (a test compares it with the face's mirror)."""
+        out = (ctypes.c_int * 6)()
+        if self._lib.lia_sched_request(self._core, request.number, out) < 0:
+            self._refused()
+        return dict(slot=None if out[0] < 0 else out[0], computed=out[1], tokens=out[2], generated=out[3],
+                    done=bool(out[4]), preemptions=out[5])
 
     def has_work(self) -> bool:
         return bool(self.queue or self.paused or any(r is not None for r in self.active))
@@ -113,105 +150,41 @@ class Scheduler:
     def live(self) -> list:
         return [r for r in self.active if r is not None]
 
-    # ---- admission ----
-    def _attach(self, request: Request) -> bool:
-        """A slot and the page of the first uncomputed token, or nothing."""
-        if self.cache.free_slots() == 0:
-            return False
-        slot = self.cache.admit()
-        if not self.cache.ensure(slot, 0, 1):
-            self.cache.release(slot)
-            return False
-        request.slot, request.computed = slot, 0
-        self.active[slot] = request
-        return True
-
-    def admit(self) -> None:
-        while self.cache.free_slots() > 0:
-            if self.paused:
-                request = self.paused[0]
-                # do not take a paused request back before its whole prefix fits again (preempt.rs:38-42)
-                needed = (len(request.tokens) + self.cache.page_size - 1) // self.cache.page_size
-                if needed > self.cache.available_pages() or not self._attach(request):
-                    return
-                self.paused.popleft()
+    # ---- admission, and what happens when pages run out ----
+    def prepare(self) -> None:
+        """Admission (first come, first served, paused requests first), then room for the step: while more live
+        requests need a new page than pages are free, one is preempted.  The core decides; what it did is taken
+        over here."""
+        n = self._lib.lia_sched_prepare(self._core, self._events, len(self._events) // 3)
+        if n < 0:
+            self._refused()
+        for i in range(n):
+            kind, number, slot = self._events[3 * i:3 * i + 3]
+            request = self._requests[number]
+            if kind == 2:                                # preempted: its pages are back, it waits to be computed again
+                self.active[slot] = None
+                request.slot, request.computed = None, 0
+                request.preemptions += 1
+                self.paused.append(request)
+                self.stats["preemptions"] += 1
                 continue
-            if not self.queue:
-                return
-            if not self._attach(self.queue[0]):
-                return
-            self.queue.popleft()
-            self.stats["admitted"] += 1
-
-    # ---- pages run out ----
-    def _needs_new_page(self, request: Request) -> bool:
-        return (not request.done) and self.cache.pages_for(request.slot, request.computed, request.computed + 1) > 0
-
-    def pause_for_capacity(self) -> None:
-        while True:
-            live = self.live()
-            needed = sum(1 for r in live if self._needs_new_page(r))
-            if needed <= self.cache.available_pages():
-                return
-            if len(live) <= 1:
-                raise SchedulerError("one request exceeded its physical KV capacity")
-            victim = max(live, key=lambda r: (bool(r.generated), self._pages_held(r), r.slot))
-            self._preempt(victim)
-
-    def _pages_held(self, request: Request) -> int:
-        return max(group.held_by(request.slot) for group in self.cache.groups) \
-            if self.cache.groups else 0
-
-    def _preempt(self, request: Request) -> None:
-        self.cache.release(request.slot)
-        self.active[request.slot] = None
-        request.slot, request.computed = None, 0
-        request.preemptions += 1
-        self.paused.append(request)
-        self.stats["preemptions"] += 1
+            waiting = self.queue if kind == 1 else self.paused
+            assert waiting[0] is request
+            waiting.popleft()
+            request.slot, request.computed = slot, 0
+            self.active[slot] = request
+            self.cache.admitted(slot)
+            if kind == 1:
+                self.stats["admitted"] += 1
 
     # ---- one step ----
-    def _portion(self, request: Request, allowance: int) -> int:
-        """How many of the request's next tokens (at most `allowance`) have pages; the portion is
-        cut at the first page that cannot be had."""
-        start = request.computed
-        want = min(allowance, len(request.tokens) - start)
-        while want > 0 and not self.cache.ensure(request.slot, start, start + want):
-            # shorten to the end of the last page that can still be had
-            ps = self.cache.page_size
-            boundary = ((start + want - 1) // ps) * ps
-            want = boundary - start if boundary > start else 0
-        return want
-
     def plan(self) -> list:
-        """[(request, count)] for this step, pages reserved."""
-        live = self.live()
-        if not live:
-            return []
-        plan, budget = [], self.budget
-        if self.even_split:
-            allowance = max(1, self.budget // len(live))
-            for request in live:
-                count = self._portion(request, allowance)
-                if count:
-                    plan.append((request, count))
-            return plan
-        decoding = [r for r in live if len(r.tokens) - r.computed == 1]
-        prefilling = [r for r in live if len(r.tokens) - r.computed > 1]
-        for request in decoding:
-            if budget <= 0:
-                break
-            if self._portion(request, 1):
-                plan.append((request, 1))
-                budget -= 1
-        for request in prefilling:
-            if budget <= 0:
-                break
-            count = self._portion(request, budget)
-            if count:
-                plan.append((request, count))
-                budget -= count
-        return plan
+        """[(request, count)] for this step, pages reserved: single decoded tokens first, then prompt portions in
+        slot order under the budget (or the even split), each portion cut at the first page that cannot be had."""
+        n = self._lib.lia_sched_plan(self._core, self._plan, len(self._plan) // 4)
+        if n < 0:
+            self._refused()
+        return [(self._requests[self._plan[4 * i]], self._plan[4 * i + 2]) for i in range(n)]
 
     def step(self) -> list:
         """Admit, make room, run one batch, sample, finish.  Returns the requests that finished (with
@@ -224,8 +197,7 @@ class Scheduler:
                 self._pending = following
                 return done
             done = self._collect()
-        self.admit()
-        self.pause_for_capacity()
+        self.prepare()
         plan = self.plan()
         live = self.live()
         if not plan:
@@ -246,7 +218,7 @@ class Scheduler:
                 self.stats["decode_tokens"] += count
         logits = self.engine.step(entries)
         for request, count in plan:
-            request.computed += count
+            self._advance(request, count)
         self.stats["steps"] += 1
         if outputs:
             if self.pipeline and all(r.sampling.on_device for r in outputs):
@@ -258,16 +230,23 @@ class Scheduler:
                 self._accept(request, int(token), now)
         return done + self._retire()
 
+    def _advance(self, request: Request, count: int) -> None:
+        if self._lib.lia_sched_advance(self._core, request.number, count) < 0:
+            self._refused()
+        request.computed += count
+
     def _retire(self) -> list:
         """Free what the finished requests hold."""
+        n = self._lib.lia_sched_retire(self._core, self._retired)
+        if n < 0:
+            self._refused()
         done = []
-        for request in self.live():
-            if request.done:
-                self.cache.release(request.slot)
-                self.active[request.slot] = None
-                request.slot = None
-                request.finished = time.perf_counter()
-                done.append(request)
+        for number in self._retired[:n]:
+            request = self._requests[number]
+            self.active[request.slot] = None
+            request.slot = None
+            request.finished = time.perf_counter()
+            done.append(request)
         self.finished.extend(done)
         return done
 
@@ -292,29 +271,22 @@ class Scheduler:
         """Whether the step after the pending one is known before its tokens are: every live request decodes
         on, whatever token it gets (short of an end of sequence)."""
         _, requests = self._pending
-        live = self.live()
-        if self.queue or self.paused or len(live) != len(requests) or len(live) > self.budget:
-            return False
-        needed = 0
-        for request, other in zip(live, requests):
-            if request is not other or request.done or len(request.tokens) != request.computed:
-                return False
-            if len(request.generated) + 1 >= request.max_tokens:        # the pending token is its last
-                return False
-            needed += self.cache.pages_for(request.slot, request.computed, request.computed + 1) > 0
-        return needed <= self.cache.available_pages()
+        numbers = (ctypes.c_int * max(1, len(requests)))(*[r.number for r in requests])
+        answer = self._lib.lia_sched_can_continue(self._core, numbers, len(requests))
+        if answer < 0:
+            self._refused()
+        return bool(answer)
 
     def _launch_fed(self):
         """The next decode step of the pending step's requests, their tokens taken on the device."""
         pending, requests = self._pending
-        entries = []
-        for request in requests:
-            if not self.cache.ensure(request.slot, request.computed, request.computed + 1):
-                raise SchedulerError("a page that was counted free could not be had")
-            entries.append(StepEntry(request.slot, [0], request.computed, [0]))
+        numbers = (ctypes.c_int * max(1, len(requests)))(*[r.number for r in requests])
+        if self._lib.lia_sched_reserve_next(self._core, numbers, len(requests)) < 0:
+            self._refused()
+        entries = [StepEntry(request.slot, [0], request.computed, [0]) for request in requests]
         logits = self.engine.step(entries, feed=pending)
         for request in requests:
-            request.computed += 1
+            self._advance(request, 1)
         self.stats["steps"] += 1
         self.stats["pipelined_steps"] += 1
         self.stats["decode_tokens"] += len(requests)
@@ -361,6 +333,8 @@ class Scheduler:
         request.generated.append(token)
         request.stopped = token in self.eos
         request.done = request.stopped or len(request.generated) >= request.max_tokens
+        if self._lib.lia_sched_accept(self._core, request.number, int(request.done)) < 0:
+            self._refused()
         if not request.done:
             request.tokens.append(token)
 

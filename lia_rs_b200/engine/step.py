@@ -146,18 +146,19 @@ class StepRuntime:
         out_rows, segments = [], []
         seen = set()
         n = 0
-        for entry in entries:
+        reserved = self.cache.reserved([entry.slot for entry in entries])
+        for entry, upto in zip(entries, reserved):
             count = len(entry.tokens)
             if count == 0:
                 raise StepError("a step entry brings no tokens")
             if entry.slot in seen:
                 raise StepError(f"request slot {entry.slot} appears twice in one step")
             seen.add(entry.slot)
-            if entry.slot not in self.cache._live:
+            if upto < 0:
                 raise StepError(f"request slot {entry.slot} is not live")
-            if entry.start < 0 or entry.start + count > self.cache.length[entry.slot]:
+            if entry.start < 0 or entry.start + count > upto:
                 raise StepError(f"slot {entry.slot}: positions [{entry.start}, {entry.start + count}) have no "
-                                f"reserved pages (reserved up to {self.cache.length[entry.slot]})")
+                                f"reserved pages (reserved up to {upto})")
             low, high = (entry.tokens[0], entry.tokens[0]) if count == 1 else (min(entry.tokens), max(entry.tokens))
             if low < 0 or high >= self.vocab_size:
                 raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "

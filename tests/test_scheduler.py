@@ -275,13 +275,45 @@ def test_a_request_ended_by_its_token_has_one_step_computed_for_nobody():
 
 def test_live_requests_without_a_row_to_run_raise_instead_of_spinning():
     """src/server/paged/schedule.rs:123-125: a step in which requests are live and none can be scheduled is an
-    error, not a loop.  The stand-in's cache is made to refuse every page after admission while claiming that
-    none is needed, which the real manager cannot do."""
+    error, not a loop.  The real cache cannot bring that about (a request that needs a page that is not there is
+    preempted or refused before the step is planned), so the request is told that all its tokens are computed
+    although none was accepted: live, not done, and nothing to run."""
     engine = StandInEngine(num_pages=8)
     s = Scheduler(engine, max_batch_tokens=8, pipeline=False)
-    s.add("a", [1, 2, 3, 4, 5, 6, 7, 8, 9], max_tokens=4)
-    s.admit()
-    engine.cache.ensure = lambda slot, start, end: False
-    engine.cache.pages_for = lambda slot, start, end: 0
+    request = s.add("a", [1, 2, 3, 4, 5, 6, 7, 8, 9], max_tokens=4)
+    s.prepare()
+    assert request.slot == 0 and s.stats["admitted"] == 1
+    assert engine.cache.ensure(request.slot, 0, 9)
+    s._advance(request, 9)
     with pytest.raises(SchedulerError, match="made no progress"):
         s.step()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+@pytest.mark.parametrize("even_split", [False, True])
+def test_random_requests_on_a_small_pool_all_finish_with_their_tokens(seed, even_split):
+    """Random prompts and limits on a pool that cannot hold them all, so requests wait, are cut, preempted and
+    computed again: every request ends with the tokens it would get alone, the cache's invariants hold after every
+    step (the stand-in checks them), nothing is held at the end, and the face's mirror of a request says what the
+    native core says."""
+    rng = np.random.default_rng(seed)
+    engine = StandInEngine(num_pages=14, page_size=4, max_slots=3, context=64)
+    s = Scheduler(engine, max_batch_tokens=int(rng.integers(3, 12)), even_split=even_split, pipeline=False)
+    wanted = {}
+    for i in range(9):
+        prompt = [int(t) for t in rng.integers(0, VOCAB, size=int(rng.integers(1, 30)))]
+        limit = int(rng.integers(1, 12))
+        wanted[i] = expected(prompt, limit)
+        s.add(i, prompt, max_tokens=limit)
+    steps = 0
+    while s.has_work():
+        s.step()
+        steps += 1
+        assert steps < 2000
+        for request in s.live() + list(s.paused) + list(s.queue):
+            state = s.core_state(request)
+            assert (state["slot"], state["computed"], state["tokens"], state["generated"], state["preemptions"]) == \
+                   (request.slot, request.computed, len(request.tokens), len(request.generated), request.preemptions)
+    assert {r.rid: r.generated for r in s.finished} == wanted
+    assert engine.cache.free_slots() == 3 and engine.cache.available_pages() == 14
+    engine.cache.check()

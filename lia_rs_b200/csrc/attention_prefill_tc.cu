@@ -217,10 +217,7 @@ attention_prefill_tc_kernel(Params p) {
             const size_t src = ((size_t)(q_offset + tok0 + (valid ? tok : 0)) * p.nq + kvh * group + head) * D + piece * 8;
             cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
         }
-        cp_async_commit();
-        cp_async_wait_all();
-        fence_async_smem();
-        mbar_arrive(smem_u32(&q_full));
+        cp_async_commit();                        // (Q is awaited below, with the first tile's copies already on their way)
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j % STAGES;
@@ -258,6 +255,11 @@ attention_prefill_tc_kernel(Params p) {
                     cp_async_16(vs + tile_offset<KT>(sub + i * ROWS_PER_PASS, piece), p.v_pages + src, valid);
                 }
                 cp_async_commit();
+            }
+            if (j == 0) {
+                asm volatile("cp.async.wait_group 2;" ::: "memory");    // Q has landed (groups complete in the order they were made)
+                fence_async_smem();
+                mbar_arrive(smem_u32(&q_full));
             }
             asm volatile("cp.async.wait_group 1;" ::: "memory");        // the keys have landed
             fence_async_smem();

@@ -18,12 +18,18 @@
 // probabilities in TMEM, so the softmax never waits for the product that reads the other): the tensor cores and
 // the exponentials overlap.  TMEM holds all of it: 2 x 128 columns of scores, 128 of output, 2 x 64 of
 // probabilities.
-// What bounds a tile: the one thread that issues the MMAs is held at the tensor pipe's pace (a 128 x 128 x 16 MMA
-// takes 64 cycles alone and 70-90 here, where tcgen05.ld and .st of the softmax share the tensor memory's ports), and
-// its waits for keys and probabilities add to that; the loaders' cp.async of a 64 KB tile take ~1,700 cycles of the
-// load/store unit; the special-function pipe needs 1,024 cycles for a tile's 16,384 ex2 (the conversion to bf16
-// pairs would run on the same pipe, 256 cycles more, so the rounding is an integer add).  Two warps per scheduler
-// hide the pipe's latency where one thread with 128 scores in registers could keep only two exponentials in flight.
+// What bounds a tile (~2,650 cycles, counted per role): the softmax warps work for ~2,100 of them (TMEM load 120,
+// the maximum and its exchange 600, the exponentials 1,270, of which the special-function pipe alone needs 1,024 for
+// a tile's 16,384 ex2; the conversion to bf16 pairs would run on the same pipe, 256 cycles more, so the rounding is
+// an integer add).  The one thread that issues the MMAs is held at the tensor pipe's pace for ~1,250 (a
+// 128 x 128 x 16 MMA takes 64 cycles alone and 70-100 here, where tcgen05.ld and .st of the softmax share the
+// tensor memory's ports) and waits for the probabilities for the rest; the loaders' cp.async of a 64 KB tile keep the
+// load/store unit busy for ~1,700.  Two warps per scheduler hide the special-function pipe's latency where one
+// thread with 128 scores in registers could keep only two exponentials in flight.
+//
+// A portion that gives fewer CTAs than the device has SMs (few tokens late in a long prompt) has its keys cut into
+// ranges of whole tiles (grid z): each range is a CTA of its own that leaves its unnormalised output, its reference
+// point and its sum in scratch memory, and attention_prefill_merge_kernel puts a row's ranges together.
 //
 // Rows are (token, head) pairs: row r is token r / g, head r % g of the CTA's tokens, so the keys of a kv
 // head are read once for all its query heads.  Head sizes 64 and 128, g a divisor of 128; the caller uses

@@ -46,6 +46,7 @@ struct Params {
     __nv_bfloat16* v_write;
     int rotary_dim, write_kv, num_pages;
     int cluster;                     // the CTAs of a token's ranges are one cluster (gridDim.z of them) and merge in shared memory
+    int all_new;                     // any of a row's keys may have been written by this step's kernels (rows of prompt portions), not only its own
     int* error_flag;
 };
 
@@ -164,7 +165,9 @@ attention_decode_kernel(Params p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     pdl_launch_dependents();
     // The step's metadata and the keys of earlier steps depend on no kernel of this step; only q and the
-    // newest key do, so everything up to pdl_wait() below overlaps the kernel ahead.
+    // newest key do, so everything up to pdl_wait() below overlaps the kernel ahead.  (Rows that are the last tokens of
+    // prompt portions, `all_new`, have keys that this step's kernels wrote anywhere before them: no tile is asked
+    // for before the wait.)
     const int t = p.rows[blockIdx.x];
     if (t < 0) return;
     const int slot = p.slots[t];
@@ -228,7 +231,7 @@ attention_decode_kernel(Params p) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {       // the first STAGES tiles are asked for at once: tile i is copy group i
         if (s < n_tiles) {
-            const bool holds_new = key_begin + (s + 1) * TILE_KEYS > pos;
+            const bool holds_new = p.all_new || key_begin + (s + 1) * TILE_KEYS > pos;
             if (holds_new && appends && !direct) {
                 deferred = s;
             } else {
@@ -795,6 +798,8 @@ LIA_EXPORT long long lia_attention_decode_scratch_floats(int n_tokens, int nq, i
 // Decode attention for the tokens listed in `rows` (indices into the step's batch), bfloat16 only,
 // head_dim 32, 64 or 128 (other sizes: LIA_ERR_SIZE; the caller falls back to the generic kernel).
 // `cluster` non-zero: `n_splits` is what lia_attention_decode_cluster_splits gave; `partial` and `counters` are not used.
+// `all_new` non-zero: the rows may be tokens of prompt portions of this step, whose earlier keys the kernels ahead
+// have written too; zero: only a row's own key is of this step (decoded tokens), and older tiles are fetched early.
 // `n_splits` ranges of `split_len` keys each must cover the longest visible span among the rows;
 // split_len 0 lets every row cut its own span into n_splits ranges (see range_length).
 LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* rows,
@@ -802,7 +807,7 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, const float* qkv, const float* inv_freq, int rotary_dim,
-                                    int write_kv, int num_pages, int cluster, int* error_flag, cudaStream_t stream) {
+                                    int write_kv, int num_pages, int cluster, int all_new, int* error_flag, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
@@ -822,6 +827,7 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
     p.k_write = (__nv_bfloat16*)const_cast<void*>(k_pages); p.v_write = (__nv_bfloat16*)const_cast<void*>(v_pages);
     p.error_flag = error_flag;
     p.cluster = cluster ? 1 : 0;
+    p.all_new = all_new ? 1 : 0;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -150,13 +150,15 @@ class Engine:
     def _replay(self, ctx) -> torch.Tensor:
         """A step through its CUDA graph.  The step's metadata (token ids, positions, slots, wanted rows,
         the portions' starts) and the block tables lie in fixed device buffers, and what the host decides about
-        a step's launches follows from the number of tokens of each entry, the number of wanted rows and the
-        context bucket; so a graph captured for these serves every later step of that shape: every decode step
-        of a batch, and every portion of a long prompt that a scheduler cuts under the same budget.  The first
+        a step's launches follows from the step's numbers of tokens, of wanted rows, of single-token entries and of
+        portions, the context bucket and what the parts add (`Part.graph_key`: the attention's number of tiles); so
+        a graph captured for these serves every later step that agrees in them, however its tokens are divided
+        among its entries: every decode step of a batch, the portions of a long prompt that a scheduler cuts under
+        one budget, and the full-budget steps of a mixed load whose portions differ in length.  The first
         step of a shape runs launch by launch (it allocates the workspace); the second is captured; a
         reallocation of any buffer makes the captured graphs stale.  The least recently used graphs go when
         there are more than MAX_GRAPHS shapes."""
-        key = (ctx.n_tokens, ctx.n_out, ctx.context_bucket, tuple(count for _, _, count, _ in ctx.segments))
+        key = self.model.graph_key(ctx)
         entry = self._graphs.pop(key, False)
         if entry is False:
             self._graphs[key] = None

@@ -51,7 +51,7 @@ class _Signatures:
     lia_wait_probe = [c_int, c_void_p, c_void_p, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_attention_decode_cluster_splits = [c_int, c_int, c_int, c_int]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
@@ -434,7 +434,7 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
-                     error_flag=None, label=None, work_bytes=0, cluster=False):
+                     error_flag=None, label=None, work_bytes=0, cluster=False, all_new=False):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
@@ -445,7 +445,9 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
     (`inv_freq`, `rotary_dim`; 0: none) and, if `write_kv`, appends each token's key and value to the cache
     itself, so no separate position-encoding kernel runs.  `cluster`: `n_splits` came from
     `attention_decode_cluster_splits`; the ranges of a token then meet in distributed shared memory and neither
-    `partial` nor `counters` is used."""
+    `partial` nor `counters` is used.  `all_new`: the rows may be tokens of this step's prompt portions, so any of
+    their keys may have been written by the kernels ahead (otherwise only a row's own key is taken to be of this step,
+    and the kernel fetches older tiles before it waits for those kernels)."""
     _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters, qkv, inv_freq, error_flag)
     if qkv is not None:
         if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
@@ -461,7 +463,8 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
                                           _p(slots), _p(block_table), block_table.shape[1], _p(out), _p(partial),
                                           0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
                                           k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
-                                          int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], 1 if cluster else 0, _p(error_flag),
+                                          int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], 1 if cluster else 0, 1 if all_new else 0,
+                                          _p(error_flag),
                                           _stream()),
                "attention_decode")
 

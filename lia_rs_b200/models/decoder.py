@@ -122,8 +122,26 @@ class DecoderModel:
             self.head = self.embedding
         else:
             self.head = prepare_weight(tensors[spec.head_name].to(device), runtime)
+        # layers of one description launch alike: one of each answers for all when a step's graph key is made
+        distinct = {}
+        for layer_spec, layer in zip(spec.layers, self.layers):
+            distinct.setdefault(repr(layer_spec), layer)
+        self._key_layers = list(distinct.values()) + [self.final_norm]
         # decode steps may be captured in CUDA graphs only if every part launches the same way each step
         self.graph_safe = all(layer.graph_safe for layer in self.layers) and bool(self.final_norm.graph_safe)
+
+    def graph_key(self, ctx) -> tuple:
+        """What a captured step is good for: the step's numbers of tokens, of wanted rows, of single-token entries
+        and of portions, its context bucket, and whatever else of its shape the parts say their launches depend on
+        (each distinct answer once)."""
+        seen, extra = set(), []
+        for layer in self._key_layers:
+            key = layer.graph_key(ctx)
+            if key and key not in seen:
+                seen.add(key)
+                extra.append(key)
+        n_single = sum(1 for _, _, count, _ in ctx.segments if count == 1)
+        return (ctx.n_tokens, ctx.n_out, ctx.context_bucket, n_single, len(ctx.segments) - n_single, tuple(extra))
 
     def forward(self, ctx) -> torch.Tensor:
         """Run the step described by `ctx`; returns 32-bit logits [ctx.n_out, vocab] (device).  When fewer rows

@@ -63,6 +63,9 @@ class GQAttention(Mixer):
         self.attention = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale,
                                         rotate_half=self.position.rotate_half())
 
+    def graph_key(self, ctx) -> tuple:
+        return self.position.graph_key(ctx) + self.attention.graph_key(ctx)
+
     def forward(self, ctx, x, residual, scale, kv=None, state=None, rows=None, n_rows=None):
         """`rows` (device int32, `n_rows` of them): only these tokens' outputs are needed.  `residual` then holds
         those rows alone ([n_rows, hidden]); keys and values of every token are still appended."""

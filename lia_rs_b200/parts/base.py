@@ -75,6 +75,14 @@ class Part:
 
     graph_safe = False
 
+    def graph_key(self, ctx) -> tuple:
+        """What else of a step's shape this part's launches depend on, beyond the step's number of tokens, of
+        wanted rows, of single-token entries and of portions, and its context bucket: two steps that agree in all
+        of these replay one captured graph.  The answer that is always right is the number of tokens of every
+        entry, which is the default; a part whose launches do not look at them answers () (a part that cuts
+        portions into tiles answers with its number of tiles)."""
+        return tuple(count for _, _, count, _ in ctx.segments)
+
     @staticmethod
     def tensor_specs(params: dict, prefix: str) -> list:
         return []
@@ -171,6 +179,11 @@ class Arrangement:
     when all its parts are."""
 
     graph_safe = False
+
+    def graph_key(self, ctx) -> tuple:
+        """As `Part.graph_key`, for the layer: what its parts answer, put together.  The default is the answer that
+        is always right."""
+        return tuple(count for _, _, count, _ in ctx.segments)
 
     @staticmethod
     def tensor_specs(layer_spec, prefix: str) -> list:

@@ -62,6 +62,10 @@ class PreNormBlock(Arrangement):
             cls(params, tensors, prefix + place, runtime) for (cls, params), place in zip(self._classes(spec), places))
         self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
+    def graph_key(self, ctx) -> tuple:
+        return (self.norm1.graph_key(ctx) + self.mixer.graph_key(ctx) + self.norm2.graph_key(ctx) +
+                self.feed_forward.graph_key(ctx))
+
     def _normed(self, ctx, norm, part, source):
         """The input of `part`: `norm(source)`, left to the part's first product where the part can take that."""
         deferred = DeferredNorm(ctx, norm, source)

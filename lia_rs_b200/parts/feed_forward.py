@@ -15,6 +15,9 @@ from .linear import ACCUM, SWIGLU, linear, prepare_weight
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     graph_safe = True
+
+    def graph_key(self, ctx) -> tuple:
+        return ()                    # rows in, rows out: only the number of tokens matters
     takes_deferred_norm = True
 
     @staticmethod

@@ -10,6 +10,9 @@ from .base import Norm, register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
+    def graph_key(self, ctx) -> tuple:
+        return ()                    # rows in, rows out: only the number of tokens matters
+
     @staticmethod
     def tensor_specs(params, prefix):
         return [TensorSpec(prefix + "weight", (params["hidden"],), kind="norm")]

@@ -104,6 +104,27 @@ class PagedAttention:
         pairs = sum(visible(start + i) for _, start, count, _ in ctx.segments if count > 1 for i in range(count))
         return keys * 2 * self.nkv * self.d * element_size, 4 * self.nq * self.d * pairs
 
+    def _prefill_kernel(self):
+        """(kernel, tokens per tile) for prompt portions, asked of the library once."""
+        if self._prefill is None:
+            per_tile = ops.attention_prefill_tc_tokens_per_tile(self.group, self.d)
+            if per_tile:
+                self._prefill = (ops.attention_prefill_tc, per_tile)
+            else:
+                self._prefill = (ops.attention_prefill, ops.attention_prefill_tokens_per_tile(self.group))
+        return self._prefill
+
+    def graph_key(self, ctx) -> tuple:
+        """What of a step's shape the launches below depend on beyond the numbers of tokens, single-token entries and
+        portions and the context bucket: into how many tiles the prompt kernel cuts the portions.  (Where the
+        portions begin and how long each is, the kernels read on the device.)"""
+        if self.variant != "tensor" or not ctx.n_prefill_segments:
+            return ()
+        per_tile = self._prefill_kernel()[1]
+        if not per_tile:
+            return ()
+        return (per_tile, sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1))
+
     # ---- the step's attention ----
     def forward(self, ctx, q, kv, out, rows=None, n_rows=None):
         """out[t] = attention of token t's encoded queries `q[t]` over the cache `kv` (keys and values of this
@@ -117,7 +138,9 @@ class PagedAttention:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, nq, nkv,
                                       d, self.window, self.scale, rows=rows[:n_rows], error_flag=ctx.error_flag)
             else:
-                self._decode(ctx, q, kv, out, rows[:n_rows], n_rows)
+                # (the wanted rows of a step with prompt portions are those portions' last tokens: the kernels ahead
+                # have written keys anywhere before them, not just their own)
+                self._decode(ctx, q, kv, out, rows[:n_rows], n_rows, all_new=ctx.n_prefill_segments > 0)
             return
         work_bytes, work_flops = self._work(ctx, q.element_size())
         if self.variant == "generic":
@@ -127,13 +150,7 @@ class PagedAttention:
         if ctx.decode_rows.numel():
             self._decode(ctx, q, kv, out, ctx.decode_rows, ctx.decode_rows.numel(), work_bytes)
         if ctx.n_prefill_segments:
-            if self._prefill is None:
-                per_tile = ops.attention_prefill_tc_tokens_per_tile(self.group, d)
-                if per_tile:
-                    self._prefill = (ops.attention_prefill_tc, per_tile)
-                else:
-                    self._prefill = (ops.attention_prefill, ops.attention_prefill_tokens_per_tile(self.group))
-            kernel, per_tile = self._prefill
+            kernel, per_tile = self._prefill_kernel()
             if per_tile:
                 tiles = sum((count + per_tile - 1) // per_tile for _, _, count, _ in ctx.segments if count > 1)
                 more = {}
@@ -149,12 +166,12 @@ class PagedAttention:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, nq, nkv,
                                       d, self.window, self.scale, rows=ctx.prefill_rows, error_flag=ctx.error_flag)
 
-    def _decode(self, ctx, q, kv, out, rows, n_rows, work_bytes=0):
+    def _decode(self, ctx, q, kv, out, rows, n_rows, work_bytes=0, all_new=False):
         n_splits, clustered = self.decode_plan(ctx, n_rows)
         partial, counters = (None, None) if clustered else self._decode_scratch(ctx, n_rows, n_splits)
         ops.attention_decode(q, kv.k_pages, kv.v_pages, rows, ctx.positions, ctx.slots, kv.block_table, out, partial,
                              self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
-                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered)
+                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered, all_new=all_new)
 
     def forward_fused(self, ctx, qkv, kv, out) -> bool:
         """For a step of single decoded tokens and a rotate-half (or no) position encoding: encoding of q and k,

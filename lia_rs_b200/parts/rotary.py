@@ -14,6 +14,9 @@ from .base import PositionEncoding, register_position_encoding
 class RotaryEncoding(PositionEncoding):
     graph_safe = True
 
+    def graph_key(self, ctx) -> tuple:
+        return ()                    # positions are read on the device
+
     @staticmethod
     def check_params(params):
         rotary_dim, theta = int(params["rotary_dim"]), float(params["theta"])
@@ -41,6 +44,9 @@ class RotaryEncoding(PositionEncoding):
 @register_position_encoding("none")
 class NoEncoding(PositionEncoding):
     graph_safe = True
+
+    def graph_key(self, ctx) -> tuple:
+        return ()                    # positions are read on the device
 
     def rotate_half(self):
         return 0, None

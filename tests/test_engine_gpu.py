@@ -163,12 +163,38 @@ def test_decoding_across_the_end_of_a_context_bucket(tmp_path, name, dtype):
         both = replay.step([("short", [short_one[2 + i]], [0]), ("long", [long_one[1010 + i]], [0])])
         rows_short.append(both[0:1])
         rows_long.append(both[1:2])
-    decode_shapes = {key[:3] for key in engine._graphs if key[3] == (1, 1)}
+    decode_shapes = {key[:3] for key in engine._graphs if key[3:5] == (2, 0)}      # two single tokens, no portion
     assert decode_shapes == {(2, 2, 1024), (2, 2, 2048)} and engine.stats["graph_replays"] >= 36
     helpers.assert_close(np.concatenate(rows_long), helpers.plain_logits(model, long_one, dtype)[1010:], dtype,
                          f"{name} across the bucket, long request")
     helpers.assert_close(np.concatenate(rows_short), helpers.plain_logits(model, short_one[:42], dtype)[2:], dtype,
                          f"{name} across the bucket, short request")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_one_captured_step_serves_other_divisions_of_its_tokens(tiny_models, name, dtype):
+    """Three steps of 128 tokens in two portions each, divided 70 + 58, 90 + 38 and 60 + 68 at different places of
+    their requests: wherever the attention cuts all three into the same number of tiles, they are one shape to the
+    engine (the first is launched, the second captured, the third replayed), and every wanted row agrees with the
+    plain implementation: where a portion begins and how long it is, the kernels read on the device."""
+    model = tiny_models[name]
+    vocab = model["config"]["vocab_size"]
+    a, b = helpers.random_tokens(vocab, 220, 21), helpers.random_tokens(vocab, 164, 22)
+    engine = make_engine(model, dtype, 512)
+    replay = helpers.Replayer(engine)
+    cuts_a, cuts_b = [0, 70, 160, 220], [0, 58, 96, 164]
+    rows = [replay.step([("a", a[cuts_a[i]:cuts_a[i + 1]], [cuts_a[i + 1] - cuts_a[i] - 1]),
+                         ("b", b[cuts_b[i]:cuts_b[i + 1]], [cuts_b[i + 1] - cuts_b[i] - 1])]) for i in range(3)]
+    got_a, got_b = np.concatenate([r[0:1] for r in rows]), np.concatenate([r[1:2] for r in rows])
+    helpers.assert_close(got_a, helpers.plain_logits(model, a, dtype)[[69, 159, 219]], dtype, f"{name} request a")
+    helpers.assert_close(got_b, helpers.plain_logits(model, b, dtype)[[57, 95, 163]], dtype, f"{name} request b")
+    if engine.cuda_graphs:
+        shapes = {key[:5] for key in engine._graphs}
+        assert shapes == {(128, 2, 1024, 0, 2)}
+        # (these lengths give the same number of tiles for every tile size the attention kernels use: 8, 10, 16, 21,
+        # 32, 64 or 128 tokens)
+        assert len(engine._graphs) == 1 and engine.stats["graph_replays"] == 2
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -20,7 +20,9 @@ printed:
              fraction of its own roofline: weight or cache bytes / time / HBM peak for the decode step,
              flops / time / bf16 peak for the prefill step
   checked    outside the timed region, the benchmarked engine runs a 64-token prompt whole and again as 48
-             tokens and 16 single tokens; both are compared with the true 32-bit path over the same weights
+             tokens and 16 single tokens; both are compared with the true 32-bit path over the same weights;
+             and the timed prompt's logits from the replayed graph are compared with those of its first step,
+             which was launched kernel by kernel (`prefill_replayed_vs_launched`)
 
 Every point is timed for at least half a second of device time: the loop of K steps is repeated and the
 median loop is reported (`repeats` says how many).  Weights (4.1 GB) and cache are far larger than the
@@ -231,6 +233,7 @@ def time_prefill(engine, warmup=3, repeats=25):
     tokens = [int(t) for t in rng.integers(0, engine.spec.vocab_size, size=PROMPT)]
     times = []
     k = -1
+    first = last = None
     while k + 1 < warmup + repeats or sum(times) < MIN_TIMED_MS:
         k += 1
         slot = engine.admit()
@@ -238,14 +241,20 @@ def time_prefill(engine, warmup=3, repeats=25):
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         begin.record()
-        engine.step([StepEntry(slot, tokens, 0, [PROMPT - 1])])
+        logits = engine.step([StepEntry(slot, tokens, 0, [PROMPT - 1])])
         end.record()
         torch.cuda.synchronize()
         engine.synchronize()
         engine.release(slot)
+        if k == 0:
+            first = logits.clone()               # launched kernel by kernel: a shape's first step
+        last = logits
         if k >= warmup:
             times.append(begin.elapsed_time(end))
-    return statistics.median(times)
+    # the same prompt through the replayed graph must give what the step launched kernel by kernel gave (kernels that
+    # start under their predecessors' tails must not read what is not written yet)
+    drift = float((last.float() - first.float()).abs().max())
+    return statistics.median(times), drift
 
 
 # The family's other sizes and the workloads they are quoted on (--workload): not the contract's line, one line each.
@@ -416,7 +425,7 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
     e2e_s, h2d, d2h = time_e2e(engine, args.batch, args.steps, args.warmup)
-    prefill_ms = time_prefill(engine)
+    prefill_ms, prefill_drift = time_prefill(engine)
     flops = prefill_flops(cfg, args.layers, PROMPT)
     points = {}
     if not args.no_points:
@@ -425,6 +434,9 @@ def main() -> int:
             points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
     kernels = kernel_shares(engine, args.batch, peak)
     checked = None if args.no_check else check_against_32_bit(engine, config, tensors, cfg)
+    if checked is not None:
+        checked["prefill_replayed_vs_launched"] = prefill_drift
+        checked["ok"] = bool(checked["ok"] and prefill_drift <= 1e-3)
     clocks = sampler.stop()
 
     line = {

@@ -199,6 +199,37 @@ def test_one_captured_step_serves_other_divisions_of_its_tokens(tiny_models, nam
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
+def test_replayed_steps_give_the_bits_of_launched_steps(tiny_models, name, dtype):
+    """The same steps through an engine that captures and replays them and through one that launches every kernel
+    itself: steps of two portions, of a single token beside a portion, and of three single tokens, each shape three
+    times at moving positions so that it is launched, captured and replayed.  Every logit must be the same to the
+    bit: a replayed graph lets a kernel start under its predecessor's tail, and a kernel that then reads what is
+    not yet written shows here (the kernels add in fixed orders, so nothing else may differ)."""
+    from lia_rs_b200.engine import Engine
+    model = tiny_models[name]
+    vocab = model["config"]["vocab_size"]
+    a, b, c = (helpers.random_tokens(vocab, n, seed) for n, seed in ((140, 31), (80, 32), (100, 33)))
+    steps = []
+    for i in range(3):                                       # two portions
+        steps.append([("a", a[40 * i:40 * i + 40], [39]), ("b", b[24 * i:24 * i + 24], [23])])
+    for i in range(3):                                       # a single token beside a portion
+        steps.append([("a", [a[120 + i]], [0]), ("c", c[31 * i:31 * i + 31], [30])])
+    for i in range(3):                                       # single tokens
+        steps.append([("c", [c[93 + i]], [0]), ("a", [a[123 + i]], [0]), ("b", [b[72 + i]], [0])])
+    outputs = []
+    for graphs in (True, False):
+        engine = Engine(model["dir"], dtype=dtype, page_size=model["page_size"], max_tokens=512, max_seqs=4,
+                        max_batch_tokens=256, cuda_graphs=graphs)
+        replay = helpers.Replayer(engine)
+        outputs.append([replay.step(step) for step in steps])
+        if graphs and engine.cuda_graphs:
+            assert engine.stats["graph_replays"] >= 3
+    for k, (replayed, launched) in enumerate(zip(*outputs)):
+        assert np.array_equal(replayed, launched), f"{name} {dtype}: step {k} differs by {np.abs(replayed - launched).max()}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
 def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
     model = tiny_models[name]
     tokens = helpers.random_tokens(model["config"]["vocab_size"], 4, 3)

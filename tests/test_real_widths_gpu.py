@@ -43,6 +43,40 @@ def test_real_widths_whole_portions_and_decode(real_models, name, dtype):
     helpers.assert_close(np.concatenate(rows_b), ref_second, dtype, f"{name} portions and decode, second request")
 
 
+@pytest.mark.parametrize("name", list(helpers.REAL_WIDTHS))
+def test_real_widths_replayed_steps_give_the_bits_of_launched_steps(real_models, name):
+    """bfloat16, the kernels the benchmark runs (tcgen05 products and prompt attention, the cluster and the
+    few-token products, decode attention in clusters): steps of two portions (100 tokens after 1,500, whose keys are
+    cut into ranges, and 200), of single tokens beside a portion, and of single tokens, each shape three times, through an engine that
+    replays captured graphs and through one that launches every kernel itself.  The logits must agree to the bit:
+    in a replayed graph a kernel starts under its predecessor's tail, and one that reads what is not yet written
+    shows here."""
+    from lia_rs_b200.engine import Engine
+    model = real_models[name]
+    vocab = model["config"]["vocab_size"]
+    a, b, c = (helpers.random_tokens(vocab, n, seed) for n, seed in ((2000, 41), (700, 42), (400, 43)))
+    steps = [[("a", a[:1000], [])], [("a", a[1000:1500], [])]]      # (then a's short portions have their keys cut into ranges)
+    for i in range(3):
+        steps.append([("a", a[1500 + 100 * i:1600 + 100 * i], [99]), ("b", b[200 * i:200 * i + 200], [199])])
+    for i in range(3):
+        steps.append([("a", [a[1800 + i]], [0]), ("b", [b[600 + i]], [0]), ("c", c[120 * i:120 * i + 120], [119])])
+    for i in range(3):
+        steps.append([("c", [c[360 + i]], [0]), ("a", [a[1803 + i]], [0]), ("b", [b[603 + i]], [0])])
+    outputs = []
+    for graphs in (True, False):
+        engine = Engine(model["dir"], dtype="bfloat16", page_size=model["page_size"], max_tokens=4096, max_seqs=4,
+                        max_batch_tokens=1024, cuda_graphs=graphs)
+        replay = helpers.Replayer(engine)
+        outputs.append([replay.step(step) for step in steps])
+        if graphs:
+            assert engine.cuda_graphs and engine.stats["graph_replays"] >= 3
+        del engine, replay
+    for k, (replayed, launched) in enumerate(zip(*outputs)):
+        if replayed is None or replayed.size == 0:
+            continue
+        assert np.array_equal(replayed, launched), f"{name}: step {k} differs by {np.abs(replayed - launched).max()}"
+
+
 @pytest.mark.parametrize("M", [1, 8, 64])
 def test_head_product_at_the_family_vocabulary(M):
     """The output product at the family's vocabulary (73,448 rows, no multiple of any tile) against 64-bit."""

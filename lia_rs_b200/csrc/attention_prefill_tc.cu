@@ -383,14 +383,15 @@ attention_prefill_tc_kernel(Params p) {
                 raw[c >> 1] = __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632);
             }
             row_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-            // This tile's buffer of probabilities (one of two) is free once the second product of two tiles ago is done;
-            // O may be rescaled only when the second product of the tile before is done.  (p_free[b] completes once
-            // per tile of parity b; the wait for the buffer keeps every later wait's parity unambiguous.)
-            if (j >= 2 && !mbar_wait(smem_u32(&p_free[j & 1]), (uint32_t)((j >> 1) - 1) & 1u)) { ok = false; break; }
+            // This tile's buffer of probabilities (one of two) is free once the second product of two tiles ago is done:
+            // it is, since this tile's scores are there: the commit that announced them stands for every MMA the
+            // issuing thread had issued before, and the second product of two tiles ago is one of them.  O may be
+            // rescaled only when the second product of the tile before is done, which is awaited where it happens
+            // (that barrier has then completed all its earlier phases and at most this one: the parity tells).
             const bool rescale = __any_sync(0xffffffffu, correction != 1.f) && j > 0;
-            if (rescale && !mbar_wait(smem_u32(&p_free[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u)) { ok = false; break; }
-            tc_fence_after();
             if (rescale) {
+                if (!mbar_wait(smem_u32(&p_free[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll 1
                 for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
                     float o[16];

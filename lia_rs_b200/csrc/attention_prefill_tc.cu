@@ -7,7 +7,7 @@
 //                   one TMEM lane, which the warps w and w + 4 can both read); the two meet through shared memory
 //                   for the row's maximum (a whole number of base-2 logarithms, so rescaling is exact and rare);
 //                   each makes the exponentials of its 64 keys and keeps their sum, in 32-bit; probabilities back
-//                   to TMEM as bf16 pairs (tcgen05.st), rounded on the integer pipe
+//                   to TMEM as bf16 pairs (tcgen05.st)
 //     O += P V      tcgen05.mma with P as the operand from TMEM, M 128, N head_dim, K 128 keys, V taken as it lies
 //                   in its pages ([key][dim], an MN-major operand), accumulator in TMEM for the whole walk
 // Roles: warps 0..7 softmax, warp 8 allocates TMEM and one of its lanes issues the MMAs, warps
@@ -20,8 +20,9 @@
 // probabilities.
 // What bounds a tile (~2,650 cycles, counted per role): the softmax warps work for ~2,100 of them (TMEM load 120,
 // the maximum and its exchange 600, the exponentials 1,270, of which the special-function pipe alone needs 1,024 for
-// a tile's 16,384 ex2; the conversion to bf16 pairs would run on the same pipe, 256 cycles more, so the rounding is
-// an integer add).  The one thread that issues the MMAs is held at the tensor pipe's pace for ~1,250 (a
+// a tile's 16,384 ex2).  It is the number of instructions the softmax warps issue that counts: arguments and sums
+// two at a time (fma.f32x2, add.f32x2) and the conversion instruction for a bf16 pair took a tile from 2,650 to
+// 2,500 cycles, while exponentials by polynomial on the FMA pipes (ten instructions for one) made it slower.  The one thread that issues the MMAs is held at the tensor pipe's pace for ~1,250 (a
 // 128 x 128 x 16 MMA takes 64 cycles alone and 70-100 here, where tcgen05.ld and .st of the softmax share the
 // tensor memory's ports) and waits for the probabilities for the rest; the loaders' cp.async of a 64 KB tile keep the
 // load/store unit busy for ~1,700.  Two warps per scheduler hide the special-function pipe's latency where one
@@ -72,6 +73,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two 32-bit floats in one 64-bit register, and the instructions that work on both at once.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 __device__ __forceinline__ float exp2_whole(float n) {       // 2^n for a whole number n <= 0 (or -infinity), exactly
     return n < -126.f ? 0.f : __int_as_float(((int)n + 127) << 23);
@@ -372,17 +392,28 @@ attention_prefill_tc_kernel(Params p) {
             row_max = new_max;
             row_sum *= correction;
             // probabilities, as bf16 pairs (the scores' registers are reused)
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};                     // four chains again, met in a fixed order
+            // (two scores at a time where the instruction set has it: one fused multiply-add for a pair's arguments,
+            // one addition for a pair's contributions to the sums; the softmax warps are bound by how many
+            // instructions they issue, not by the pipes)
+            uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};             // four chains of pairs again, met in a fixed order
+            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), shift2 = pack_f32x2(-safe_max, -safe_max);
 #pragma unroll
             for (int c = 0; c < HALF; c += 2) {
-                const float e0 = ex2_approx(fmaf(__uint_as_float(raw[c]), p.scale_log2, -safe_max));
-                const float e1 = ex2_approx(fmaf(__uint_as_float(raw[c + 1]), p.scale_log2, -safe_max));
-                sums[(c >> 1) & 3] += e0 + e1;
-                // to bf16 with an integer add (round half up: the values are finite and not negative) and a byte
-                // permute that keeps the two upper halves: the conversion instruction would share ex2's pipe
-                raw[c >> 1] = __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632);
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1])), scale2, shift2), x0, x1);
+                const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                sums[(c >> 1) & 3] = add_f32x2(sums[(c >> 1) & 3], pack_f32x2(e0, e1));
+                // to a bf16 pair with the conversion instruction: it shares the exponentials' pipe (4 cycles a warp
+                // beside their 2 x 8), which has room, and is one instruction where rounding with integer adds and a
+                // byte permute is three (measured: 340 -> 331 us at 8,192 tokens)
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
+                raw[c >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
             }
-            row_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            {
+                float lo, hi;
+                unpack_f32x2(add_f32x2(add_f32x2(sums[0], sums[1]), add_f32x2(sums[2], sums[3])), lo, hi);
+                row_sum += lo + hi;
+            }
             // This tile's buffer of probabilities (one of two) is free once the second product of two tiles ago is done:
             // it is, since this tile's scores are there: the commit that announced them stands for every MMA the
             // issuing thread had issued before, and the second product of two tiles ago is one of them.  O may be

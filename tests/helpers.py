@@ -254,3 +254,80 @@ class Replayer:
             self.engine.release(self.live.pop(name)[0])
         self.engine.cache.check()
         return logits
+
+
+def random_trace(rng, vocab, max_positions, longest_portion, long_first):
+    """A random trace for up to four requests: steps of one to four entries, each a portion of 2..longest_portion
+    tokens or, for a request that has begun, a single token half of the time; `long_first` > 0 opens with one long
+    portion of the first request, so that later short portions see a long context.  Returns (steps, tokens): steps
+    of (request, count, wanted places), tokens by request."""
+    ids = ["a", "b", "c", "d"]
+    fed = {i: 0 for i in ids}
+    steps = []
+    if long_first:
+        steps.append([("a", long_first, [])])
+        fed["a"] = long_first
+    for _ in range(rng.randint(4, 9)):
+        entries = []
+        for i in rng.sample(ids, rng.randint(1, 4)):
+            count = 1 if (fed[i] > 0 and rng.random() < 0.5) else rng.randint(2, longest_portion)
+            if fed[i] + count > max_positions - 2:
+                continue
+            want = sorted(rng.sample(range(count), min(count, rng.choice([0, 1, 1, 2])))) if count > 1 else [0]
+            if count > 1 and rng.random() < 0.7 and (count - 1) not in want:
+                want.append(count - 1)
+            entries.append((i, count, want))
+            fed[i] += count
+        if entries:
+            steps.append(entries)
+    tokens = {i: random_tokens(vocab, max(fed[i], 1), rng.randint(0, 1 << 30)) for i in ids}
+    return steps, tokens
+
+
+def run_trace(engine, steps, tokens):
+    """The trace through the engine, every request ended after the last step; the logits of every step."""
+    replay = Replayer(engine)
+    at = {}
+    outputs = []
+    for step in steps:
+        batch = []
+        for request, count, want in step:
+            start = at.get(request, 0)
+            batch.append((request, tokens[request][start:start + count], want))
+            at[request] = start + count
+        outputs.append(replay.step(batch))
+    replay.step([], end=list(replay.live))
+    return outputs
+
+
+def assert_random_traces_replay_to_the_bit(model, seeds, longest_portion, long_first_range):
+    """Random traces, each three times through an engine with graphs (launched, captured, replayed: a pass ends
+    every request, so the next one has the same shapes at the same positions, on other pages) and once through an
+    engine that launches every kernel: all four must agree to the bit."""
+    import random
+
+    from lia_rs_b200.engine import Engine
+    vocab = model["config"]["vocab_size"]
+    for seed in seeds:
+        rng = random.Random(seed)
+        low, high = long_first_range
+        long_first = rng.choice([0, rng.randint(low, high)])
+        steps, tokens = random_trace(rng, vocab, model["config"]["max_position_embeddings"], longest_portion, long_first)
+        pool = sum((len(t) + 63) // 64 * 64 for t in tokens.values()) + 64
+        widest = max(sum(count for _, count, _ in step) for step in steps)
+        outputs = []
+        for graphs in (True, False):
+            engine = Engine(model["dir"], dtype="bfloat16", page_size=model["page_size"], max_tokens=pool, max_seqs=4,
+                            max_batch_tokens=widest, cuda_graphs=graphs)
+            for _ in range(3 if graphs else 1):
+                outputs.append(run_trace(engine, steps, tokens))
+            if graphs and engine.cuda_graphs:
+                assert engine.stats["graph_replays"] >= len(steps)
+            del engine
+        launched = outputs[-1]
+        for p, replayed in enumerate(outputs[:-1]):
+            for k, (x, y) in enumerate(zip(replayed, launched)):
+                if x is None or x.size == 0:
+                    continue
+                assert np.array_equal(x, y), (f"{model['name']} seed {seed}, pass {p}, step {k} "
+                                              f"{[(r, c) for r, c, _ in steps[k]]}: differs by {np.abs(x - y).max()}")

@@ -228,6 +228,15 @@ def test_replayed_steps_give_the_bits_of_launched_steps(tiny_models, name, dtype
         assert np.array_equal(replayed, launched), f"{name} {dtype}: step {k} differs by {np.abs(replayed - launched).max()}"
 
 
+@pytest.mark.parametrize("name", MODELS)
+def test_random_traces_replay_to_the_bit(tiny_models, name):
+    """Random traces (portions of 2..40 tokens beside single tokens, up to four requests) launched, captured,
+    replayed and launched without graphs: the same bits."""
+    limit = tiny_models[name]["config"]["max_position_embeddings"]
+    helpers.assert_random_traces_replay_to_the_bit(tiny_models[name], seeds=(11, 12, 13), longest_portion=40,
+                                                   long_first_range=(50, min(150, limit // 2)))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
 def test_first_tokens_of_a_sequence(tiny_models, name, dtype):

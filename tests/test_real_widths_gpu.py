@@ -77,6 +77,14 @@ def test_real_widths_replayed_steps_give_the_bits_of_launched_steps(real_models,
         assert np.array_equal(replayed, launched), f"{name}: step {k} differs by {np.abs(replayed - launched).max()}"
 
 
+@pytest.mark.parametrize("name", list(helpers.REAL_WIDTHS))
+def test_real_widths_random_traces_replay_to_the_bit(real_models, name):
+    """Random traces (portions of 2..300 tokens beside single tokens, up to four requests, sometimes after a
+    prompt of 600..3,000 tokens) launched, captured, replayed and launched without graphs: the same bits."""
+    helpers.assert_random_traces_replay_to_the_bit(real_models[name], seeds=(1, 2, 3), longest_portion=300,
+                                                   long_first_range=(600, 3000))
+
+
 @pytest.mark.parametrize("M", [1, 8, 64])
 def test_head_product_at_the_family_vocabulary(M):
     """The output product at the family's vocabulary (73,448 rows, no multiple of any tile) against 64-bit."""

@@ -764,6 +764,23 @@ int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
     return rc;
 }
 
+// CTAs of the kernel that one SM holds at once (asked of the driver once; 0: unknown).
+template <int D, int NH>
+int ctas_per_sm() {
+    static int cached = 0;
+    if (cached == 0) {
+        cached = -1;
+        int blocks = 0;
+        if (configure_decode<D, NH>() == LIA_OK &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, NH>, WARPS * 32, decode_smem_bytes<D>()) == cudaSuccess &&
+            blocks > 0)
+            cached = blocks;
+        else
+            cudaGetLastError();
+    }
+    return cached > 0 ? cached : 0;
+}
+
 template <int D>
 int cluster_splits_for(bool wide, int clusters, int wanted) {
     for (int size = MAX_CLUSTER; size >= 2; size /= 2) {
@@ -785,6 +802,16 @@ LIA_EXPORT int lia_attention_decode_cluster_splits(int d, int heads_per_kv_head,
     if (d == 64) return cluster_splits_for<64>(wide, clusters, wanted);
     if (d == 32) return cluster_splits_for<32>(wide, clusters, wanted);
     return 1;
+}
+
+// CTAs of the kernel that an SM holds at once for this head size (registers and shared memory decide: 2 at head
+// size 128, more below); 0: the kernel does not take the head size, or the driver did not say.
+LIA_EXPORT int lia_attention_decode_ctas_per_sm(int d, int heads_per_kv_head) {
+    const bool wide = heads_per_kv_head > 8;
+    if (d == 128) return wide ? ctas_per_sm<128, 2>() : ctas_per_sm<128, 1>();
+    if (d == 64) return wide ? ctas_per_sm<64, 2>() : ctas_per_sm<64, 1>();
+    if (d == 32) return wide ? ctas_per_sm<32, 2>() : ctas_per_sm<32, 1>();
+    return 0;
 }
 
 // Floats of scratch that n_rows tokens with n_splits ranges need.

@@ -53,6 +53,7 @@ class _Signatures:
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_attention_decode_cluster_splits = [c_int, c_int, c_int, c_int]
+    lia_attention_decode_ctas_per_sm = [c_int, c_int]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                    c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p]
     lia_gemm_cluster = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -473,6 +474,11 @@ def attention_decode_cluster_splits(d: int, group: int, clusters: int, wanted: i
     """Ranges per token (2, 4, 8 or 16, at most `wanted`) with which `attention_decode(..., cluster=True)` can
     serve `clusters` (token, head group) pairs at once; 1: it cannot (one range, or too many clusters for the device)."""
     return int(lib().lia_attention_decode_cluster_splits(d, group, clusters, wanted))
+
+
+def attention_decode_ctas_per_sm(d: int, group: int) -> int:
+    """CTAs of `attention_decode` that one SM holds at once for this head size (0: unknown)."""
+    return int(lib().lia_attention_decode_ctas_per_sm(d, group))
 
 
 def attention_prefill_tokens_per_tile(group: int) -> int:

@@ -53,17 +53,21 @@ class PagedAttention:
         self.rotate_half = rotate_half if (self.variant == "tensor" and self.group <= 16) else None
         self._prefill = None          # (kernel, tokens per tile), asked of the library at the first prompt portion
         self._decode_plans = {}       # (rows, wanted ranges) -> (ranges, as clusters)
+        self._ctas_per_sm = None      # CTAs of the decode kernel that an SM holds, asked of the library at the first decode step
 
     # ---- how a decode row's keys are cut ----
     def decode_splits(self, ctx, rows: int) -> int:
-        """Into how many ranges the decode kernel cuts each token's keys: as many as fill the two CTAs that an
-        SM holds, in one round; no more than 32 (the last CTA of a token reads them all) and none shorter than
-        256 keys at the step's longest context.  It depends on the number of rows and on the context bucket
-        alone (each token then cuts its own span, on the device), so a captured step serves every step of its
-        shape and bucket."""
+        """Into how many ranges the decode kernel cuts each token's keys: as many as fill the CTAs that the SMs
+        hold at once (two an SM at head size 128, four at 64: 64 tokens of 16/2 heads of 64 over ~2,250 keys take
+        25.6 us in two ranges, 16.3 in four), in one round; no more than 32 (the last CTA of a token reads them
+        all) and none shorter than 256 keys at the step's longest context.  It depends on the number of rows and
+        on the context bucket alone (each token then cuts its own span, on the device), so a captured step serves
+        every step of its shape and bucket."""
         groups = self.nkv * ((self.group + 15) // 16)
         ctas = max(1, rows * groups)
-        wanted = (2 * ctx.runtime.sm_count) // ctas
+        if self._ctas_per_sm is None:
+            self._ctas_per_sm = ops.attention_decode_ctas_per_sm(self.d, self.group) or 2
+        wanted = (self._ctas_per_sm * ctx.runtime.sm_count) // ctas
         return max(1, min(wanted, 32, ctx.context_bucket // 256))
 
     def decode_plan(self, ctx, rows: int):

@@ -136,8 +136,8 @@ class Engine:
                 logits = self._launch(ctx)
             self.runtime_step.finish()
         self.stats["steps"] += 1
-        self.stats["tokens"] += ctx.n_tokens
-        return logits
+        self.stats["tokens"] += ctx.n_tokens - ctx.padding
+        return logits[:ctx.n_out - ctx.padding] if ctx.padding else logits
 
     def _launch(self, ctx) -> torch.Tensor:
         before = ops.kernel_launches()

@@ -41,10 +41,16 @@ class StepEntry:
 class StepContext:
     """Everything the parts may ask for during one step."""
 
-    def __init__(self, runtime, n_tokens, n_out, segments, meta):
+    def __init__(self, runtime, n_tokens, n_out, segments, meta, padding=0):
         self.runtime = runtime
+        # rows of the batch and of the logits, padding rows included: what the kernels run
         self.n_tokens, self.n_out = n_tokens, n_out
+        # `padding` rows at the end of a step of single tokens bring it to a round number of rows (fewer shapes to
+        # capture); they have slot -1 on the device, which every kernel that touches the cache skips, and are not
+        # among the segments
+        self.padding = padding
         self.segments = segments                      # [(slot, start, count, offset in the batch)]
+        self.n_single = sum(1 for _, _, count, _ in segments if count == 1) + padding
         (self.tokens, self.positions, self.slots, self.out_rows, self.decode_rows, self.prefill_rows,
          self.prefill_segments) = meta
         self.n_prefill_segments = sum(1 for _, _, count, _ in segments if count > 1)
@@ -169,9 +175,14 @@ class StepRuntime:
                 out_rows.append(n + w)
             segments.append((entry.slot, entry.start, count, n))
             n += count
-        n_out = len(out_rows)
         if n > self.max_batch_tokens:
             raise StepError(f"{n} tokens in one step exceed max_batch_tokens={self.max_batch_tokens}")
+        real = n
+        padding = self.padding_for(n, len(segments))
+        for _ in range(padding):                             # rows of nobody: token 0 at position 0 of slot -1, logits wanted (and dropped)
+            out_rows.append(n)
+            n += 1
+        n_out = len(out_rows)
         self._copy_event.synchronize()               # the staging buffer of the last step is free again
         self.raise_device_errors()
         # the metadata is written straight into the pinned staging buffer, a slice per entry:
@@ -179,6 +190,8 @@ class StepRuntime:
         host = self._meta_host
         view = self._meta_view
         token_part, position_part, slot_part = view[0:n], view[n:2 * n], view[2 * n:3 * n]
+        if padding:
+            token_part[real:], position_part[real:], slot_part[real:] = 0, 0, -1
         for entry, (slot, start, count, offset) in zip(entries, segments):
             if count == 1:
                 token_part[offset], position_part[offset], slot_part[offset] = entry.tokens[0], start, slot
@@ -186,7 +199,7 @@ class StepRuntime:
                 token_part[offset:offset + count] = entry.tokens
                 position_part[offset:offset + count] = np.arange(start, start + count, dtype=np.int32)
                 slot_part[offset:offset + count] = slot
-        decode_rows = [offset for _, _, count, offset in segments if count == 1]
+        decode_rows = [offset for _, _, count, offset in segments if count == 1] + list(range(real, n))
         at = 3 * n
         view[at:at + n_out] = out_rows
         at += n_out
@@ -201,9 +214,9 @@ class StepRuntime:
         total = 4 * n + n_out + len(prefill_segments)
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
         if feed is not None:
-            if any(count != 1 for _, _, count, _ in segments) or feed.numel() < n or feed.dtype != torch.int32:
+            if any(count != 1 for _, _, count, _ in segments) or feed.numel() < real or feed.dtype != torch.int32:
                 raise StepError("tokens can be fed on the device only to a step of single tokens, one per entry")
-            self._meta_device[:n].copy_(feed[:n], non_blocking=True)
+            self._meta_device[:real].copy_(feed[:real], non_blocking=True)
         self.cache.flush()
         self._copy_event.record()
         dev = self._meta_device
@@ -211,7 +224,19 @@ class StepRuntime:
         meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:at], dev[at:at + len(decode_rows)],
                 dev[at + len(decode_rows):at + n], dev[at + n:total])
         self.h2d_bytes = total * 4
-        return StepContext(self, n, n_out, segments, meta)
+        return StepContext(self, n, n_out, segments, meta, padding)
+
+    PAD_ABOVE, PAD_TO = 8, 8
+
+    def padding_for(self, n_tokens: int, n_entries: int) -> int:
+        """Rows of nobody behind a step of single tokens: beyond PAD_ABOVE entries the batch is brought to a
+        multiple of PAD_TO rows (while the step's buffers have room), so that the steps of a batch whose requests
+        end one after another are a few shapes, each captured once and replayed, instead of one shape per size
+        (two launched steps each before a replay).  Smaller batches run as they are."""
+        if n_entries != n_tokens or n_tokens <= self.PAD_ABOVE:
+            return 0
+        padded = (n_tokens + self.PAD_TO - 1) // self.PAD_TO * self.PAD_TO
+        return padded - n_tokens if padded <= self.max_batch_tokens else 0
 
     def finish(self):
         self._error_host.copy_(self.error_flag, non_blocking=True)

@@ -140,8 +140,7 @@ class DecoderModel:
             if key and key not in seen:
                 seen.add(key)
                 extra.append(key)
-        n_single = sum(1 for _, _, count, _ in ctx.segments if count == 1)
-        return (ctx.n_tokens, ctx.n_out, ctx.context_bucket, n_single, len(ctx.segments) - n_single, tuple(extra))
+        return (ctx.n_tokens, ctx.n_out, ctx.context_bucket, ctx.n_single, ctx.n_prefill_segments, tuple(extra))
 
     def forward(self, ctx) -> torch.Tensor:
         """Run the step described by `ctx`; returns 32-bit logits [ctx.n_out, vocab] (device).  When fewer rows

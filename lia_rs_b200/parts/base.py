@@ -71,7 +71,12 @@ class Part:
     starts, slots, pages) it reads on the device, from `ctx.tokens`, `ctx.positions`, `ctx.slots`,
     `ctx.prefill_segments` and the block tables, never on the host.  Only when every part of a model says
     so are its steps captured in CUDA graphs and replayed; a part that looks at the starts in
-    `ctx.segments` in Python, or allocates, leaves this False and the model runs launch by launch."""
+    `ctx.segments` in Python, or allocates, leaves this False and the model runs launch by launch.
+
+    Rows of nobody: a step of many single tokens may bring `ctx.padding` extra rows at its end (token 0, position 0,
+    slot -1 in `ctx.slots`), counted in `ctx.n_tokens`, `ctx.n_out` and `ctx.decode_rows` but not listed in
+    `ctx.segments`.  A part's kernels run them like any row, except that nothing is read from or written to a
+    cache or a state for a negative slot; what they compute is dropped."""
 
     graph_safe = False
 

@@ -228,6 +228,38 @@ def test_replayed_steps_give_the_bits_of_launched_steps(tiny_models, name, dtype
         assert np.array_equal(replayed, launched), f"{name} {dtype}: step {k} differs by {np.abs(replayed - launched).max()}"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny-B", "tiny-C", "tiny-E"])
+def test_steps_of_single_tokens_padded_to_a_round_number_of_rows(tiny_models, name, dtype):
+    """Eleven requests decode side by side, then nine of them, then all eleven fed on the device: beyond eight
+    entries a step of single tokens runs with rows of nobody up to a multiple of eight (11 and 9 share one shape),
+    and the logits of the real rows are those of the plain implementation."""
+    from lia_rs_b200.engine import StepEntry
+    model = tiny_models[name]
+    vocab = model["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, 9 + 3 * i, 70 + i) for i in range(11)]
+    engine = make_engine(model, dtype, 1024, max_seqs=12)
+    assert engine.runtime_step.padding_for(11, 11) == 5 and engine.runtime_step.padding_for(8, 8) == 0
+    assert engine.runtime_step.padding_for(11, 10) == 0          # a portion among the entries: no padding
+    replay = helpers.Replayer(engine)
+    names = [f"r{i}" for i in range(11)]
+    replay.step([(n, p[:-4], []) for n, p in zip(names, prompts)])
+    at = {n: len(p) - 4 for n, p in zip(names, prompts)}      # r9 and r10 sit out the second step
+    for live in (names, names[:9], names):
+        batch = [(n, [prompts[names.index(n)][at[n]]], [0]) for n in live]
+        logits = replay.step(batch)
+        assert logits.shape[0] == len(live)
+        for row, n in enumerate(live):
+            reference = helpers.plain_logits(model, prompts[names.index(n)], dtype)[at[n]:at[n] + 1]
+            helpers.assert_close(logits[row:row + 1], reference, dtype, f"{name} padded step, {len(live)} requests, {n}")
+            at[n] += 1
+    stats = engine.stats
+    assert stats["tokens"] == sum(len(p) - 4 for p in prompts) + 11 + 9 + 11
+    if engine.cuda_graphs:
+        assert any(key[0] == 16 and key[3] == 16 for key in engine._graphs), "11 and 9 single tokens run as 16 rows"
+        assert not any(key[0] in (9, 11) for key in engine._graphs)
+
+
 @pytest.mark.parametrize("name", MODELS)
 def test_random_traces_replay_to_the_bit(tiny_models, name):
     """Random traces (portions of 2..40 tokens beside single tokens, up to four requests) launched, captured,

@@ -317,3 +317,18 @@ def test_random_requests_on_a_small_pool_all_finish_with_their_tokens(seed, even
     assert {r.rid: r.generated for r in s.finished} == wanted
     assert engine.cache.free_slots() == 3 and engine.cache.available_pages() == 14
     engine.cache.check()
+
+
+def test_padding_of_single_token_steps_is_a_function_of_the_counts_alone():
+    """Up to eight single tokens run as they are; beyond, a step is brought to a multiple of eight rows while the
+    step's buffers have room; a step with a portion among its entries is never padded."""
+    from types import SimpleNamespace
+
+    from lia_rs_b200.engine.step import StepRuntime
+    runtime = SimpleNamespace(max_batch_tokens=64, PAD_ABOVE=StepRuntime.PAD_ABOVE, PAD_TO=StepRuntime.PAD_TO)
+    padding = lambda tokens, entries: StepRuntime.padding_for(runtime, tokens, entries)
+    assert [padding(n, n) for n in range(1, 9)] == [0] * 8
+    assert [padding(n, n) for n in (9, 11, 16, 17, 57, 63, 64)] == [7, 5, 0, 7, 7, 1, 0]
+    assert padding(12, 11) == 0 and padding(40, 2) == 0
+    runtime.max_batch_tokens = 20
+    assert padding(17, 17) == 0 and padding(15, 15) == 1          # 24 rows would not fit the buffers

@@ -282,7 +282,39 @@ def fill_in_portions(engine, batch, prompt_tokens, portion, rng_seed):
     return slots
 
 
-def other_workload(name, steps, warmup) -> int:
+def device_trace(run) -> dict:
+    """`run()` under a trace of the device's activity (CUPTI through torch's profiler): how long the device was
+    busy, and each kernel's share.  Kernels chained with programmatic launch overlap (a successor waits on the device
+    for its predecessor), so at every moment the time goes to the kernel that began first among those running; the
+    sum of the kernels' own durations would count the waiting twice."""
+    import heapq
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+    spans = sorted((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                   if e.device_type == torch.autograd.DeviceType.CUDA)
+    if not spans:
+        return {"unavailable": "the profiler recorded no device activity"}
+    points = sorted({t for begin, end, _ in spans for t in (begin, end)})
+    busy, share, running, k = 0.0, {}, [], 0
+    for t0, t1 in zip(points, points[1:]):
+        while k < len(spans) and spans[k][0] <= t0:
+            heapq.heappush(running, spans[k])
+            k += 1
+        while running and running[0][1] <= t0:
+            heapq.heappop(running)
+        if running:
+            busy += t1 - t0
+            name = running[0][2].replace("void ", "").replace("(anonymous namespace)::", "").split("(")[0]
+            share[name] = share.get(name, 0.0) + (t1 - t0)
+    span = spans[-1][1] - spans[0][0]
+    top = sorted(share.items(), key=lambda item: -item[1])[:12]
+    return {"span_s": round(span / 1e6, 3), "busy_s": round(busy / 1e6, 3),
+            "kernels_ms": {name: round(t / 1e3, 1) for name, t in top}}
+
+
+def other_workload(name, steps, warmup, trace=False) -> int:
     import numpy as np
     import torch
     from lia_rs_b200 import LlamaConfig
@@ -341,11 +373,14 @@ def other_workload(name, steps, warmup) -> int:
         engine = Engine.random(LlamaConfig.from_dict(cfg), seed=4, dtype="bfloat16", page_size=PAGE, max_tokens=pool,
                                max_seqs=requests, max_batch_tokens=PROMPT, max_context=cfg["max_position_embeddings"])
         result = {}
-        for repeat in range(2):                      # the first pass compiles nothing but allocates and captures
+        for repeat in range(3 if trace else 2):      # the first pass compiles nothing but allocates and captures
             scheduler = Scheduler(engine, max_batch_tokens=PROMPT)
             for i, prompt in enumerate(prompts):
                 scheduler.add(i, prompt, max_tokens=decode_tokens)
             torch.cuda.synchronize()
+            if trace and repeat == 2:                # a third pass under the trace; the line's figures are the second's
+                result["device_trace"] = device_trace(lambda: (scheduler.run(), torch.cuda.synchronize()))
+                break
             started = time.perf_counter()
             scheduler.run()
             torch.cuda.synchronize()
@@ -375,6 +410,9 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
     parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
+    parser.add_argument("--device-trace", action="store_true",
+                        help="with --workload 0.5b-mixed: one more pass under a trace of the device's kernels; adds "
+                             "the device's busy time and each kernel's share of it to the line")
     parser.add_argument("--no-check", action="store_true", help="skip the comparison with the 32-bit path")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode steps kernel by kernel instead of replaying CUDA graphs (for profilers)")
@@ -390,7 +428,7 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     if args.workload:
-        return other_workload(args.workload, args.steps, args.warmup)
+        return other_workload(args.workload, args.steps, args.warmup, trace=args.device_trace)
 
     import torch
     from lia_rs_b200 import LlamaConfig

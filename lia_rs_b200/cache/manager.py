@@ -210,6 +210,10 @@ class CacheManager:
         if handle:
             self._lib.lia_cache_destroy(handle)
 
+    def native_handle(self):
+        """The native cache, for the host library's other entry points (the scheduler's policy, the step's staging)."""
+        return self._handle
+
     # ---- slots (kept by the native cache: the scheduler's native policy works on the same state) ----
     def free_slots(self) -> int:
         return int(self._lib.lia_cache_free_slots(self._handle))

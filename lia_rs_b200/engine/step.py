@@ -18,9 +18,12 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Sequence
 
+import ctypes
+
 import numpy as np
 import torch
 
+from ..cache.pages import host_library
 from ..kernels import ops
 
 
@@ -102,6 +105,8 @@ class StepRuntime:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._copy_event = torch.cuda.Event()
+        self._host = host_library()
+        self._summary = (ctypes.c_int * 8)()
         self._buffers = {}
         self._attentions = {}
         self._logits_buffer = None
@@ -149,69 +154,42 @@ class StepRuntime:
         """Check the batch, stage its metadata and the changed block-table rows on the device,
         and return the context for the model.  `feed` (int32, on the device): the token of entry i is
         feed[i] (every entry then brings one token, whose id in the entry only stands in)."""
-        out_rows, segments = [], []
-        seen = set()
-        n = 0
-        reserved = self.cache.reserved([entry.slot for entry in entries])
-        for entry, upto in zip(entries, reserved):
-            count = len(entry.tokens)
-            if count == 0:
-                raise StepError("a step entry brings no tokens")
-            if entry.slot in seen:
-                raise StepError(f"request slot {entry.slot} appears twice in one step")
-            seen.add(entry.slot)
-            if upto < 0:
-                raise StepError(f"request slot {entry.slot} is not live")
-            if entry.start < 0 or entry.start + count > upto:
-                raise StepError(f"slot {entry.slot}: positions [{entry.start}, {entry.start + count}) have no "
-                                f"reserved pages (reserved up to {upto})")
-            low, high = (entry.tokens[0], entry.tokens[0]) if count == 1 else (min(entry.tokens), max(entry.tokens))
-            if low < 0 or high >= self.vocab_size:
-                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of "
-                                f"{self.vocab_size}")
-            for w in entry.want:
-                if not 0 <= w < count:
-                    raise StepError(f"wanted index {w} is outside the entry's {count} tokens")
-                out_rows.append(n + w)
-            segments.append((entry.slot, entry.start, count, n))
-            n += count
-        if n > self.max_batch_tokens:
-            raise StepError(f"{n} tokens in one step exceed max_batch_tokens={self.max_batch_tokens}")
-        real = n
-        padding = self.padding_for(n, len(segments))
-        for _ in range(padding):                             # rows of nobody: token 0 at position 0 of slot -1, logits wanted (and dropped)
-            out_rows.append(n)
-            n += 1
-        n_out = len(out_rows)
+        # the entries, flattened for the native side: it checks the batch (no request twice, positions covered by
+        # reserved pages, token ids inside the vocabulary, wanted places among an entry's tokens) and writes the
+        # metadata straight into the pinned staging buffer (csrc/host/step_host.cpp)
+        n_entries = len(entries)
+        counts = [len(entry.tokens) for entry in entries]
+        if n_entries and min(counts) == 1 == max(counts):
+            tokens = [entry.tokens[0] for entry in entries]
+        else:
+            tokens = [t for entry in entries for t in entry.tokens]
+        wants = [w for entry in entries for w in entry.want]
+        Entries = ctypes.c_int * max(1, n_entries)
+        try:
+            slots, starts = Entries(*[entry.slot for entry in entries]), Entries(*[entry.start for entry in entries])
+            token_array = np.asarray(tokens, dtype=np.int64)
+            if token_array.size and (token_array.min() < -2**31 or token_array.max() >= 2**31):
+                bad = int(token_array.min() if token_array.min() < 0 else token_array.max())
+                raise StepError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+            token_array = token_array.astype(np.int32)
+            want_array = (ctypes.c_int * max(1, len(wants)))(*wants)
+        except (TypeError, OverflowError) as error:
+            raise StepError(f"a step entry's numbers must be integers: {error}") from None
         self._copy_event.synchronize()               # the staging buffer of the last step is free again
         self.raise_device_errors()
-        # the metadata is written straight into the pinned staging buffer, a slice per entry:
-        # [tokens n][positions n][slots n][wanted rows][rows of single tokens][rows of portions][portions: row, start, count]
         host = self._meta_host
-        view = self._meta_view
-        token_part, position_part, slot_part = view[0:n], view[n:2 * n], view[2 * n:3 * n]
-        if padding:
-            token_part[real:], position_part[real:], slot_part[real:] = 0, 0, -1
-        for entry, (slot, start, count, offset) in zip(entries, segments):
-            if count == 1:
-                token_part[offset], position_part[offset], slot_part[offset] = entry.tokens[0], start, slot
-            else:
-                token_part[offset:offset + count] = entry.tokens
-                position_part[offset:offset + count] = np.arange(start, start + count, dtype=np.int32)
-                slot_part[offset:offset + count] = slot
-        decode_rows = [offset for _, _, count, offset in segments if count == 1] + list(range(real, n))
-        at = 3 * n
-        view[at:at + n_out] = out_rows
-        at += n_out
-        view[at:at + len(decode_rows)] = decode_rows
-        at += len(decode_rows)
-        for _, _, count, offset in segments:
-            if count > 1:
-                view[at:at + count] = np.arange(offset, offset + count, dtype=np.int32)
-                at += count
-        prefill_segments = [x for _, start, count, offset in segments if count > 1 for x in (offset, start, count)]
-        view[at:at + len(prefill_segments)] = prefill_segments
-        total = 4 * n + n_out + len(prefill_segments)
+        if self._host.lia_step_stage(self.cache.native_handle(), n_entries, slots, starts, Entries(*counts),
+                                     ctypes.c_void_p(token_array.ctypes.data), Entries(*[len(entry.want) for entry in entries]),
+                                     want_array, self.vocab_size, self.max_batch_tokens, self.PAD_ABOVE, self.PAD_TO,
+                                     ctypes.c_void_p(host.data_ptr()), ctypes.c_longlong(host.numel()), self._summary) < 0:
+            message = self._host.lia_host_error()
+            raise StepError(message.decode() if message else "the step was refused")
+        n, n_out, padding, n_single, n_portions, total = self._summary[:6]
+        real = n - padding
+        segments, offset = [], 0
+        for entry, count in zip(entries, counts):
+            segments.append((entry.slot, entry.start, count, offset))
+            offset += count
         self._meta_device[:total].copy_(host[:total], non_blocking=True)
         if feed is not None:
             if any(count != 1 for _, _, count, _ in segments) or feed.numel() < real or feed.dtype != torch.int32:
@@ -221,8 +199,8 @@ class StepRuntime:
         self._copy_event.record()
         dev = self._meta_device
         at = 3 * n + n_out
-        meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:at], dev[at:at + len(decode_rows)],
-                dev[at + len(decode_rows):at + n], dev[at + n:total])
+        meta = (dev[0:n], dev[n:2 * n], dev[2 * n:3 * n], dev[3 * n:at], dev[at:at + n_single],
+                dev[at + n_single:at + n], dev[at + n:total])
         self.h2d_bytes = total * 4
         return StepContext(self, n, n_out, segments, meta, padding)
 
@@ -232,11 +210,9 @@ class StepRuntime:
         """Rows of nobody behind a step of single tokens: beyond PAD_ABOVE entries the batch is brought to a
         multiple of PAD_TO rows (while the step's buffers have room), so that the steps of a batch whose requests
         end one after another are a few shapes, each captured once and replayed, instead of one shape per size
-        (two launched steps each before a replay).  Smaller batches run as they are."""
-        if n_entries != n_tokens or n_tokens <= self.PAD_ABOVE:
-            return 0
-        padded = (n_tokens + self.PAD_TO - 1) // self.PAD_TO * self.PAD_TO
-        return padded - n_tokens if padded <= self.max_batch_tokens else 0
+        (two launched steps each before a replay).  Smaller batches run as they are.  (The native side's rule.)"""
+        return int(host_library().lia_step_padding(int(n_tokens), int(n_entries), self.PAD_ABOVE, self.PAD_TO,
+                                                    self.max_batch_tokens))
 
     def finish(self):
         self._error_host.copy_(self.error_flag, non_blocking=True)

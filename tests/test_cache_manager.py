@@ -197,3 +197,107 @@ def test_staging_ring_waits_for_its_own_copies_before_it_is_written_again():
     device.run_until()
     assert m.groups[0].device_table[s, :len(seen[-1])].tolist() == seen[-1]
     m.check()
+
+
+def plain_staging(entries, reserved, vocab, max_batch_tokens, pad_above=8, pad_to=8):
+    """The step's metadata as plain Python writes it (the oracle of the native staging): returns (words, rows of
+    the batch, wanted rows, rows of nobody, rows of single tokens, portions) or the refusal's message."""
+    out_rows, rows, seen, n = [], [], set(), 0
+    for (slot, tokens, start, want), upto in zip(entries, reserved):
+        count = len(tokens)
+        if count == 0:
+            return "a step entry brings no tokens"
+        if slot in seen:
+            return f"request slot {slot} appears twice in one step"
+        seen.add(slot)
+        if upto < 0:
+            return f"request slot {slot} is not live"
+        if start < 0 or start + count > upto:
+            return f"slot {slot}: positions [{start}, {start + count}) have no reserved pages (reserved up to {upto})"
+        if min(tokens) < 0 or max(tokens) >= vocab:
+            return f"token id {min(tokens) if min(tokens) < 0 else max(tokens)} is outside the vocabulary of {vocab}"
+        for w in want:
+            if not 0 <= w < count:
+                return f"wanted index {w} is outside the entry's {count} tokens"
+            out_rows.append(n + w)
+        rows.append((slot, start, count, n, tokens))
+        n += count
+    if n > max_batch_tokens:
+        return f"{n} tokens in one step exceed max_batch_tokens={max_batch_tokens}"
+    padding = 0
+    if len(rows) == n and n > pad_above and (n + pad_to - 1) // pad_to * pad_to <= max_batch_tokens:
+        padding = (n + pad_to - 1) // pad_to * pad_to - n
+    token_part = [t for _, _, _, _, tokens in rows for t in tokens] + [0] * padding
+    position_part = [start + i for _, start, count, _, _ in rows for i in range(count)] + [0] * padding
+    slot_part = [slot for slot, _, count, _, _ in rows for _ in range(count)] + [-1] * padding
+    out_rows += list(range(n, n + padding))
+    singles = [offset for _, _, count, offset, _ in rows if count == 1] + list(range(n, n + padding))
+    portion_rows = [offset + i for _, _, count, offset, _ in rows if count > 1 for i in range(count)]
+    portions = [x for _, start, count, offset, _ in rows if count > 1 for x in (offset, start, count)]
+    words = token_part + position_part + slot_part + out_rows + singles + portion_rows + portions
+    return words, n + padding, len(out_rows), padding, len(singles), len(portions) // 3
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_native_staging_of_a_step_against_plain_python(seed):
+    """Random batches, good ones and ones with every kind of fault, through the native staging of the step function
+    (csrc/host/step_host.cpp) and through plain Python: the same words, the same counts, the same refusals."""
+    import ctypes
+
+    import numpy as np
+    from lia_rs_b200.cache.pages import host_library
+    rng = random.Random(seed)
+    lib = host_library()
+    m = manager(num_pages=400, page_size=4, max_slots=24)
+    lengths = {}
+    for _ in range(rng.randint(4, 20)):
+        slot = m.admit()
+        lengths[slot] = rng.randint(1, 60)
+        assert m.ensure(slot, 0, lengths[slot])
+    vocab, budget = 97, 96
+    meta = np.full(7 * budget, -7, dtype=np.int32)
+    summary = (ctypes.c_int * 8)()
+    refusals = 0
+    for trial in range(300):
+        chosen = rng.sample(sorted(lengths), rng.randint(1, len(lengths)))
+        singles_only = rng.random() < 0.5
+        entries = []
+        for slot in chosen:
+            count = 1 if singles_only else rng.randint(1, min(12, lengths[slot]))
+            start = rng.randint(0, lengths[slot] - count)
+            want = sorted(rng.sample(range(count), rng.randint(0, min(count, 2))))
+            entries.append([slot, [rng.randrange(vocab) for _ in range(count)], start, want])
+        fault = rng.randrange(12)
+        victim = rng.randrange(len(entries))
+        if fault == 0:
+            entries[victim][1] = []
+        elif fault == 1 and len(entries) > 1:
+            entries[victim][0] = entries[victim - 1][0]
+        elif fault == 2:
+            entries[victim][0] = rng.choice([-1, 24, 23 if 23 not in lengths else 99])
+        elif fault == 3:
+            entries[victim][2] = lengths[entries[victim][0]] - len(entries[victim][1]) + 1
+        elif fault == 4:
+            entries[victim][1][rng.randrange(len(entries[victim][1]))] = rng.choice([-1, vocab, 10**6])
+        elif fault == 5:
+            entries[victim][3] = [len(entries[victim][1])]
+        reserved = m.reserved([e[0] for e in entries])
+        expected = plain_staging(entries, reserved, vocab, budget)
+        n_entries = len(entries)
+        Entries = ctypes.c_int * n_entries
+        tokens = [t for e in entries for t in e[1]]
+        wants = [w for e in entries for w in e[3]]
+        meta[:] = -7
+        rc = lib.lia_step_stage(m.native_handle(), n_entries, Entries(*[e[0] for e in entries]), Entries(*[e[2] for e in entries]),
+                                Entries(*[len(e[1]) for e in entries]), (ctypes.c_int * max(1, len(tokens)))(*tokens),
+                                Entries(*[len(e[3]) for e in entries]), (ctypes.c_int * max(1, len(wants)))(*wants), vocab, budget,
+                                8, 8, ctypes.c_void_p(meta.ctypes.data), ctypes.c_longlong(meta.size), summary)
+        if isinstance(expected, str):
+            refusals += 1
+            assert rc < 0 and lib.lia_host_error().decode() == expected
+            continue
+        words, n, n_out, padding, n_single, n_portions = expected
+        assert rc == 0, lib.lia_host_error().decode()
+        assert list(summary[:6]) == [n, n_out, padding, n_single, n_portions, len(words)]
+        assert meta[:len(words)].tolist() == words and (meta[len(words):] == -7).all()
+    assert 60 < refusals < 250

@@ -166,7 +166,11 @@ class StepRuntime:
         wants = [w for entry in entries for w in entry.want]
         Entries = ctypes.c_int * max(1, n_entries)
         try:
-            slots, starts = Entries(*[entry.slot for entry in entries]), Entries(*[entry.start for entry in entries])
+            slot_list, start_list = [entry.slot for entry in entries], [entry.start for entry in entries]
+            for values in (slot_list, start_list, wants):       # (a ctypes integer would wrap silently)
+                if values and not (-2**31 <= min(values) and max(values) < 2**31):
+                    raise StepError("a step entry's slot, start and wanted places must fit 32 bits")
+            slots, starts = Entries(*slot_list), Entries(*start_list)
             token_array = np.asarray(tokens, dtype=np.int64)
             if token_array.size and (token_array.min() < -2**31 or token_array.max() >= 2**31):
                 bad = int(token_array.min() if token_array.min() < 0 else token_array.max())
